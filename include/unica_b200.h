@@ -1,0 +1,101 @@
+/* unica_b200: C ABI of the B200 (sm_100a) forward quantized attention.
+ *
+ * The reference reaches its kernels through the CUDA driver API from Python: `module("flash")[name](grid, block, *args)`
+ * looks an `extern "C" __global__` symbol up by name and launches it with positional arguments (unica/cuda.py:138-160;
+ * call sites in unica/__init__.py).  This library replaces that boundary by host entry points, one per reference
+ * kernel launch, with plain pointers and sizes: the launch geometry, shared-memory sizes and tensor-memory use are its
+ * own business.  A binding needs nothing but dlopen/ctypes.
+ *
+ * Conventions
+ *   - every pointer is a device pointer on the current CUDA device unless said otherwise; nothing here allocates,
+ *     frees or synchronises (except where an entry point says so); work is queued on `stream` (a cudaStream_t; NULL
+ *     is the default stream);
+ *   - `heads` is batch * heads; inputs are bf16 [batch, heads, tokens, 128] in any strides with a contiguous last
+ *     dimension and 16-byte aligned tokens, described by unica_token_layout;
+ *   - return value 0 = queued; otherwise one of the UNICA_B200_ERR_* codes, and unica_b200_last_error() gives the
+ *     message (thread-local).
+ *
+ * Operand layouts written by the quantizers and read by the attention kernels (all per head, tiles in token order):
+ *   Q8   [q_tiles][8][128 rows][16]  int8, q_tiles rounded up to even, 16 KB per tile of 128 queries
+ *   K8   [k_tiles][8][ 64 rows][16]  int8, 8 KB per tile of 64 keys          (chunk c, row r: channels 16c..16c+15 of key r)
+ *   V8   [k_tiles][4][128 chan][16]  int8, 8 KB per tile                     (chunk c, channel d: keys 16c..16c+15)
+ *   v_token [k_tiles][2][64] float: log2 s_j then 1 / s_j of the tile's keys (per-token mode)
+ * These are the shared-memory images tcgen05.mma reads (K-major, no swizzle: core matrices of 8 rows x 16 bytes), so a
+ * tile is one contiguous bulk copy.  Rows past the last token are zeros.
+ */
+#ifndef UNICA_B200_H
+#define UNICA_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Strides in elements of a [batch, heads, tokens, 128] tensor, and its heads: the reference's TokenLayout
+ * (csrc/flash.cu:231-237, unica/__init__.py:92-100), field for field. */
+typedef struct {
+    long long batch, head, token;
+    int heads;
+} unica_token_layout;
+
+enum {
+    UNICA_B200_OK = 0,
+    UNICA_B200_ERR_ARGUMENT = 1, /* a size, pointer or mode the entry point does not take */
+    UNICA_B200_ERR_CUDA = 2,     /* the CUDA runtime refused the launch or a set-up call */
+    UNICA_B200_ERR_DEVICE = 3,   /* not an sm_100 device */
+    UNICA_B200_ERR_KERNEL = 4    /* a kernel reported a non-zero status word (unica_b200_read_status) */
+};
+
+/* V scale modes of the accurate kernel (the reference's V_TOKEN / V_OUTLIERS build settings, unica/__init__.py:88-89) */
+enum { UNICA_B200_V_CHANNEL = 0, UNICA_B200_V_TOKEN = 1 };
+
+const char* unica_b200_last_error(void);
+int unica_b200_version(void);
+
+/* Replaces rope_stats + the torch reduction over its partials (csrc/flash.cu:287-327; unica/__init__.py:580-612).
+ * Per channel of each head, over each group of `per` tokens (0: the whole head; else a multiple of 256): mean, min,
+ * max, float [heads][groups][128].  partial: scratch, float [heads][ceil(n_tokens / 256)][3][128].  Sums run in a
+ * fixed order, so results do not depend on how many heads a call holds. */
+int unica_b200_channel_stats(const void* x, unica_token_layout layout, int heads, int n_tokens, int per, float* partial,
+                             float* mean, float* low, float* high, void* stream);
+
+/* Replaces quantize_int8 (csrc/flash.cu:334-372; unica/__init__.py:363-378).  x - mean (mean float [heads][128] or
+ * NULL) in INT8 with one scale per block_tokens tokens: 128 for Q, 64 for K.  `tiles` >= ceil(n_tokens /
+ * block_tokens) tiles are written (the extra ones zeros): the attention kernel wants Q8 with an even tile count.
+ * codes: Q8 / K8 layout above; scales: float [heads][tiles]. */
+int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const float* mean, int heads, int n_tokens,
+                             int block_tokens, int tiles, int8_t* codes, float* scales, void* stream);
+
+/* Replaces quantize_v and the torch aminmax before it (csrc/flash.cu:590-630; unica/__init__.py:402-444).
+ * per_token = 0: one scale per channel from the channel's min and max over the head (low, high float [heads][128],
+ * from unica_b200_channel_stats), written to v_scale [heads][128].  per_token = 1: one scale per key over its
+ * channels; v_scale becomes ones and v_token gets {log2 s, 1 / s}.  skip: uint8 [heads][n_tokens], 1 = write the key
+ * as zeros (the outlier keys), or NULL. */
+int unica_b200_quantize_v_int8(const void* v, unica_token_layout layout, const float* low, const float* high,
+                               const uint8_t* skip, int per_token, int heads, int n_tokens, int8_t* v8, float* v_scale,
+                               float* v_token, void* stream);
+
+/* Replaces attention_int8pv_tma (csrc/flash.cu:806-959; launched from unica/__init__.py:179-189).  The accurate mode:
+ * S = Q8.K8^T on tcgen05 kind::i8, softmax in the log2 domain against each 64-key tile's own maximum, P as u8,
+ * P.V8 on kind::i8 (u8 x s8), flushed into a float accumulator with alpha / beta every tile.
+ * out: bf16 in out_layout.  scale_log2 = log2(e) / sqrt(128).  status: device int the kernel leaves non-zero if one
+ * of its bounded waits gave up (must be 0 on entry), or NULL. */
+int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
+                              const int8_t* v8, const float* v_scale, const float* v_token, int v_mode, void* out,
+                              unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
+                              int* status, void* stream);
+
+/* Hardware self-test of the tensor-core path (the idea of the reference's tests/test_mma.py: small integers make every
+ * result exact, so a wrong lane or layout cannot hide).  One tcgen05.mma kind::i8 chain D[128 x n] = A[128 x k] . B[n x k]^T
+ * with A (u8 if a_unsigned, else s8) and B (s8) given as the shared-memory images described above
+ * ([k / 16][rows][16] bytes); d gets int32 [128][n] row-major.  variant 0 describes the operands as the attention
+ * kernels do; 1 exchanges the descriptor's two byte offsets (a diagnostic, expected to give wrong results).
+ * Allocates a status word and synchronises the stream: not for the hot path. */
+int unica_b200_selftest_mma_i8(const void* a_image, const void* b_image, int n, int k, int a_unsigned, int variant,
+                               int32_t* d, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

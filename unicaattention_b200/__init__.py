@@ -1,0 +1,357 @@
+"""unicaattention_b200: UnicaAttention's forward quantized attention, rebuilt for the B200 (sm_100a).
+
+    import unicaattention_b200 as unica
+    out = unica.attention(q, k, v, **unica.PRESETS["per_channel"])   # [batch, heads, tokens, 128] bf16
+
+The call surface is the reference's (unica/__init__.py): `attention`, `kernel_inputs`, `PRESETS`, the quantizer
+functions, `TokenLayout`, the head-split planner, `compatibility`.  Underneath, every device step is an entry point of
+libunica_b200.so (include/unica_b200.h): hand-written sm_100a kernels, tcgen05 tensor cores with accumulators in
+tensor memory, K/V tiles staged by bulk TMA copies.  There is no CPU path and no other backend: without the library
+or a B200 the calls raise.
+
+What differs from the reference, on purpose: the packed operand layouts the quantizers return are this library's
+(the shared-memory images of the tcgen05 operands, see include/unica_b200.h), not the sm_120 fragment layouts; the
+`decode_*` helpers turn them back into plain [batch, heads, tokens, 128] codes for comparisons.  Build settings that
+only steered the sm_120 kernels (WARPS_PER_BLOCK, PRODUCER, WAVE_DISPATCH) are accepted and have no effect.
+"""
+
+from __future__ import annotations
+
+import functools
+import math
+import os
+import warnings
+
+import torch
+
+from unicaattention_b200 import lib
+from unicaattention_b200.check import OK, UNSUPPORTED, UNTESTED, Compatibility, compatibility, machine  # noqa: F401
+from unicaattention_b200.lib import TokenLayout
+
+HEAD_DIM = 128
+Q_SCALE_BLOCK = 128  # queries per Q scale = rows of one tcgen05.mma
+K_SCALE_BLOCK = 64  # keys per K scale = keys per softmax tile (part of the numerics contract)
+KEYS_PER_TILE = 64
+V8_PAD_KEYS = 64  # V8 is padded to whole tiles
+FP4_TILE = 64
+STATS_TOKENS = 256
+LOG2E = 1.4426950408889634
+
+# The two production modes, under the reference's kernel names (unica/__init__.py:34-40, 88-89).
+KERNELS = ("attention_int8pv_tma", "attention_fp4")
+QUANTIZED = set(KERNELS)
+LAYOUT_KERNELS = set(KERNELS)  # both read q, k, v and write the output in the caller's layout
+DEFAULT_KERNEL = "attention_int8pv_tma"
+# Settings a call may pass (the reference's TILE).  The first three select numerics; the others steered the sm_120
+# kernels' shape and are accepted for drop-in compatibility only.
+TILE = {"V_TOKEN": 0, "V_OUTLIERS": 0, "SMOOTH_Q": 0, "KEYS_PER_TILE": 64, "WARPS_PER_BLOCK": 4, "PRODUCER": 0,
+        "WAVE_DISPATCH": 0}
+PRESETS = {"per_token": dict(V_TOKEN=1, WAVE_DISPATCH=1), "per_channel": dict(PRODUCER=1, WAVE_DISPATCH=1),
+           "outliers": dict(V_OUTLIERS=8), "fast": dict(kernel="attention_fp4", SMOOTH_Q=512)}
+
+VRAM_RESERVE: int | None = (int(os.environ["UNICA_VRAM_RESERVE_MB"]) * 2**20
+                             if "UNICA_VRAM_RESERVE_MB" in os.environ else None)
+LOG_VRAM = os.environ.get("UNICA_LOG_VRAM") == "1"
+SMALL_CALL_FRACTION = 4
+
+
+def warn_if_untested() -> None:
+    """Says once, as the reference does on import, when this machine is not the measured combination."""
+    status = compatibility()
+    if status.status != OK:
+        warnings.warn(str(status), stacklevel=2)
+
+
+if os.environ.get("UNICA_QUIET") != "1" and torch.cuda.is_available():
+    warn_if_untested()
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# layouts
+
+
+def token_layout(x: torch.Tensor) -> TokenLayout:
+    return TokenLayout(x.stride(0), x.stride(1), x.stride(2), x.shape[1])
+
+
+def readable(x: torch.Tensor) -> torch.Tensor:
+    """x itself if the kernels can read it in place (contiguous last dimension, 16-byte aligned tokens), else a
+    contiguous copy (unica/__init__.py:103-108)."""
+    in_place = (x.stride(-1) == 1 and x.data_ptr() % 16 == 0
+                and all(x.stride(i) % 8 == 0 or x.shape[i] == 1 for i in range(3)))
+    return x if in_place else x.contiguous()
+
+
+def on_their_device(function):
+    """Runs function(q, ...) with q's device current: launches go to that device's context and current stream."""
+
+    @functools.wraps(function)
+    def run(q, *args, **kwargs):
+        with torch.cuda.device(q.device):
+            return function(q, *args, **kwargs)
+
+    return run
+
+
+def _check_input(x: torch.Tensor, what: str) -> None:
+    if not x.is_cuda:
+        raise ValueError(f"{what} must be on the GPU")
+    if x.dtype != torch.bfloat16:
+        raise TypeError(f"{what} must be bfloat16, got {x.dtype}")
+    if x.dim() != 4 or x.shape[-1] != HEAD_DIM:
+        raise ValueError(f"{what} must be [batch, heads, tokens, {HEAD_DIM}], got {tuple(x.shape)}")
+    if x.shape[2] == 0:
+        raise ValueError(f"{what} must hold at least one token")
+
+
+_status_words: dict = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """The int32 word the attention kernels leave non-zero when one of their bounded waits gave up; one per device."""
+    device = torch.device(device)
+    if device not in _status_words:
+        _status_words[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[device]
+
+
+def check_status(device=None) -> None:
+    """Synchronises and raises RuntimeError if a kernel reported a pipeline time-out since the last check.  The hot
+    path never calls this (it would wait for the GPU); tests and the self-test do."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    word = status_word(device)
+    code = int(word.item())
+    if code:
+        word.zero_()
+        raise RuntimeError(f"a unica-b200 kernel gave up waiting (status {code}, see common.cuh Status)")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# statistics
+
+
+def _stats(x: torch.Tensor, per: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    batch, heads, n, _ = x.shape
+    blocks = math.ceil(n / STATS_TOKENS)
+    groups = 1 if per == 0 else math.ceil(n / per)
+    partial = torch.empty(batch * heads, blocks, 3, HEAD_DIM, device=x.device)
+    mean, low, high = (torch.empty(batch, heads, groups, HEAD_DIM, device=x.device) for _ in range(3))
+    lib.call("unica_b200_channel_stats", lib.ptr(x), token_layout(x), batch * heads, n, per, lib.ptr(partial),
+             lib.ptr(mean), lib.ptr(low), lib.ptr(high), lib.stream())
+    return mean, low, high
+
+
+@on_their_device
+def rope_stats(x: torch.Tensor, rope: torch.Tensor | None = None, per: int | None = None):
+    """Per channel of each head over all tokens of x: mean, min, max, float32 [batch, heads, 128]; with per (a multiple
+    of 256) over each block of that many tokens, [batch, heads, blocks, 128] (unica/__init__.py:592-612).  One pass
+    over x; sums in a fixed order, so the mean does not depend on how many heads the call holds."""
+    _no_rope(rope)
+    _check_input(x, "x")
+    if per is not None and per % STATS_TOKENS:
+        raise ValueError(f"per must be a multiple of {STATS_TOKENS}, got {per}")
+    mean, low, high = _stats(readable(x), per or 0)
+    return (mean, low, high) if per else (mean[:, :, 0], low[:, :, 0], high[:, :, 0])
+
+
+def _no_rope(rope) -> None:
+    if rope is not None:
+        raise NotImplementedError("rope= (RoPE fused into the quantizers) is not built yet in the B200 library")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# INT8 quantizers
+
+
+@on_their_device
+def quantize_int8(x: torch.Tensor, mean: torch.Tensor | None, block: int, rope: torch.Tensor | None = None,
+                  tiles: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """x - mean ~ x8 * scale with one scale per `block` tokens over all of d (128: Q, 64: K); bit for bit the
+    reference's quant() (unica/__init__.py:363-378).  mean: float32 [batch, heads, 128] or None.
+    Returns int8 [batch, heads, tiles, 8, block, 16] (tile, 16-channel chunk, token, channel: the tcgen05 operand
+    image; `decode_int8` gives [batch, heads, N, 128]) and float32 scales [batch, heads, tiles]."""
+    _no_rope(rope)
+    _check_input(x, "x")
+    x = readable(x)
+    batch, heads, n, _ = x.shape
+    need = math.ceil(n / block)
+    tiles = need if tiles is None else tiles
+    x8 = torch.empty(batch, heads, tiles, HEAD_DIM // 16, block, 16, dtype=torch.int8, device=x.device)
+    scale = torch.empty(batch, heads, tiles, device=x.device)
+    mean = None if mean is None else mean.float().contiguous()
+    lib.call("unica_b200_quantize_int8", lib.ptr(x), token_layout(x), lib.ptr(mean), batch * heads, n, block, tiles,
+             lib.ptr(x8), lib.ptr(scale), lib.stream())
+    return x8, scale
+
+
+def decode_int8(x8: torch.Tensor, n: int) -> torch.Tensor:
+    """quantize_int8's codes as plain int8 [batch, heads, n, 128]."""
+    batch, heads, tiles, chunks, block, _ = x8.shape
+    return x8.permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles * block, HEAD_DIM)[:, :, :n]
+
+
+@on_their_device
+def quantize_v(v: torch.Tensor, layout: int = 2, per_token: bool = False, outliers: int = 0) -> tuple[torch.Tensor, ...]:
+    """v ~ v8 * scale (unica/__init__.py:402-444).  Per channel (default): one scale per channel over the head's
+    tokens, float32 [batch, heads, 128].  per_token: one scale per token over its channels; returns v8, a scale of ones
+    and float32 [batch, heads, tiles, 2, 64] = log2 s then 1 / s of each tile's keys (zeros past N).
+    v8: int8 [batch, heads, tiles, 4, 128, 16] (tile, 16-key chunk, channel, key: the K-major operand of P.V);
+    `decode_v8` gives [batch, heads, N, 128].  `layout` is accepted for compatibility: there is one layout here."""
+    if outliers:
+        raise NotImplementedError("outliers= (V_OUTLIERS) is not built yet in the B200 library")
+    _check_input(v, "v")
+    v = readable(v)
+    batch, heads, n, _ = v.shape
+    tiles = math.ceil(n / V8_PAD_KEYS)
+    v8 = torch.empty(batch, heads, tiles, 4, HEAD_DIM, 16, dtype=torch.int8, device=v.device)
+    scale = torch.empty(batch, heads, HEAD_DIM, device=v.device)
+    low = high = tokens = None
+    if per_token:
+        tokens = torch.empty(batch, heads, tiles, 2, V8_PAD_KEYS, device=v.device)
+    else:
+        _, low, high = _stats(v, 0)
+    lib.call("unica_b200_quantize_v_int8", lib.ptr(v), token_layout(v), lib.ptr(low), lib.ptr(high), lib.ptr(None),
+             int(per_token), batch * heads, n, lib.ptr(v8), lib.ptr(scale), lib.ptr(tokens), lib.stream())
+    return (v8, scale, tokens) if per_token else (v8, scale)
+
+
+def decode_v8(v8: torch.Tensor, n: int) -> torch.Tensor:
+    """quantize_v's codes as plain int8 [batch, heads, n, 128]."""
+    batch, heads, tiles = v8.shape[:3]
+    return v8.permute(0, 1, 2, 3, 5, 4).reshape(batch, heads, tiles * V8_PAD_KEYS, HEAD_DIM)[:, :, :n]
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# the call
+
+
+@on_their_device
+def kernel_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = DEFAULT_KERNEL,
+                  rope: torch.Tensor | None = None, **tile: int) -> tuple:
+    """The quantized operands `kernel` takes, apart from attention() so that quantization and kernel can be timed
+    separately (unica/__init__.py:288-356)."""
+    _no_rope(rope)
+    settings = _settings(kernel, tile)
+    if kernel == "attention_fp4":
+        raise NotImplementedError("the fast mode (attention_fp4) is not built yet in the B200 library")
+    q, k, v = readable(q), readable(k), readable(v)
+    q_tiles = 2 * math.ceil(q.shape[2] / (2 * Q_SCALE_BLOCK))  # the kernel takes query tiles in pairs
+    q8, q_scale = quantize_int8(q, None, Q_SCALE_BLOCK, tiles=q_tiles)
+    k_mean = rope_stats(k)[0]  # softmax cancels the mean
+    k8, k_scale = quantize_int8(k, k_mean, K_SCALE_BLOCK)
+    if settings["V_TOKEN"]:
+        v8, v_scale, v_token = quantize_v(v, per_token=True)
+        return q8, q_scale, k8, k_scale, v8, v_scale, v_token, lib.V_TOKEN
+    if settings["V_OUTLIERS"]:
+        raise NotImplementedError("V_OUTLIERS is not built yet in the B200 library")
+    v8, v_scale = quantize_v(v)
+    return q8, q_scale, k8, k_scale, v8, v_scale, None, lib.V_CHANNEL
+
+
+def _settings(kernel: str, tile: dict) -> dict:
+    if kernel not in KERNELS:
+        raise ValueError(f"unknown kernel {kernel!r}, expected one of {KERNELS}")
+    if unknown := tile.keys() - TILE.keys():
+        raise ValueError(f"unknown tile settings {sorted(unknown)}, expected some of {sorted(TILE)}")
+    settings = TILE | tile
+    if settings["KEYS_PER_TILE"] != KEYS_PER_TILE:
+        raise ValueError(f"KEYS_PER_TILE is fixed at {KEYS_PER_TILE}: it is part of the numerics")
+    return settings
+
+
+@on_their_device
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = DEFAULT_KERNEL,
+              inputs: tuple | None = None, rope: torch.Tensor | None = None, **tile: int) -> torch.Tensor:
+    """softmax(q k^T / sqrt(d)) v, non-causal.  q [batch, heads, n_queries, 128]; k, v [batch, heads, n_keys, 128]; all
+    bfloat16 or all float16, on a B200.  Returns a tensor like q (dtype and strides).  kernel / tile pick the mode, as
+    in PRESETS.  inputs: what kernel_inputs() returned for these q, k, v; the kernel then runs alone.
+    Same checks and exceptions as the reference (unica/__init__.py:126-190)."""
+    settings = _settings(kernel, tile)
+    if not (q.dtype == k.dtype == v.dtype and q.dtype in (torch.bfloat16, torch.float16)):
+        raise TypeError(f"q, k, v must all be bfloat16 or all float16, got {q.dtype}, {k.dtype}, {v.dtype}")
+    if inputs is not None and q.dtype != torch.bfloat16:
+        raise TypeError("with inputs=, q, k, v must be bfloat16")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise ValueError("q, k, v must be on the GPU")
+    if q.dim() != 4 or q.shape[-1] != HEAD_DIM:
+        raise ValueError(f"q must be [batch, heads, tokens, {HEAD_DIM}], got {tuple(q.shape)}")
+    if k.shape != v.shape or k.shape[:2] != q.shape[:2] or k.shape[-1] != HEAD_DIM:
+        raise ValueError(f"k and v must be [batch, heads, n_keys, {HEAD_DIM}] like q, "
+                         f"got q {tuple(q.shape)}, k {tuple(k.shape)}, v {tuple(v.shape)}")
+    batch, heads, n_queries, _ = q.shape
+    n_keys = k.shape[2]
+    if n_keys == 0:
+        raise ValueError("k and v must hold at least one token")
+    _no_rope(rope)
+    if inputs is None and (q.dtype != torch.bfloat16 or heads_per_call(q, k, kernel, tile) < heads):
+        return in_pieces(q, k, v, kernel, rope, tile)
+    q, k, v = readable(q), readable(k), readable(v)
+    out = torch.empty_like(q)
+    if n_queries == 0:
+        return out
+    if inputs is None:
+        inputs = kernel_inputs(q, k, v, kernel, rope, **tile)
+    if kernel == "attention_fp4":
+        raise NotImplementedError("the fast mode (attention_fp4) is not built yet in the B200 library")
+    q8, q_scale, k8, k_scale, v8, v_scale, v_token, v_mode = inputs
+    lib.call("unica_b200_attention_int8", lib.ptr(q8), lib.ptr(q_scale), lib.ptr(k8), lib.ptr(k_scale), lib.ptr(v8),
+             lib.ptr(v_scale), lib.ptr(v_token), v_mode, lib.ptr(out), token_layout(out), batch * heads, n_queries,
+             n_keys, HEAD_DIM**-0.5 * LOG2E, lib.ptr(status_word(q.device)), lib.stream())
+    del settings
+    return out
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# the head-split planner (unica/__init__.py:193-245): on a 180 GB part it rarely splits, but the contract stays
+
+
+def free_vram(device: torch.device) -> int:
+    """Bytes the driver has free on the device; does not wait for the GPU."""
+    free, _ = torch.cuda.mem_get_info(device)
+    return free
+
+
+def vram_reserve(device: torch.device) -> int:
+    if VRAM_RESERVE is not None:
+        return VRAM_RESERVE
+    return max(2**30, torch.cuda.get_device_properties(device).total_memory // 10)
+
+
+def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) -> int:
+    """How many heads one call takes without its temporary buffers reaching the reserve.  Per head: the quantized q, k,
+    v and the output, at most 2 bytes per element of q, k, v; 2 more for bf16 copies of float16 inputs.  (The fast
+    mode's smoothing term is computed inside the kernel here, so it adds no table.)  A small call runs whole."""
+    batch, heads, n_queries, _ = q.shape
+    n_keys = k.shape[2]
+    elements = batch * HEAD_DIM * (n_queries + 2 * n_keys)
+    per_head = max(1, elements * (2 + (2 if q.dtype != torch.bfloat16 else 0)))
+    free, reserve = free_vram(q.device), vram_reserve(q.device)
+    if heads * per_head <= min(reserve // SMALL_CALL_FRACTION, free):
+        step = heads
+    else:
+        step = max(1, min(heads, (free - reserve) // per_head))
+    if LOG_VRAM:
+        print(f"[unica vram] tokens {n_queries} heads {heads} {q.dtype} driver_free {free / 2**30:.2f} "
+              f"reserve {reserve / 2**30:.2f} per_head {per_head / 2**30:.3f} GiB -> {step} heads per call", flush=True)
+    return step
+
+
+def in_pieces(q, k, v, kernel: str, rope, tile: dict) -> torch.Tensor:
+    """attention() a few heads at a time, each piece converted to bfloat16 on its own, into one output in q's dtype and
+    layout.  Every head has its own statistics and scales, summed in a fixed order, so the result is bit for bit that
+    of one call."""
+    out = torch.empty_like(q)
+    step = heads_per_call(q, k, kernel, tile)
+    for first in range(0, q.shape[1], step):
+        piece = slice(first, first + step)
+        out[:, piece] = attention(*(x[:, piece].to(torch.bfloat16) for x in (q, k, v)), kernel, None, rope, **tile)
+    return out
+
+
+_SM_COUNTS: dict = {}
+
+
+def sm_count(device: torch.device) -> int:
+    if device not in _SM_COUNTS:
+        _SM_COUNTS[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNTS[device]

@@ -1,0 +1,431 @@
+// The accurate mode's flash-attention loop on tcgen05 (replaces the reference's attention_int8pv_tma, csrc/flash.cu:806-959).
+//
+// One block = 256 query rows of one head = two tiles of 128 rows, each owned by one warpgroup of 4 warps in which a
+// thread owns one query row (tensor-memory lane = row, so row maxima and sums need no shuffles).  Both warpgroups share
+// every K and V tile.  Warp 8 streams K8 / V8 tiles (contiguous 8 KB images written by the quantizers) into a ring of
+// shared-memory stages with bulk TMA copies; one thread of warp 9 issues every tcgen05.mma:
+//
+//   S[g]   = Q8[g] . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, double-buffered in tensor memory
+//   acc[g] = P^[g](t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, fresh accumulator every tile
+//
+// Numerics (bench/emulate.py:298-369 with the accurate contract): scores in the log2 domain, c = (q_scale * k_scale) *
+// log2(e) / sqrt(d); P^ = rint(255 * 2^(x - tile max)) as u8 against the tile's own maximum; the denominator sums the
+// rounded P^ (per channel) or p / s_j in float before rounding (per token); every tile is flushed as
+// out = out * alpha + beta * float(acc) with alpha = 2^(m_old - m_new), beta = 2^(m_tile - m_new).
+// The 255 stays in numerator and denominator alike (as csrc/flash.cu:409-414 does).
+//
+// Tensor memory: 512 columns = per warpgroup S x 2 (64 each) + acc (128).  All waits are bounded (common.cuh).
+#include "capi.h"
+
+namespace unica {
+
+constexpr int ATT_THREADS = 384;  // 8 softmax/flush warps + a warpgroup holding the producer warp and the MMA warp
+constexpr int COMPUTE_REGISTERS = 232, SERVICE_REGISTERS = 40;  // registers move from the third warpgroup to the two that hold `out`
+constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
+constexpr int STAGES = 3;
+constexpr int Q_BYTES = QUERY_TILE * HEAD_DIM;  // 16384
+constexpr int K_BYTES = KEY_TILE * HEAD_DIM;    // 8192
+constexpr int V_BYTES = KEY_TILE * HEAD_DIM;    // 8192
+constexpr int TOK_BYTES = 2 * KEY_TILE * 4;     // 512
+constexpr int P_BYTES = QUERY_TILE * KEY_TILE;  // 8192
+constexpr int TMEM_COLUMNS = 512;
+
+struct __align__(128) AttSmem {
+    int8_t q[2][Q_BYTES];
+    int8_t k[STAGES][K_BYTES];
+    int8_t v[STAGES][V_BYTES];
+    float tok[STAGES][2 * KEY_TILE];
+    uint8_t p[2][2][P_BYTES];
+    uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
+constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM);
+
+template <bool V_TOKEN>
+__global__ void __launch_bounds__(ATT_THREADS, 1)
+    attention_int8_kernel(const int8_t* __restrict__ q8, const float* __restrict__ q_scale, const int8_t* __restrict__ k8,
+                          const float* __restrict__ k_scale, const int8_t* __restrict__ v8, const float* __restrict__ v_scale,
+                          const float* __restrict__ v_token, __nv_bfloat16* __restrict__ out, TokenLayout out_layout,
+                          int n_queries, int n_keys, float scale_log2, int* status) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    AttSmem& sm = *reinterpret_cast<AttSmem*>(smem_raw);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int head = blockIdx.y;
+    const int q_tiles = 2 * gridDim.x;  // allocated Q tiles per head (even)
+    const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sm.abort_flag = 0;
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        for (int g = 0; g < 2; ++g) {
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(&sm.s_full[g][b], 1);
+                mbar_init(&sm.s_free[g][b], 128);
+                mbar_init(&sm.p_ready[g][b], 128);
+            }
+            mbar_init(&sm.acc_full[g], 1);
+            mbar_init(&sm.acc_free[g], 128);
+        }
+        mbar_init(&sm.drain, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) tmem_alloc(&sm.tmem_base, TMEM_COLUMNS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SERVICE_REGISTERS));
+      if (warp == PRODUCER_WARP) {
+        // ------------------------------------------------------------------------------------------------ producer
+        if (lane == 0) {
+            const int8_t* q_src = q8 + (size_t(head) * q_tiles + 2 * blockIdx.x) * Q_BYTES;
+            mbar_expect_tx(&sm.q_full, 2 * Q_BYTES);
+            bulk_load(sm.q[0], q_src, Q_BYTES, &sm.q_full);
+            bulk_load(sm.q[1], q_src + Q_BYTES, Q_BYTES, &sm.q_full);
+            int issued = 0;
+            for (int t = 0; t < k_tiles; ++t) {
+                const int s = t % STAGES, use = t / STAGES;
+                if (use > 0 && !mbar_wait(&sm.k_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) break;
+                mbar_expect_tx(&sm.k_full[s], K_BYTES);
+                bulk_load(sm.k[s], k8 + (size_t(head) * k_tiles + t) * K_BYTES, K_BYTES, &sm.k_full[s]);
+                if (use > 0 && !mbar_wait(&sm.v_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) {
+                    issued = t + 1;  // K of tile t is in flight, V is not
+                    break;
+                }
+                mbar_expect_tx(&sm.v_full[s], V_BYTES + (V_TOKEN ? TOK_BYTES : 0));
+                bulk_load(sm.v[s], v8 + (size_t(head) * k_tiles + t) * V_BYTES, V_BYTES, &sm.v_full[s]);
+                if (V_TOKEN) bulk_load(sm.tok[s], v_token + (size_t(head) * k_tiles + t) * (2 * KEY_TILE), TOK_BYTES, &sm.v_full[s]);
+                issued = t + 1;
+            }
+            if (*abort_flag) {  // let the copies still in flight land before the block's shared memory goes away
+                int never = 0;
+                for (int t = max(0, issued - STAGES); t < issued; ++t)
+                    mbar_wait(&sm.k_full[t % STAGES], (t / STAGES) & 1, &never, nullptr, 0);
+                mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
+            }
+        }
+      } else if (warp == MMA_WARP) {
+        // ------------------------------------------------------------------------------------------------ MMA issue
+        if (lane == 0) {
+            const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
+            auto issue_scores = [&](int g, int stage, int buf) {
+                const uint32_t k_addr = smem_u32(sm.k[stage]);
+#pragma unroll
+                for (int ks = 0; ks < HEAD_DIM / 32; ++ks)
+                    mma_i8_ss(tmem + g * 256 + buf * 64, smem_desc(q_addr[g] + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                              smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_QK, ks > 0);
+            };
+            auto issue_pv = [&](int g, int stage, int buf) {
+                const uint32_t p_addr = smem_u32(sm.p[g][buf]), v_addr = smem_u32(sm.v[stage]);
+#pragma unroll
+                for (int ks = 0; ks < KEY_TILE / 32; ++ks)
+                    mma_i8_ss(tmem + g * 256 + 128, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, ks > 0);
+            };
+            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
+                      mbar_wait(&sm.k_full[0], 0, abort_flag, status, STATUS_WAIT_TILE);
+            if (ok) {
+                tc_fence_after();
+                for (int g = 0; g < 2; ++g) {
+                    issue_scores(g, 0, 0);
+                    mma_commit(&sm.s_full[g][0]);
+                }
+                mma_commit(&sm.k_empty[0]);
+            }
+            for (int t = 0; ok && t < k_tiles; ++t) {
+                if (t + 1 < k_tiles) {  // scores of the next tile first: the softmax threads never wait for them
+                    const int n = t + 1, s = n % STAGES, buf = n & 1;
+                    ok = mbar_wait(&sm.k_full[s], (n / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+                    for (int g = 0; ok && g < 2; ++g) {
+                        if (n >= 2) ok = mbar_wait(&sm.s_free[g][buf], ((n >> 1) - 1) & 1, abort_flag, status, STATUS_WAIT_FREE);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_scores(g, s, buf);
+                        mma_commit(&sm.s_full[g][buf]);
+                    }
+                    if (!ok) break;
+                    mma_commit(&sm.k_empty[s]);
+                }
+                const int s = t % STAGES, buf = t & 1;
+                ok = mbar_wait(&sm.v_full[s], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+                for (int g = 0; ok && g < 2; ++g) {
+                    ok = mbar_wait(&sm.p_ready[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P);
+                    if (ok && t >= 1) ok = mbar_wait(&sm.acc_free[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_FREE);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(g, s, buf);
+                    mma_commit(&sm.acc_full[g]);
+                }
+                if (!ok) break;
+                mma_commit(&sm.v_empty[s]);
+            }
+            if (!ok) {  // whatever was issued must finish before tensor memory is freed
+                int never = 0;
+                mma_commit(&sm.drain);
+                mbar_wait(&sm.drain, 0, &never, nullptr, 0);
+            }
+        }
+      }
+    } else {
+        // ------------------------------------------------------------------------------------- softmax and flush
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(COMPUTE_REGISTERS));
+        const int g = warp / 4, row = threadIdx.x % 128;
+        const int q_tile = 2 * blockIdx.x + g, q_row = q_tile * QUERY_TILE + row;
+        const uint32_t lane_base = uint32_t((warp % 4) * 32) << 16;
+        const uint32_t t_scores = tmem + lane_base + g * 256, t_acc = tmem + lane_base + g * 256 + 128;
+        const float sq = q_scale[size_t(head) * q_tiles + q_tile];
+        const float* sk = k_scale + size_t(head) * k_tiles;
+        float m = -INFINITY, den = 0.0f;
+        float o[HEAD_DIM];
+#pragma unroll
+        for (int i = 0; i < HEAD_DIM; ++i) o[i] = 0.0f;
+        bool ok = true;
+
+        // Tile t: scores -> P^ in shared memory; returns alpha and beta of the tile for its flush.
+        auto softmax = [&](int t, float& alpha, float& beta) -> bool {
+            const int buf = t & 1, stage = t % STAGES;
+            const int valid = min(KEY_TILE, n_keys - t * KEY_TILE);
+            const float c = (sq * sk[t]) * scale_log2;
+            if (!mbar_wait(&sm.s_full[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+            if (V_TOKEN && !mbar_wait(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+            tc_fence_after();
+            uint32_t raw[2][32];
+            tmem_ld32(t_scores + buf * 64, raw[0]);
+            tmem_ld32(t_scores + buf * 64 + 32, raw[1]);
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sm.s_free[g][buf]);
+
+            float x[KEY_TILE];
+            float tile_max;
+            if (!V_TOKEN) {
+                int imax = INT_MIN;
+#pragma unroll
+                for (int j = 0; j < KEY_TILE; ++j) {
+                    int s = int(raw[j / 32][j % 32]);
+                    if (j >= valid) s = INT_MIN;
+                    imax = max(imax, s);
+                    x[j] = __int2float_rn(s);
+                }
+                tile_max = __int2float_rn(imax) * c;
+            } else {
+                const float* log_s = sm.tok[stage];
+                tile_max = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < KEY_TILE; ++j) {
+                    x[j] = j < valid ? fmaf(__int2float_rn(int(raw[j / 32][j % 32])), c, log_s[j]) : -INFINITY;
+                    tile_max = fmaxf(tile_max, x[j]);
+                }
+            }
+            const float m_new = fmaxf(m, tile_max);
+            alpha = ex2(m - m_new);
+            beta = ex2(tile_max - m_new);
+            m = m_new;
+            const float offset = LOG2_255 - tile_max;
+            uint8_t* p_row = sm.p[g][buf] + row * 16;
+            unsigned isum = 0;
+            float fsum = 0.0f;
+#pragma unroll
+            for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        const int j = chunk * 16 + i * 4 + b;
+                        float p = V_TOKEN ? ex2(x[j] + offset) : ex2(fmaf(x[j], c, offset));
+                        if (j >= valid) p = 0.0f;
+                        if (V_TOKEN) fsum = fmaf(p, sm.tok[stage][KEY_TILE + j], fsum);
+                        word |= min(__float2uint_rn(p), 255u) << (8 * b);
+                    }
+                    isum = __dp4a(word, 0x01010101u, isum);
+                    w[i] = word;
+                }
+                *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            fence_proxy_async();
+            mbar_arrive(&sm.p_ready[g][buf]);
+            den = den * alpha + (V_TOKEN ? fsum : __uint2float_rn(isum)) * beta;
+            return true;
+        };
+
+        float alpha = 1.0f, beta = 1.0f;
+        ok = softmax(0, alpha, beta);
+        for (int t = 0; ok && t < k_tiles; ++t) {
+            float alpha_next = 1.0f, beta_next = 1.0f;
+            if (t + 1 < k_tiles) ok = softmax(t + 1, alpha_next, beta_next);
+            if (!ok) break;
+            // flush of tile t: out = out * alpha + beta * float(acc)
+            ok = mbar_wait(&sm.acc_full[g], t & 1, abort_flag, status, STATUS_WAIT_PV);
+            if (!ok) break;
+            tc_fence_after();
+            if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+#pragma unroll
+                for (int i = 0; i < HEAD_DIM; ++i) o[i] *= alpha;
+            }
+#pragma unroll
+            for (int chunk = 0; chunk < HEAD_DIM / 32; ++chunk) {
+                uint32_t a[32];
+                tmem_ld32(t_acc + chunk * 32, a);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[chunk * 32 + i] = fmaf(beta, __int2float_rn(int(a[i])), o[chunk * 32 + i]);
+            }
+            tc_fence_before();
+            mbar_arrive(&sm.acc_free[g]);
+            alpha = alpha_next;
+            beta = beta_next;
+        }
+
+        if (ok && q_row < n_queries) {
+            const float inv = 1.0f / den;
+            __nv_bfloat16* dst = out + out_layout.offset(head, q_row);
+#pragma unroll
+            for (int chunk = 0; chunk < HEAD_DIM / 8; ++chunk) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c0 = chunk * 8 + 2 * i;
+                    const float a = o[c0] * v_scale[head * HEAD_DIM + c0] * inv;
+                    const float b = o[c0 + 1] * v_scale[head * HEAD_DIM + c0 + 1] * inv;
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(a, b);
+                    w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                }
+                *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        tmem_dealloc(tmem, TMEM_COLUMNS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Self-test: one tcgen05.mma chain on operand images given by the caller, accumulator copied out as it lies in tensor memory.
+
+__global__ void __launch_bounds__(128) selftest_mma_i8_kernel(const uint8_t* __restrict__ a_image, const uint8_t* __restrict__ b_image,
+                                                              int n, int k, int a_unsigned, int variant, int32_t* __restrict__ d,
+                                                              int* status) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t* a_s = smem_raw;             // [k / 16][128][16]
+    uint8_t* b_s = smem_raw + 128 * k;   // [k / 16][n][16]
+    __shared__ uint64_t done;
+    __shared__ uint32_t tmem_base;
+    __shared__ int abort_flag;
+    for (int i = threadIdx.x; i < 128 * k / 16; i += 128) reinterpret_cast<uint4*>(a_s)[i] = reinterpret_cast<const uint4*>(a_image)[i];
+    for (int i = threadIdx.x; i < n * k / 16; i += 128) reinterpret_cast<uint4*>(b_s)[i] = reinterpret_cast<const uint4*>(b_image)[i];
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_proxy_async();
+    if (threadIdx.x / 32 == 0) tmem_alloc(&tmem_base, 128);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_base;
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = idesc_i8(!a_unsigned, 128, n);
+        for (int ks = 0; ks < k / 32; ++ks) {
+            uint64_t da, db;
+            if (variant == 0) {
+                da = smem_desc(smem_u32(a_s) + ks * 2 * 128 * 16, 128 * 16, 128);
+                db = smem_desc(smem_u32(b_s) + ks * 2 * n * 16, n * 16, 128);
+            } else {  // diagnostic: the two offsets exchanged
+                da = smem_desc(smem_u32(a_s) + ks * 2 * 128 * 16, 128, 128 * 16);
+                db = smem_desc(smem_u32(b_s) + ks * 2 * n * 16, 128, n * 16);
+            }
+            mma_i8_ss(tmem, da, db, idesc, ks > 0);
+        }
+        mma_commit(&done);
+    }
+    const bool ok = mbar_wait(&done, 0, &abort_flag, status, STATUS_WAIT_SCORES);
+    tc_fence_after();
+    if (ok) {
+        const uint32_t lane_base = uint32_t((threadIdx.x / 32) * 32) << 16;
+        for (int c0 = 0; c0 < n; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem + lane_base + c0, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) d[threadIdx.x * n + c0 + i] = int32_t(r[i]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x / 32 == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 128);
+    }
+}
+
+}  // namespace unica
+
+using namespace unica;
+
+extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
+                                         const int8_t* v8, const float* v_scale, const float* v_token, int v_mode, void* out,
+                                         unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
+                                         int* status, void* stream) {
+    if (!q8 || !q_scale || !k8 || !k_scale || !v8 || !v_scale || !out) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: null pointer");
+    if (heads <= 0 || heads > 65535 || n_queries <= 0 || n_keys <= 0)
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: heads must be in 1..65535, n_queries and n_keys positive");
+    if (v_mode != UNICA_B200_V_CHANNEL && v_mode != UNICA_B200_V_TOKEN) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: unknown v_mode");
+    if (v_mode == UNICA_B200_V_TOKEN && !v_token) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: per-token mode needs v_token");
+    if (int e = unica_check_device()) return e;
+    const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE), heads);
+    const size_t smem = sizeof(AttSmem) + 128;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    auto launch = [&](auto kernel) -> int {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+            return unica_check_launch("attention_int8 (shared memory size)");
+        kernel<<<grid, ATT_THREADS, smem, s>>>(q8, q_scale, k8, k_scale, v8, v_scale, v_token, static_cast<__nv_bfloat16*>(out),
+                                               to_layout(out_layout), n_queries, n_keys, scale_log2, status);
+        return unica_check_launch("attention_int8");
+    };
+    return v_mode == UNICA_B200_V_TOKEN ? launch(attention_int8_kernel<true>) : launch(attention_int8_kernel<false>);
+}
+
+extern "C" int unica_b200_selftest_mma_i8(const void* a_image, const void* b_image, int n, int k, int a_unsigned, int variant,
+                                          int32_t* d, void* stream) {
+    if (!a_image || !b_image || !d) return unica_fail(UNICA_B200_ERR_ARGUMENT, "selftest_mma_i8: null pointer");
+    if (n < 32 || n > 128 || n % 32 || k < 32 || k > 128 || k % 32)
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "selftest_mma_i8: n and k must be multiples of 32 in 32..128");
+    if (int e = unica_check_device()) return e;
+    const size_t smem = size_t(128 + n) * k + 128;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int* status = nullptr;
+    if (cudaMalloc(&status, sizeof(int)) != cudaSuccess || cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess)
+        return unica_check_launch("selftest_mma_i8 (status word)");
+    selftest_mma_i8_kernel<<<1, 128, smem, s>>>(static_cast<const uint8_t*>(a_image), static_cast<const uint8_t*>(b_image), n, k,
+                                                a_unsigned, variant, d, status);
+    int host_status = 0;
+    cudaError_t e = cudaMemcpyAsync(&host_status, status, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    cudaFree(status);
+    if (e != cudaSuccess) {
+        unica_fail(UNICA_B200_ERR_CUDA, cudaGetErrorString(e));
+        return UNICA_B200_ERR_CUDA;
+    }
+    if (host_status) return unica_fail(UNICA_B200_ERR_KERNEL, "selftest_mma_i8: the tensor-core instruction never completed");
+    return UNICA_B200_OK;
+}

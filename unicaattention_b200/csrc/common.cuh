@@ -1,0 +1,182 @@
+// Shared device-side helpers for the sm_100a kernels: the caller's tensor layout, bounded mbarrier waits, bulk (TMA)
+// copies, tensor-memory allocation and the tcgen05 instructions the attention kernels issue.
+//
+// Every wait here is bounded: a wait that does not complete within WAIT_LIMIT_CYCLES records a status code and
+// returns false, and the kernels then leave their loops, drain what they started and free their tensor memory.  A
+// kernel therefore always terminates, whatever went wrong with its pipeline.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace unica {
+
+constexpr int HEAD_DIM = 128;
+constexpr int KEY_TILE = 64;     // keys per tile: the K scale block and the softmax tile of the numerics contract
+constexpr int QUERY_TILE = 128;  // query rows per tile: the Q scale block, and M of one tcgen05.mma
+constexpr float LOG2_255 = 7.99435343685886f;
+
+// Where token `token` of head `head_index` (= batch * heads + head) starts in a [batch, heads, tokens, 128] tensor with
+// a contiguous last dimension and any other strides; strides in elements.  Field for field the reference's struct
+// (csrc/flash.cu:231-237), so a caller fills it the same way.
+struct TokenLayout {
+    long long batch, head, token;
+    int heads;
+    __host__ __device__ __forceinline__ size_t offset(int head_index, int token_index) const {
+        return size_t(head_index / heads) * batch + size_t(head_index % heads) * head + size_t(token_index) * token;
+    }
+};
+
+// status codes a kernel leaves in its status word (0: fine)
+enum Status : int {
+    STATUS_OK = 0,
+    STATUS_WAIT_TILE = 1,     // a K/V/Q tile never arrived
+    STATUS_WAIT_SCORES = 2,   // S = Q.K^T never completed
+    STATUS_WAIT_P = 3,        // the softmax threads never delivered P
+    STATUS_WAIT_PV = 4,       // P.V never completed
+    STATUS_WAIT_FREE = 5,     // a buffer was never released
+    STATUS_WAIT_STAGE = 6,    // the producer never got a stage back
+};
+
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// mbarrier
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
+    uint32_t done;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for the phase of parity `parity`.  abort_flag: a word in shared memory any thread of the block sets when it
+// gave up; everyone else then stops waiting at once.  Returns false when the wait was abandoned.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try(bar, parity)) return true;
+    const long long start = clock64();
+    while (true) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// bulk copies (the untiled TMA path): global -> shared, completion counted in bytes on an mbarrier.
+// dst, src 16-byte aligned, bytes a multiple of 16.
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, int bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// generic-proxy writes to shared memory made visible to the async proxy (tcgen05.mma operand reads)
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// tensor memory
+
+// One warp allocates `columns` (a power of two >= 32) and leaves the base address in *dst (shared memory).
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst, int columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, int columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 32 consecutive 32-bit columns of this thread's lane (lane = 32 * (warp % 4) + lane id): r[i] = column i.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// tcgen05.mma operands
+
+// Shared-memory matrix descriptor, no swizzle, K-major.  The operand is stored as core matrices of 8 rows x 16 bytes,
+// each 128 contiguous bytes; `k_step_bytes` separates the two core matrices one instruction reads along K (the
+// "leading" offset), `row_group_bytes` separates groups of 8 rows (the "stride" offset).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t smem_addr, uint32_t k_step_bytes, uint32_t row_group_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_addr >> 4) & 0x3fff);
+    d |= uint64_t((k_step_bytes >> 4) & 0x3fff) << 16;
+    d |= uint64_t((row_group_bytes >> 4) & 0x3fff) << 32;
+    d |= uint64_t(1) << 46;  // descriptor version of this architecture
+    return d;                // base offset 0, layout type 0: no swizzle
+}
+
+// Instruction descriptor of kind::i8: D s32; A u8 or s8; B s8; both K-major; M x N.
+__host__ __device__ constexpr uint32_t idesc_i8(bool a_signed, int m, int n) {
+    return (2u << 4) | (uint32_t(a_signed) << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] . B[smem]^T, issued by one thread.
+__device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate))
+        : "memory");
+}
+
+// The mbarrier gets one arrival once every tcgen05.mma this thread issued before has completed.
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+}  // namespace unica

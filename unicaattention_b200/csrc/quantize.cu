@@ -1,0 +1,286 @@
+// Statistics and INT8 quantization passes of the accurate mode: HBM-bound kernels that read bf16 Q, K, V once in the
+// caller's layout and write the 8-bit operands already arranged as the shared-memory images tcgen05.mma reads (no
+// swizzle, K-major core matrices of 8 rows x 16 bytes), so that the attention kernel fetches each tile with one
+// contiguous bulk copy.
+//
+// Numerics follow the reference bit for bit (bench/emulate.py quant(), csrc/flash.cu:334-372 and 590-630):
+// amax over the scale block, scale = max(amax * (1/127), 1e-12), code = clamp(rint(x / scale), -127, 127) with an IEEE
+// division and round-half-even.
+#include "common.cuh"
+
+namespace unica {
+
+constexpr int THREADS = 256;
+constexpr int STATS_TOKENS = 256;  // tokens per partial sum; the summation order below is part of the contract
+constexpr int STATS_LANES = 16;
+
+__device__ __forceinline__ void load8(float (&v)[8], const __nv_bfloat16* src) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(pairs[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+// Sum, min and max per channel over a block of 256 tokens of one head (the reference's rope_stats, csrc/flash.cu:287-327,
+// without RoPE): thread = (lane of 16 tokens, chunk of 8 channels); lane l adds tokens l, l + 16, ... in order, then
+// the 16 lanes are added in order.  partial: [heads][blocks][3][128].  Grid (blocks, heads).
+__global__ void __launch_bounds__(THREADS) channel_stats_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
+                                                                 int n_tokens, float* __restrict__ partial) {
+    const int chunk = threadIdx.x % 16, lane = threadIdx.x / 16;
+    const int head = blockIdx.y, token0 = blockIdx.x * STATS_TOKENS;
+    float sum[8], low[8], high[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum[i] = 0.0f, low[i] = INFINITY, high[i] = -INFINITY;
+    const int end = min(token0 + STATS_TOKENS, n_tokens);
+#pragma unroll 4
+    for (int token = token0 + lane; token < end; token += STATS_LANES) {
+        float v[8];
+        load8(v, x + in.offset(head, token) + chunk * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            sum[i] += v[i];
+            low[i] = fminf(low[i], v[i]);
+            high[i] = fmaxf(high[i], v[i]);
+        }
+    }
+    __shared__ float stats[3][STATS_LANES][HEAD_DIM];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        stats[0][lane][chunk * 8 + i] = sum[i];
+        stats[1][lane][chunk * 8 + i] = low[i];
+        stats[2][lane][chunk * 8 + i] = high[i];
+    }
+    __syncthreads();
+    if (threadIdx.x < HEAD_DIM) {
+        float s = 0.0f, lo = INFINITY, hi = -INFINITY;
+        for (int l = 0; l < STATS_LANES; ++l) {
+            s += stats[0][l][threadIdx.x];
+            lo = fminf(lo, stats[1][l][threadIdx.x]);
+            hi = fmaxf(hi, stats[2][l][threadIdx.x]);
+        }
+        float* out = partial + (size_t(head) * gridDim.x + blockIdx.x) * 3 * HEAD_DIM + threadIdx.x;
+        out[0] = s;
+        out[HEAD_DIM] = lo;
+        out[2 * HEAD_DIM] = hi;
+    }
+}
+
+// The partials of each group of `blocks_per_group` blocks added in order (the reference leaves this to torch, whose
+// order is unspecified: unica/__init__.py:603-612): mean = sum / true token count, min, max.  Grid (groups, heads), 128 threads.
+__global__ void __launch_bounds__(HEAD_DIM) channel_stats_finish_kernel(const float* __restrict__ partial, int blocks,
+                                                                        int blocks_per_group, int n_tokens,
+                                                                        float* __restrict__ mean, float* __restrict__ low,
+                                                                        float* __restrict__ high) {
+    const int head = blockIdx.y, group = blockIdx.x, c = threadIdx.x;
+    const int b0 = group * blocks_per_group, b1 = min(b0 + blocks_per_group, blocks);
+    float s = 0.0f, lo = INFINITY, hi = -INFINITY;
+    for (int b = b0; b < b1; ++b) {
+        const float* p = partial + (size_t(head) * blocks + b) * 3 * HEAD_DIM + c;
+        s += p[0];
+        lo = fminf(lo, p[HEAD_DIM]);
+        hi = fmaxf(hi, p[2 * HEAD_DIM]);
+    }
+    const int count = min(b1 * STATS_TOKENS, n_tokens) - b0 * STATS_TOKENS;
+    const size_t o = (size_t(head) * gridDim.x + group) * HEAD_DIM + c;
+    mean[o] = s / float(count);
+    low[o] = lo;
+    high[o] = hi;
+}
+
+__device__ __forceinline__ float block_max(float x, float* scratch) {
+#pragma unroll
+    for (int d = 16; d > 0; d /= 2) x = fmaxf(x, __shfl_xor_sync(0xffffffff, x, d));
+    if (threadIdx.x % 32 == 0) scratch[threadIdx.x / 32] = x;
+    __syncthreads();
+    x = scratch[0];
+#pragma unroll
+    for (int w = 1; w < THREADS / 32; ++w) x = fmaxf(x, scratch[w]);
+    return x;
+}
+
+__device__ __forceinline__ uint32_t pack4(const float* v, float scale) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int code = __float2int_rn(fminf(fmaxf(rintf(__fdiv_rn(v[i], scale)), -127.0f), 127.0f));
+        word |= uint32_t(code & 0xff) << (8 * i);
+    }
+    return word;
+}
+
+// Q or K (minus `mean`, [heads][128] or null) in INT8 with one scale per tile of ROWS tokens (128: Q, 64: K).
+// One block per tile; the tile stays in registers between the max and the write, so HBM is read once.
+// codes: [heads][tiles][8 chunks of 16 channels][ROWS][16] bytes; rows past n_tokens and tiles past the last are zeros.
+// scales: [heads][tiles].  Grid (tiles, heads).
+template <int ROWS>
+__global__ void __launch_bounds__(THREADS) quantize_rows_int8_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
+                                                                      const float* __restrict__ mean, int n_tokens,
+                                                                      int8_t* __restrict__ codes, float* __restrict__ scales) {
+    constexpr int ITEMS = ROWS * 8 / THREADS;  // (row, 16-channel chunk) items per thread
+    __shared__ float scratch[THREADS / 32];
+    const int head = blockIdx.y, tile = blockIdx.x, token0 = tile * ROWS;
+    float v[ITEMS][16];
+    float local = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int item = it * THREADS + threadIdx.x, row = item % ROWS, chunk = item / ROWS;
+        if (token0 + row < n_tokens) {
+            const __nv_bfloat16* src = x + in.offset(head, token0 + row) + chunk * 16;
+            float a[8], b[8];
+            load8(a, src);
+            load8(b, src + 8);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float m0 = mean ? mean[head * HEAD_DIM + chunk * 16 + i] : 0.0f;
+                const float m1 = mean ? mean[head * HEAD_DIM + chunk * 16 + 8 + i] : 0.0f;
+                v[it][i] = a[i] - m0;
+                v[it][8 + i] = b[i] - m1;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[it][i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) local = fmaxf(local, fabsf(v[it][i]));
+    }
+    const float scale = fmaxf(block_max(local, scratch) * (1.0f / 127.0f), 1e-12f);
+    if (threadIdx.x == 0) scales[size_t(head) * gridDim.x + tile] = scale;
+    int8_t* out = codes + (size_t(head) * gridDim.x + tile) * (ROWS * HEAD_DIM);
+#pragma unroll
+    for (int it = 0; it < ITEMS; ++it) {
+        const int item = it * THREADS + threadIdx.x, row = item % ROWS, chunk = item / ROWS;
+        uint4 w;
+        w.x = pack4(&v[it][0], scale);
+        w.y = pack4(&v[it][4], scale);
+        w.z = pack4(&v[it][8], scale);
+        w.w = pack4(&v[it][12], scale);
+        *reinterpret_cast<uint4*>(out + (chunk * ROWS + row) * 16) = w;
+    }
+}
+
+// V in INT8, one block per tile of 64 keys.  PER_TOKEN false: one scale per channel, max(|low|, |high|) * (1/127) from
+// the channel's min and max over the head (low, high: [heads][128]); true: one scale per key over its channels, and
+// v_token [heads][tiles][2][64] gets log2 s and 1 / s of the tile's keys (zeros past n_tokens).  skip: [heads][n_tokens],
+// 1 = the key is written as zeros (outlier keys), or null.
+// v8: [heads][tiles][4 chunks of 16 keys][128 channels][16] bytes: the K-major B operand of P.V.  v_scale [heads][128].
+template <bool PER_TOKEN>
+__global__ void __launch_bounds__(THREADS) quantize_v_int8_kernel(const __nv_bfloat16* __restrict__ v, TokenLayout in,
+                                                                   const float* __restrict__ low, const float* __restrict__ high,
+                                                                   const uint8_t* __restrict__ skip, int n_tokens,
+                                                                   int8_t* __restrict__ v8, float* __restrict__ v_scale,
+                                                                   float* __restrict__ v_token) {
+    __shared__ __align__(16) int8_t tile_out[KEY_TILE * HEAD_DIM];
+    const int head = blockIdx.y, tile = blockIdx.x, token0 = tile * KEY_TILE;
+    const int chunk = threadIdx.x % 16;  // 8 channels
+    float scale[8];
+    if (!PER_TOKEN) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = head * HEAD_DIM + chunk * 8 + i;
+            scale[i] = fmaxf(fmaxf(high[c], -low[c]) * (1.0f / 127.0f), 1e-12f);
+        }
+        if (tile == 0 && threadIdx.x < 16) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v_scale[head * HEAD_DIM + chunk * 8 + i] = scale[i];
+        }
+    } else if (tile == 0 && threadIdx.x < 16) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v_scale[head * HEAD_DIM + chunk * 8 + i] = 1.0f;
+    }
+#pragma unroll
+    for (int it = 0; it < KEY_TILE * 16 / THREADS; ++it) {
+        const int key = it * (THREADS / 16) + threadIdx.x / 16;
+        const bool valid = token0 + key < n_tokens;
+        float x[8];
+        if (valid && !(skip && skip[size_t(head) * n_tokens + token0 + key])) {
+            load8(x, v + in.offset(head, token0 + key) + chunk * 8);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[i] = 0.0f;
+        }
+        if (PER_TOKEN) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+#pragma unroll
+            for (int d = 8; d > 0; d /= 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, d));
+            const float s = fmaxf(amax * (1.0f / 127.0f), 1e-12f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) scale[i] = s;
+            if (chunk == 0) {
+                float* tok = v_token + (size_t(head) * gridDim.x + tile) * 2 * KEY_TILE;
+                tok[key] = valid ? log2f(s) : 0.0f;
+                tok[KEY_TILE + key] = valid ? __fdiv_rn(1.0f, s) : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int code = __float2int_rn(fminf(fmaxf(rintf(__fdiv_rn(x[i], scale[i])), -127.0f), 127.0f));
+            tile_out[((key / 16) * HEAD_DIM + chunk * 8 + i) * 16 + key % 16] = int8_t(code);
+        }
+    }
+    __syncthreads();
+    uint4* dst = reinterpret_cast<uint4*>(v8 + (size_t(head) * gridDim.x + tile) * (KEY_TILE * HEAD_DIM));
+    const uint4* src = reinterpret_cast<const uint4*>(tile_out);
+#pragma unroll
+    for (int i = threadIdx.x; i < KEY_TILE * HEAD_DIM / 16; i += THREADS) dst[i] = src[i];
+}
+
+}  // namespace unica
+
+// ---------------------------------------------------------------------------------------------------------------------
+// C entry points (declared in include/unica_b200.h)
+
+#include "capi.h"
+
+using namespace unica;
+
+extern "C" int unica_b200_channel_stats(const void* x, unica_token_layout layout, int heads, int n_tokens, int per,
+                                        float* partial, float* mean, float* low, float* high, void* stream) {
+    if (!x || !partial || !mean || !low || !high) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats: heads and n_tokens must be positive");
+    if (per != 0 && (per < 0 || per % STATS_TOKENS)) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats: per must be 0 or a multiple of 256");
+    const int blocks = (n_tokens + STATS_TOKENS - 1) / STATS_TOKENS;
+    const int per_group = per ? per / STATS_TOKENS : blocks;
+    const int groups = (blocks + per_group - 1) / per_group;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    channel_stats_kernel<<<dim3(blocks, heads), THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(x), to_layout(layout), n_tokens, partial);
+    channel_stats_finish_kernel<<<dim3(groups, heads), HEAD_DIM, 0, s>>>(partial, blocks, per_group, n_tokens, mean, low, high);
+    return unica_check_launch("channel_stats");
+}
+
+extern "C" int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const float* mean, int heads, int n_tokens,
+                                        int block_tokens, int tiles, int8_t* codes, float* scales, void* stream) {
+    if (!x || !codes || !scales) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: heads and n_tokens must be positive");
+    if (block_tokens != 128 && block_tokens != 64) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: block_tokens must be 128 (Q) or 64 (K)");
+    if (tiles < (n_tokens + block_tokens - 1) / block_tokens) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: tiles does not cover n_tokens");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    if (block_tokens == 128)
+        quantize_rows_int8_kernel<128><<<dim3(tiles, heads), THREADS, 0, s>>>(xb, to_layout(layout), mean, n_tokens, codes, scales);
+    else
+        quantize_rows_int8_kernel<64><<<dim3(tiles, heads), THREADS, 0, s>>>(xb, to_layout(layout), mean, n_tokens, codes, scales);
+    return unica_check_launch("quantize_int8");
+}
+
+extern "C" int unica_b200_quantize_v_int8(const void* v, unica_token_layout layout, const float* low, const float* high,
+                                          const uint8_t* skip, int per_token, int heads, int n_tokens, int8_t* v8,
+                                          float* v_scale, float* v_token, void* stream) {
+    if (!v || !v8 || !v_scale) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_v_int8: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_v_int8: heads and n_tokens must be positive");
+    if (per_token ? !v_token : (!low || !high))
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_v_int8: per token needs v_token, per channel needs low and high");
+    const int tiles = (n_tokens + KEY_TILE - 1) / KEY_TILE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* vb = static_cast<const __nv_bfloat16*>(v);
+    if (per_token)
+        quantize_v_int8_kernel<true><<<dim3(tiles, heads), THREADS, 0, s>>>(vb, to_layout(layout), low, high, skip, n_tokens, v8, v_scale, v_token);
+    else
+        quantize_v_int8_kernel<false><<<dim3(tiles, heads), THREADS, 0, s>>>(vb, to_layout(layout), low, high, skip, n_tokens, v8, v_scale, v_token);
+    return unica_check_launch("quantize_v_int8");
+}
