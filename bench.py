@@ -176,9 +176,14 @@ def main():
     ap.add_argument("--cpu-rows", type=int, default=2048, help="query rows of the CPU baseline's sample")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg")
+    ap.add_argument("--heads", type=int, default=0, help="override the workload's head count (profiling on a small case)")
+    ap.add_argument("--tokens", type=int, default=0, help="override the workload's token count (profiling on a small case)")
+    ap.add_argument("--profile", action="store_true",
+                    help="for captures under a profiler: one warm-up call and --steps calls, nothing else, no JSON line")
     args = ap.parse_args()
-    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.profile else args.warmup
     batch, heads, tokens = WORKLOADS[args.workload]
+    heads, tokens = args.heads or heads, args.tokens or tokens
     if args.impl == "reference":
         return run_reference_arm(args, batch, heads, tokens)
 
@@ -230,6 +235,11 @@ def main():
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item() / steps
 
+    if args.profile:
+        for _ in range(1 + args.steps):
+            step(q, k, v)
+        unica.check_status(device)
+        return
     for _ in range(args.warmup):
         step(q, k, v)
     unica.check_status(device)

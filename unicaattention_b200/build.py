@@ -31,17 +31,24 @@ def stale() -> bool:
     return any(p.stat().st_mtime > built for p in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every .cu of csrc/ into objects (in build/) and link the shared library.  Returns its path."""
+def build(force: bool = False, verbose: bool = False, defines: tuple[str, ...] = (), output: Path | None = None) -> Path:
+    """Compile every .cu of csrc/ into objects (in build/) and link the shared library.  Returns its path.
+    defines: extra -D flags (e.g. ("UNICA_TRACE",)) for a diagnostic build written to `output` instead of LIB."""
+    if defines or output:
+        return _build(HERE / "build" / ("-".join(defines) or "alt"), output or HERE / ("libunica_b200-" + "-".join(defines) + ".so"),
+                      [f"-D{d}" for d in defines], verbose)
     if not force and not stale():
         return LIB
-    objdir = HERE / "build"
-    objdir.mkdir(exist_ok=True)
+    return _build(HERE / "build", LIB, [], verbose)
+
+
+def _build(objdir: Path, lib: Path, extra: list[str], verbose: bool) -> Path:
+    objdir.mkdir(parents=True, exist_ok=True)
     objects = []
     procs = []
     for src in sources():
         obj = objdir / (src.stem + ".o")
-        cmd = ["nvcc", *ARCH_FLAGS, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", str(src), "-o", str(obj)]
+        cmd = ["nvcc", *ARCH_FLAGS, *NVCC_FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-c", str(src), "-o", str(obj)]
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objects.append(str(obj))
     for src, proc in procs:
@@ -50,8 +57,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(out)
         if proc.returncode:
             raise RuntimeError(f"nvcc failed on {src.name}")
-    subprocess.run(["nvcc", *ARCH_FLAGS, "-shared", "-cudart", "static", "-o", str(LIB), *objects], check=True)
-    return LIB
+    subprocess.run(["nvcc", *ARCH_FLAGS, "-shared", "-cudart", "static", "-o", str(lib), *objects], check=True)
+    return lib
 
 
 if __name__ == "__main__":

@@ -56,6 +56,16 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, int bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Non-blocking: has the phase of parity `parity` completed?
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, int parity) {
+    uint32_t done;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
 __device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
     uint32_t done;
     asm volatile(
@@ -80,6 +90,13 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile in
             return false;
         }
     }
+}
+
+// The same for a whole warp: every lane waits, and all get the same answer.  The vote also reconverges the warp, which
+// the .sync.aligned tensor-memory instructions that usually follow require: a tcgen05.ld executed by part of a warp
+// never completes.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, int parity, volatile int* abort_flag, int* status, int code) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -123,6 +140,83 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
+        : "memory");
+}
+
+// 64 consecutive columns as 32 float2 (bit patterns untouched), load and wait in ONE statement so that no use of the
+// registers can be scheduled before the wait.
+__device__ __forceinline__ void tmem_ld64_sync(uint32_t taddr, float2 (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+        "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+        "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=f"(v[0].x), "=f"(v[0].y), "=f"(v[1].x), "=f"(v[1].y), "=f"(v[2].x), "=f"(v[2].y), "=f"(v[3].x), "=f"(v[3].y),
+          "=f"(v[4].x), "=f"(v[4].y), "=f"(v[5].x), "=f"(v[5].y), "=f"(v[6].x), "=f"(v[6].y), "=f"(v[7].x), "=f"(v[7].y),
+          "=f"(v[8].x), "=f"(v[8].y), "=f"(v[9].x), "=f"(v[9].y), "=f"(v[10].x), "=f"(v[10].y), "=f"(v[11].x), "=f"(v[11].y),
+          "=f"(v[12].x), "=f"(v[12].y), "=f"(v[13].x), "=f"(v[13].y), "=f"(v[14].x), "=f"(v[14].y), "=f"(v[15].x), "=f"(v[15].y),
+          "=f"(v[16].x), "=f"(v[16].y), "=f"(v[17].x), "=f"(v[17].y), "=f"(v[18].x), "=f"(v[18].y), "=f"(v[19].x), "=f"(v[19].y),
+          "=f"(v[20].x), "=f"(v[20].y), "=f"(v[21].x), "=f"(v[21].y), "=f"(v[22].x), "=f"(v[22].y), "=f"(v[23].x), "=f"(v[23].y),
+          "=f"(v[24].x), "=f"(v[24].y), "=f"(v[25].x), "=f"(v[25].y), "=f"(v[26].x), "=f"(v[26].y), "=f"(v[27].x), "=f"(v[27].y),
+          "=f"(v[28].x), "=f"(v[28].y), "=f"(v[29].x), "=f"(v[29].y), "=f"(v[30].x), "=f"(v[30].y), "=f"(v[31].x), "=f"(v[31].y)
+        : "r"(taddr)
+        : "memory");
+}
+
+// 32 consecutive columns as 16 float2, issued without waiting; tmem_wait_ld() then reg_fence16() before the first use.
+__device__ __forceinline__ void tmem_ld32_async(uint32_t taddr, float2 (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=f"(v[0].x), "=f"(v[0].y), "=f"(v[1].x), "=f"(v[1].y), "=f"(v[2].x), "=f"(v[2].y), "=f"(v[3].x), "=f"(v[3].y),
+          "=f"(v[4].x), "=f"(v[4].y), "=f"(v[5].x), "=f"(v[5].y), "=f"(v[6].x), "=f"(v[6].y), "=f"(v[7].x), "=f"(v[7].y),
+          "=f"(v[8].x), "=f"(v[8].y), "=f"(v[9].x), "=f"(v[9].y), "=f"(v[10].x), "=f"(v[10].y), "=f"(v[11].x), "=f"(v[11].y),
+          "=f"(v[12].x), "=f"(v[12].y), "=f"(v[13].x), "=f"(v[13].y), "=f"(v[14].x), "=f"(v[14].y), "=f"(v[15].x), "=f"(v[15].y)
+        : "r"(taddr)
+        : "memory");
+}
+
+// Emits nothing; ties the 32 registers to this point of the (volatile-ordered) instruction stream, so that uses of
+// an asynchronous tensor-memory load cannot move above the tcgen05.wait::ld that precedes this call.
+__device__ __forceinline__ void reg_fence16(float2 (&v)[16]) {
+    asm volatile(""
+                 : "+f"(v[0].x), "+f"(v[0].y), "+f"(v[1].x), "+f"(v[1].y), "+f"(v[2].x), "+f"(v[2].y), "+f"(v[3].x), "+f"(v[3].y),
+                   "+f"(v[4].x), "+f"(v[4].y), "+f"(v[5].x), "+f"(v[5].y), "+f"(v[6].x), "+f"(v[6].y), "+f"(v[7].x), "+f"(v[7].y),
+                   "+f"(v[8].x), "+f"(v[8].y), "+f"(v[9].x), "+f"(v[9].y), "+f"(v[10].x), "+f"(v[10].y), "+f"(v[11].x), "+f"(v[11].y),
+                   "+f"(v[12].x), "+f"(v[12].y), "+f"(v[13].x), "+f"(v[13].y), "+f"(v[14].x), "+f"(v[14].y), "+f"(v[15].x), "+f"(v[15].y)
+                 :
+                 : "memory");
+}
+
+// 16 consecutive columns as 8 float2, load and wait in one statement / store (tmem_wait_st() before they are read back).
+__device__ __forceinline__ void tmem_ld16_sync(uint32_t taddr, float2 (&v)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
+        : "=f"(v[0].x), "=f"(v[0].y), "=f"(v[1].x), "=f"(v[1].y), "=f"(v[2].x), "=f"(v[2].y), "=f"(v[3].x), "=f"(v[3].y),
+          "=f"(v[4].x), "=f"(v[4].y), "=f"(v[5].x), "=f"(v[5].y), "=f"(v[6].x), "=f"(v[6].y), "=f"(v[7].x), "=f"(v[7].y)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float2 (&v)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "f"(v[0].x), "f"(v[0].y), "f"(v[1].x), "f"(v[1].y), "f"(v[2].x), "f"(v[2].y), "f"(v[3].x), "f"(v[3].y), "f"(v[4].x),
+        "f"(v[4].y), "f"(v[5].x), "f"(v[5].y), "f"(v[6].x), "f"(v[6].y), "f"(v[7].x), "f"(v[7].y)
+        : "memory");
+}
+
+// 32 consecutive columns of this thread's lane set to one value.
+__device__ __forceinline__ void tmem_fill32(uint32_t taddr, uint32_t v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
+        "r"(v)
         : "memory");
 }
 
@@ -172,6 +266,44 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// arithmetic helpers
+
+// Packed FP32: one instruction for two lanes of a float2 (sm_100 has FFMA2 / FADD2 / FMUL2).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+          "l"(reinterpret_cast<unsigned long long&>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// An s32 accumulator that starts at MAGIC_BITS instead of 0 reads back as the float MAGIC + value, exactly, for
+// |value| < 2^22: the conversion to float costs one FADD instead of an I2F on the quarter-rate conversion pipe.
+// Adding MAGIC to a float in [0, 2^22) likewise leaves its round-half-even integer in the low mantissa bits.
+constexpr uint32_t MAGIC_BITS = 0x4B400000u;
+constexpr float MAGIC = 12582912.0f;  // 1.5 * 2^23
 
 __device__ __forceinline__ float ex2(float x) {
     float y;

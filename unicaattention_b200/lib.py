@@ -14,7 +14,10 @@ import functools
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-LIB_PATH = HERE / "libunica_b200.so"
+import os  # noqa: E402
+
+# UNICA_B200_LIB: another build of the same library (e.g. a -DUNICA_TRACE build from unicaattention_b200.build)
+LIB_PATH = Path(os.environ["UNICA_B200_LIB"]) if "UNICA_B200_LIB" in os.environ else HERE / "libunica_b200.so"
 
 ERR_ARGUMENT, ERR_CUDA, ERR_DEVICE, ERR_KERNEL = 1, 2, 3, 4
 V_CHANNEL, V_TOKEN = 0, 1
