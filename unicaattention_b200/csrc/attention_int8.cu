@@ -1,33 +1,32 @@
 // The accurate mode's flash-attention loop on tcgen05 (replaces the reference's attention_int8pv_tma, csrc/flash.cu:806-959).
 //
-// One block = 256 query rows of one head = two tiles of 128 rows that share every K and V tile.  Per query tile g:
-//   a softmax warpgroup  (warps 4g .. 4g+3):   thread = query row (tensor-memory lane), 64 scores of the tile -> P^ (u8)
-//   a flush warpgroup    (warps 8+4g .. 11+4g): thread = query row, keeps out (float) in TENSOR MEMORY and folds every
-//                                               tile's integer P^.V^ into it:  out = out * alpha + beta * float(acc)
-// plus warp 16, which streams K8 / V8 tiles (contiguous 8 KB images written by the quantizers) into a ring of
-// shared-memory stages with bulk TMA copies, and one thread of warp 17, which issues every tcgen05.mma as soon as its
-// operands and its accumulator are free:
-//   S[g]   = Q8[g] . K8(t)^T       kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32
-//   acc[g] = P^[g](t) . V8(t)[h]   kind::i8 u8 x s8 -> s32, 128 x 64 (channel half h), 2 instructions of K = 32
-// Keeping `out` out of the registers is what lets 16 computing warps live on one SM (4 per scheduler): the arithmetic
-// of this kernel is a chain of dependent FP32 operations per row, and only several warps per scheduler hide its latency.
+// One block = 256 query rows of one head = two tiles of 128 rows, each owned by one warpgroup of 4 warps in which a
+// thread owns one query row (tensor-memory lane = row, so row maxima and sums need no shuffles) and keeps that row's
+// 128 output channels in registers.  Both warpgroups share every K and V tile.  A third warpgroup holds warp 8, which
+// streams K8 / V8 tiles (contiguous 8 KB images written by the quantizers) into a ring of shared-memory stages with
+// bulk TMA copies, and warp 9, one thread of which polls what is ready and issues every tcgen05.mma:
 //
-// Tensor memory, per query tile (256 columns): S 64 | acc 64 (one channel half at a time) | out 128 (float).
+//   S[g]   = Q8[g] . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, double-buffered in tensor memory
+//   acc[g] = P^[g](t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, one accumulator per tile
 //
 // Numerics (bench/emulate.py:298-369 with the accurate contract): scores in the log2 domain, c = (q_scale * k_scale) *
 // log2(e) / sqrt(d); P^ = rint(255 * 2^(x - tile max)) as u8 against the tile's own maximum; the denominator sums the
-// rounded P^ (per channel) or p / s_j in float before rounding (per token); every tile is flushed with
-// alpha = 2^(m_old - m_new), beta = 2^(m_tile - m_new).  The 255 stays in numerator and denominator alike (as
-// csrc/flash.cu:409-414 does).  No int<->float conversion instruction runs in the loop (see MAGIC in common.cuh): they
-// share the quarter-rate pipe with ex2, which is the unit this kernel keeps busiest.
-// All waits are bounded (common.cuh).
+// rounded P^ (per channel) or p / s_j in float before rounding (per token); every tile is flushed as
+// out = out * alpha + beta * float(acc) with alpha = 2^(m_old - m_new), beta = 2^(m_tile - m_new).
+// The 255 stays in numerator and denominator alike (as csrc/flash.cu:409-414 does).
+//
+// What bounds it (measured on B200, see the micro-benchmarks quoted in DESIGN.md): ex2 issues once per 8 cycles per
+// scheduler, float->int conversions too, so the loop has no conversion instruction at all (MAGIC in common.cuh) and
+// the exponentials are the busiest unit; a tensor-memory load costs ~180 cycles of latency, so the flush prefetches.
+//
+// Tensor memory: 512 columns = per warpgroup S x 2 (64 each) + acc (128).  All waits are bounded (common.cuh).
 #include "capi.h"
 
 namespace unica {
 
-constexpr int ATT_THREADS = 640;  // 8 softmax warps, 8 flush warps, and a warpgroup holding the producer and MMA warps
-constexpr int SOFTMAX_REGISTERS = 112, FLUSH_REGISTERS = 112, SERVICE_REGISTERS = 32;
-constexpr int PRODUCER_WARP = 16, MMA_WARP = 17;
+constexpr int ATT_THREADS = 384;  // 8 softmax/flush warps + a warpgroup holding the producer warp and the MMA warp
+constexpr int COMPUTE_REGISTERS = 232, SERVICE_REGISTERS = 40;  // registers move from the third warpgroup to the two that hold `out`
+constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
 constexpr int STAGES = 3;
 constexpr int Q_BYTES = QUERY_TILE * HEAD_DIM;  // 16384
 constexpr int K_BYTES = KEY_TILE * HEAD_DIM;    // 8192
@@ -35,7 +34,7 @@ constexpr int V_BYTES = KEY_TILE * HEAD_DIM;    // 8192
 constexpr int TOK_BYTES = 2 * KEY_TILE * 4;     // 512
 constexpr int P_BYTES = QUERY_TILE * KEY_TILE;  // 8192
 constexpr int TMEM_COLUMNS = 512;
-constexpr int COL_S = 0, COL_ACC = 64, COL_OUT = 128;  // inside a query tile's 256 columns
+constexpr int COL_S = 0, COL_ACC = 128;  // inside a query tile's 256 columns: S buffers at 0 and 64, acc at 128
 
 struct __align__(128) AttSmem {
     int8_t q[2][Q_BYTES];
@@ -43,47 +42,49 @@ struct __align__(128) AttSmem {
     int8_t v[STAGES][V_BYTES];
     float tok[STAGES][2 * KEY_TILE];
     uint8_t p[2][2][P_BYTES];
-    float2 alpha_beta[2][2][QUERY_TILE];
-    float den[2][QUERY_TILE];
     uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    uint64_t s_full[2], s_free[2], p_ready[2][2], p_free[2][2], acc_full[2], acc_free[2], den_ready[2], drain;
+    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], drain;
     uint32_t tmem_base;
     int abort_flag;
 };
 
 // -DUNICA_TRACE: the first thread of each warpgroup of block (0, 0) adds up the cycles it spends in each phase of the
-// tile loop (the reference has a TRACE build for the same purpose: csrc/legacy.cu, bench/timeline.py).
+// tile loop (the reference has a TRACE build for the same purpose: csrc/legacy.cu, bench/timeline.py).  The totals
+// stay in registers until the end, so tracing itself costs a clock read per phase.
 #ifdef UNICA_TRACE
 __device__ long long g_trace[4][8];
-#define TRACE_DECL(slot) long long trace_t0 = clock64(); const int trace_slot = (slot); const bool tracing = blockIdx.x == 0 && blockIdx.y == 0 && row == 0
-#define TRACE(phase)                                      \
-    do {                                                  \
-        if (tracing) {                                    \
-            const long long now = clock64();              \
-            g_trace[trace_slot][phase] += now - trace_t0; \
-            trace_t0 = now;                               \
-        }                                                 \
+#define TRACE_DECL long long trace_t0 = clock64(), trace_sum[8] = {}; const bool tracing = blockIdx.x == 0 && blockIdx.y == 0 && row == 0
+#define TRACE(phase)                                 \
+    do {                                             \
+        if (tracing) {                               \
+            const long long now = clock64();         \
+            trace_sum[phase] += now - trace_t0;      \
+            trace_t0 = now;                          \
+        }                                            \
+    } while (0)
+#define TRACE_END(slot)                                                   \
+    do {                                                                  \
+        if (tracing)                                                      \
+            for (int i = 0; i < 8; ++i) g_trace[slot][i] = trace_sum[i];  \
     } while (0)
 #else
-#define TRACE_DECL(slot)
+#define TRACE_DECL
 #define TRACE(phase)
+#define TRACE_END(slot)
 #endif
-// Trace builds also leave progress marks in status[1 ..] (block (0, 0) only): pass host-mapped memory to watch a run.
-#ifdef UNICA_TRACE
-#define MARK(slot, value)                                                    \
-    do {                                                                     \
-        if (status && blockIdx.x == status[32] && blockIdx.y == status[33]) { \
-            reinterpret_cast<volatile int*>(status)[slot] = (value);         \
-            __threadfence_system();                                          \
-        }                                                                    \
-    } while (0)
+enum { TR_WAIT_S = 0, TR_LOAD_S = 1, TR_SOFTMAX = 2, TR_STORE_P = 3, TR_WAIT_PV = 4, TR_FLUSH = 5, TR_OTHER = 6 };
+
+// EXPERIMENT: tcgen05 fences of the computing warps
+#ifdef UNICA_NO_COMPUTE_FENCES
+#define COMPUTE_FENCE_AFTER()
+#define COMPUTE_FENCE_BEFORE()
 #else
-#define MARK(slot, value)
+#define COMPUTE_FENCE_AFTER() tc_fence_after()
+#define COMPUTE_FENCE_BEFORE() tc_fence_before()
 #endif
-enum { TR_WAIT = 0, TR_LOAD = 1, TR_MATH = 2, TR_STORE = 3, TR_WAIT2 = 4, TR_OTHER = 5 };
 
 constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
-constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM / 2);
+constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM);
 
 template <bool V_TOKEN>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
@@ -109,15 +110,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_init(&sm.v_empty[s], 1);
         }
         for (int g = 0; g < 2; ++g) {
-            mbar_init(&sm.s_full[g], 1);
-            mbar_init(&sm.s_free[g], 128);
             for (int b = 0; b < 2; ++b) {
+                mbar_init(&sm.s_full[g][b], 1);
+                mbar_init(&sm.s_free[g][b], 128);
                 mbar_init(&sm.p_ready[g][b], 128);
-                mbar_init(&sm.p_free[g][b], 1);
             }
             mbar_init(&sm.acc_full[g], 1);
             mbar_init(&sm.acc_free[g], 128);
-            mbar_init(&sm.den_ready[g], 128);
         }
         mbar_init(&sm.drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -128,7 +127,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    if (warp >= 16) {
+    if (warp >= 8) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SERVICE_REGISTERS));
       if (warp == PRODUCER_WARP) {
         // ------------------------------------------------------------------------------------------------ producer
@@ -151,7 +150,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 bulk_load(sm.v[s], v8 + (size_t(head) * k_tiles + t) * V_BYTES, V_BYTES, &sm.v_full[s]);
                 if (V_TOKEN) bulk_load(sm.tok[s], v_token + (size_t(head) * k_tiles + t) * (2 * KEY_TILE), TOK_BYTES, &sm.v_full[s]);
                 issued = t + 1;
-                MARK(9, issued);
             }
             if (*abort_flag) {  // let the copies still in flight land before the block's shared memory goes away
                 int never = 0;
@@ -162,55 +160,50 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         }
       } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------------------------------------------ MMA issue
-        // One thread polls what is ready and issues it: per query tile, the scores of the next key tile as soon as the
-        // softmax threads have taken the previous ones, and each channel half of P.V as soon as the flush threads have
-        // taken the previous half.
+        // One thread polls what is ready and issues it, per query tile: the scores of key tile n as soon as its K tile
+        // has landed and the softmax threads have taken the scores of tile n - 2 out of that buffer; P.V of tile t as
+        // soon as P^(t) is written, V(t) has landed and the flush of tile t - 1 has read the accumulator.
         if (lane == 0) {
             const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
             bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE);
-            int s_next[2] = {0, 0};  // next key tile whose scores to issue
-            int h_next[2] = {0, 0};  // next P.V half: 2 * tile + channel half
+            int s_next[2] = {0, 0};   // next key tile whose scores to issue
+            int pv_next[2] = {0, 0};  // next key tile whose P.V to issue
             long long idle_since = clock64();
-            while (ok && (s_next[0] < k_tiles || s_next[1] < k_tiles || h_next[0] < 2 * k_tiles || h_next[1] < 2 * k_tiles)) {
+            while (ok && (s_next[0] < k_tiles || s_next[1] < k_tiles || pv_next[0] < k_tiles || pv_next[1] < k_tiles)) {
                 bool progress = false;
 #pragma unroll
                 for (int g = 0; g < 2; ++g) {
                     const int n = s_next[g];
-                    if (n < k_tiles && mbar_test(&sm.k_full[n % STAGES], (n / STAGES) & 1) && mbar_test(&sm.s_free[g], n & 1)) {
+                    if (n < k_tiles && mbar_test(&sm.k_full[n % STAGES], (n / STAGES) & 1) &&
+                        mbar_test(&sm.s_free[g][n & 1], (n >> 1) & 1)) {
                         tc_fence_after();
                         const uint32_t k_addr = smem_u32(sm.k[n % STAGES]);
 #pragma unroll
                         for (int ks = 0; ks < HEAD_DIM / 32; ++ks)
-                            mma_i8_ss(tmem + g * 256 + COL_S, smem_desc(q_addr[g] + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                            mma_i8_ss(tmem + g * 256 + COL_S + (n & 1) * 64,
+                                      smem_desc(q_addr[g] + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
                                       smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_QK, true);
-                        mma_commit(&sm.s_full[g]);
+                        mma_commit(&sm.s_full[g][n & 1]);
                         s_next[g] = n + 1;
                         if (s_next[1 - g] > n) mma_commit(&sm.k_empty[n % STAGES]);  // both query tiles have read it
                         progress = true;
                     }
-                    const int h = h_next[g], t = h >> 1, half = h & 1, buf = t & 1;
-                    if (h < 2 * k_tiles && mbar_test(&sm.v_full[t % STAGES], (t / STAGES) & 1) &&
-                        mbar_test(&sm.p_ready[g][buf], (t >> 1) & 1) && mbar_test(&sm.acc_free[g], h & 1)) {
+                    const int t = pv_next[g];
+                    if (t < k_tiles && mbar_test(&sm.v_full[t % STAGES], (t / STAGES) & 1) &&
+                        mbar_test(&sm.p_ready[g][t & 1], (t >> 1) & 1) && mbar_test(&sm.acc_free[g], t & 1)) {
                         tc_fence_after();
-                        const uint32_t p_addr = smem_u32(sm.p[g][buf]), v_addr = smem_u32(sm.v[t % STAGES]) + half * (HEAD_DIM / 2) * 16;
+                        const uint32_t p_addr = smem_u32(sm.p[g][t & 1]), v_addr = smem_u32(sm.v[t % STAGES]);
 #pragma unroll
                         for (int ks = 0; ks < KEY_TILE / 32; ++ks)
                             mma_i8_ss(tmem + g * 256 + COL_ACC, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                                      smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, ks > 0);
+                                      smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, true);
                         mma_commit(&sm.acc_full[g]);
-                        h_next[g] = h + 1;
-                        if (half) {
-                            mma_commit(&sm.p_free[g][buf]);
-                            if (h_next[1 - g] > h) mma_commit(&sm.v_empty[t % STAGES]);
-                        }
+                        pv_next[g] = t + 1;
+                        if (pv_next[1 - g] > t) mma_commit(&sm.v_empty[t % STAGES]);
                         progress = true;
                     }
                 }
                 if (progress) {
-                    MARK(5, s_next[0]);
-                    MARK(6, s_next[1]);
-                    MARK(7, h_next[0]);
-                    MARK(8, h_next[1]);
                     idle_since = clock64();
                 } else if (*abort_flag) {
                     ok = false;
@@ -227,69 +220,83 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
         }
       }
-    } else if (warp < 8) {
-        // ------------------------------------------------------------------------------------------------ softmax
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGISTERS));
+    } else {
+        // ------------------------------------------------------------------------------------- softmax and flush
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(COMPUTE_REGISTERS));
         const int g = warp / 4, row = threadIdx.x % 128;
-        const int q_tile = 2 * blockIdx.x + g;
-        const uint32_t t_scores = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256 + COL_S;
+        const int q_tile = 2 * blockIdx.x + g, q_row = q_tile * QUERY_TILE + row;
+        const uint32_t lane_base = uint32_t((warp % 4) * 32) << 16;
+        const uint32_t t_scores = tmem + lane_base + g * 256 + COL_S, t_acc = tmem + lane_base + g * 256 + COL_ACC;
         const float sq = q_scale[size_t(head) * q_tiles + q_tile];
         const float* sk = k_scale + size_t(head) * k_tiles;
         const float2 minus_magic = make_float2(-MAGIC, -MAGIC), plus_magic = make_float2(MAGIC, MAGIC);
         float m = -INFINITY, den = 0.0f;
-        float sk_next = sk[0];
+        // The K scale of the tile the next softmax() takes, loaded a whole tile ahead of its use (volatile: the compiler
+        // would otherwise sink the load to the use and expose its latency on every tile).
+        auto load_scale = [](const float* p) {
+            float v;
+            asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+            return v;
+        };
+        float sk_reg = load_scale(sk);
+        // Tensor-memory refills are not waited for where they are issued: the buffer goes back to the MMA thread a
+        // little later, at a point where the refill has long completed (nobody needs it for another tile).
+        int pending_scores = -1;   // score buffer whose refill is in flight
+        bool pending_acc = false;  // accumulator refill in flight
+        float2 o[HEAD_DIM / 2];
+#pragma unroll
+        for (int i = 0; i < HEAD_DIM / 2; ++i) o[i] = make_float2(0.0f, 0.0f);
         bool ok = true;
-        TRACE_DECL(g);
+        TRACE_DECL;
 
-        // The score accumulator starts at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
-        tmem_fill32(t_scores, MAGIC_BITS);
-        tmem_fill32(t_scores + 32, MAGIC_BITS);
+        // Every accumulator starts at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
+#pragma unroll
+        for (int c = 0; c < 256; c += 32) tmem_fill32(t_scores + c, MAGIC_BITS);
         tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&sm.s_free[g]);
+        COMPUTE_FENCE_BEFORE();
+        mbar_arrive(&sm.s_free[g][0]);
+        mbar_arrive(&sm.s_free[g][1]);
+        mbar_arrive(&sm.acc_free[g]);
+        // The second warpgroup starts half a period late (when the first has delivered its first P^): the two then
+        // alternate between the exponentials and the flush instead of competing for the same unit at the same time.
+        if (g == 1) ok = mbar_wait_warp(&sm.p_ready[0][0], 0, abort_flag, status, STATUS_WAIT_P);
 
-        for (int t = 0; ok && t < k_tiles; ++t) {
+        // Tile t: scores -> P^ in shared memory; returns alpha and beta of the tile for its flush.
+        auto softmax = [&](int t, float& alpha, float& beta) -> bool {
             const int buf = t & 1, stage = t % STAGES;
             const int valid = min(KEY_TILE, n_keys - t * KEY_TILE);
-            const float c = (sq * sk_next) * scale_log2;
-            if (t + 1 < k_tiles) sk_next = sk[t + 1];  // needed a whole tile from now
+            const float c = (sq * sk_reg) * scale_log2;
+            if (t + 1 < k_tiles) sk_reg = load_scale(sk + t + 1);
             TRACE(TR_OTHER);
-            if (row == 0) MARK(1 + g, t * 16 + 1);
-            ok = mbar_wait_warp(&sm.s_full[g], t & 1, abort_flag, status, STATUS_WAIT_SCORES);
-            if (ok && V_TOKEN) ok = mbar_wait_warp(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
-            if (!ok) break;
-            tc_fence_after();
-            TRACE(TR_WAIT);
-            if (row == 0) MARK(1 + g, t * 16 + 2);
-            float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
-            tmem_ld64_sync(t_scores, x);
-            tmem_fill32(t_scores, MAGIC_BITS);
-            tmem_fill32(t_scores + 32, MAGIC_BITS);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&sm.s_free[g]);
-            if (row == 0) MARK(1 + g, t * 16 + 3);
-            TRACE(TR_LOAD);
-
+            if (!mbar_wait_warp(&sm.s_full[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+            if (V_TOKEN && !mbar_wait_warp(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+            COMPUTE_FENCE_AFTER();
+            TRACE(TR_WAIT_S);
+            // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels already fill most
+            // of the register file, so pass 2 reads the scores again, 16 at a time.
             const float2 c2 = make_float2(c, c);
             float tile_max;
-            if (!V_TOKEN) {
+            {
+                float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
+                tmem_ld64_sync(t_scores + buf * 64, x);
+                if (pending_acc || pending_scores >= 0) {
+                    tmem_wait_st();
+                    COMPUTE_FENCE_BEFORE();
+                    if (pending_acc) mbar_arrive(&sm.acc_free[g]);  // the accumulator the previous flush refilled
+                    if (pending_scores >= 0) mbar_arrive(&sm.s_free[g][pending_scores]);  // only between tiles 0 and 1
+                    pending_acc = false;
+                    pending_scores = -1;
+                }
+                if (V_TOKEN) {
+                    const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
+#pragma unroll
+                    for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
+                }
                 if (valid < KEY_TILE) {  // keys past the end: below every real score (|score| < 2^21)
 #pragma unroll
                     for (int j = 0; j < KEY_TILE; ++j)
-                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = MAGIC - 4194303.0f;
+                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
                 }
-            } else {
-                const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
-#pragma unroll
-                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
-                if (valid < KEY_TILE) {
-#pragma unroll
-                    for (int j = 0; j < KEY_TILE; ++j)
-                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
-                }
-            }
-            {  // the maximum as a tree: four independent chains
                 float top[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
@@ -298,21 +305,29 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
                 if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
             }
+            TRACE(TR_LOAD_S);
             const float m_new = fmaxf(m, tile_max);
-            const float alpha = ex2(m - m_new), beta = ex2(tile_max - m_new);
+            alpha = ex2(m - m_new);
+            beta = ex2(tile_max - m_new);
             m = m_new;
             const float offset = LOG2_255 - tile_max;
             const float2 offset2 = make_float2(offset, offset);
-            if (row == 0) MARK(1 + g, t * 16 + 4);
-            if (t >= 2) {  // the P buffer is free once P.V of tile t - 2 has read it
-                ok = mbar_wait_warp(&sm.p_free[g][buf], ((t >> 1) - 1) & 1, abort_flag, status, STATUS_WAIT_FREE);
-                if (!ok) break;
-            }
             uint8_t* p_row = sm.p[g][buf] + row * 16;
             unsigned isum[2] = {0, 0};
             float2 fsum = make_float2(0.0f, 0.0f);
+            // Pass 2: P^ = rint(255 * 2^(x - tile max)), 16 keys per step, the next 16 scores loading meanwhile.
+            float2 x[2][8];
+            tmem_ld16_async(t_scores + buf * 64, x[0]);
 #pragma unroll
             for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
+                tmem_wait_ld();
+                reg_fence8(x[chunk % 2]);
+                if (chunk + 1 < KEY_TILE / 16) {
+                    tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
+                } else {  // every score has been read: the buffer goes back to the MMA thread, refilled
+                    tmem_fill32(t_scores + buf * 64, MAGIC_BITS);
+                    tmem_fill32(t_scores + buf * 64 + 32, MAGIC_BITS);
+                }
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -320,7 +335,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
                         const int j = chunk * 8 + i * 2 + h;  // a pair of keys
-                        const float2 e = V_TOKEN ? add2(x[j], offset2) : fma2(add2(x[j], minus_magic), c2, offset2);
+                        float2 e = add2(x[chunk % 2][i * 2 + h], minus_magic);
+                        if (V_TOKEN) {
+                            e = add2(fma2(e, c2, reinterpret_cast<const float2*>(sm.tok[stage])[j]), offset2);
+                            if (valid < KEY_TILE) {
+                                if (2 * j >= valid) e.x = -INFINITY;
+                                if (2 * j + 1 >= valid) e.y = -INFINITY;
+                            }
+                        } else {
+                            e = fma2(e, c2, offset2);
+                        }
                         const float2 p = make_float2(ex2(e.x), ex2(e.y));
                         if (V_TOKEN) fsum = fma2(p, reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE)[j], fsum);
                         const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
@@ -335,115 +359,95 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 }
                 *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            sm.alpha_beta[g][buf][row] = make_float2(alpha, beta);
-            TRACE(TR_MATH);
+            pending_scores = buf;
+            TRACE(TR_SOFTMAX);
             fence_proxy_async();
             mbar_arrive(&sm.p_ready[g][buf]);
-            if (row == 0) MARK(1 + g, t * 16 + 5);
-            TRACE(TR_STORE);
+            TRACE(TR_STORE_P);
             den = den * alpha + (V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1])) * beta;
-        }
-        sm.den[g][row] = den;
-        mbar_arrive(&sm.den_ready[g]);
-    } else {
-        // ------------------------------------------------------------------------------------------------ flush
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FLUSH_REGISTERS));
-        const int g = (warp - 8) / 4, row = threadIdx.x % 128;
-        const int q_row = (2 * blockIdx.x + g) * QUERY_TILE + row;
-        const uint32_t t_base = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256;
-        const uint32_t t_acc = t_base + COL_ACC, t_out = t_base + COL_OUT;
-        const float2 minus_magic = make_float2(-MAGIC, -MAGIC);
-        bool ok = true;
-        TRACE_DECL(2 + g);
+            return true;
+        };
 
-#pragma unroll
-        for (int c = 0; c < HEAD_DIM; c += 32) tmem_fill32(t_out + c, 0u);  // out = 0
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&sm.acc_free[g]);
-
+        float alpha = 1.0f, beta = 1.0f;
+        if (ok) ok = softmax(0, alpha, beta);
         for (int t = 0; ok && t < k_tiles; ++t) {
-            const int buf = t & 1;
-            float2 ab = make_float2(1.0f, 1.0f);
-            bool rescale = false;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                TRACE(TR_OTHER);
-                if (row == 0) MARK(3 + g, (2 * t + half) * 16 + 1);
-                ok = mbar_wait_warp(&sm.acc_full[g], (2 * t + half) & 1, abort_flag, status, STATUS_WAIT_PV);
-                if (!ok) break;
-                tc_fence_after();
-                TRACE(TR_WAIT);
-                if (half == 0) {
-                    // alpha and beta were written before the arrival on p_ready, which P.V of this tile waited for; they
-                    // are read before acc is released, because the second half's completion frees them for tile t + 2
-                    ok = mbar_wait_warp(&sm.p_ready[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P);
-                    if (!ok) break;
-                    ab = sm.alpha_beta[g][buf][row];
-                    rescale = !__all_sync(0xffffffffu, ab.x == 1.0f);
-                }
-                if (row == 0) MARK(3 + g, (2 * t + half) * 16 + 2);
-                float2 a[32];  // 64 channels of P^.V^, integers
-                tmem_ld64_sync(t_acc, a);
-                tc_fence_before();
-                mbar_arrive(&sm.acc_free[g]);  // the other half (or the next tile) may start
-                if (row == 0) MARK(3 + g, (2 * t + half) * 16 + 3);
-                TRACE(TR_LOAD);
-                const float2 alpha2 = make_float2(ab.x, ab.x), beta2 = make_float2(ab.y, ab.y);
-#pragma unroll
-                for (int part = 0; part < 4; ++part) {
-                    float2 o[8];
-                    tmem_ld16_sync(t_out + half * 64 + part * 16, o);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float2 f;  // float(acc): MAGIC_BITS + value read as a float is MAGIC + value
-                        f.x = __uint_as_float(__float_as_uint(a[part * 8 + i].x) + MAGIC_BITS);
-                        f.y = __uint_as_float(__float_as_uint(a[part * 8 + i].y) + MAGIC_BITS);
-                        if (rescale) o[i] = mul2(o[i], alpha2);
-                        o[i] = fma2(beta2, add2(f, minus_magic), o[i]);
-                    }
-                    tmem_st16(t_out + half * 64 + part * 16, o);
-                }
+            float alpha_next = 1.0f, beta_next = 1.0f;
+            if (t + 1 < k_tiles) ok = softmax(t + 1, alpha_next, beta_next);
+            if (!ok) break;
+            // flush of tile t: out = out * alpha + beta * float(acc)
+            if (pending_acc) {  // only on the last tile, which no softmax() precedes
                 tmem_wait_st();
-                if (row == 0) MARK(3 + g, (2 * t + half) * 16 + 4);
-                TRACE(TR_MATH);
+                COMPUTE_FENCE_BEFORE();
+                mbar_arrive(&sm.acc_free[g]);
+                pending_acc = false;
             }
-        }
-
-        if (ok) ok = mbar_wait_warp(&sm.den_ready[g], 0, abort_flag, status, STATUS_WAIT_P);
-        ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-wide: no lane may skip them
-        if (ok) {
-            const bool valid_row = q_row < n_queries;
-            const float inv = 1.0f / sm.den[g][row];
-            __nv_bfloat16* dst = out + out_layout.offset(head, valid_row ? q_row : 0);
+            TRACE(TR_OTHER);
+            ok = mbar_wait_warp(&sm.acc_full[g], t & 1, abort_flag, status, STATUS_WAIT_PV);
+            if (!ok) break;
+            COMPUTE_FENCE_AFTER();
+            TRACE(TR_WAIT_PV);
+            float2 a[4][8];  // a ring of four 16-channel loads: tensor-memory latency (~180 cycles) hides behind the arithmetic
+#pragma unroll
+            for (int i = 0; i < 4; ++i) tmem_ld16_async(t_acc + i * 16, a[i]);
+            if (pending_scores >= 0) {  // the score buffer the last softmax refilled
+                tmem_wait_st();
+                COMPUTE_FENCE_BEFORE();
+                mbar_arrive(&sm.s_free[g][pending_scores]);
+                pending_scores = -1;
+            }
+            if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+                const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+                for (int i = 0; i < HEAD_DIM / 2; ++i) o[i] = mul2(o[i], alpha2);
+            }
+            const float2 beta2 = make_float2(beta, beta);
 #pragma unroll
             for (int part = 0; part < HEAD_DIM / 16; ++part) {
-                float2 o[8];
-                tmem_ld16_sync(t_out + part * 16, o);
-                uint32_t w[8];
+                if (part % 4 == 0) {  // tcgen05.wait::ld waits for every load issued so far
+                    tmem_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int c0 = part * 16 + 2 * i;
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i].x * v_scale[head * HEAD_DIM + c0] * inv,
-                                                                      o[i].y * v_scale[head * HEAD_DIM + c0 + 1] * inv);
+                    for (int i = 0; i < 4; ++i) reg_fence8(a[i]);
+                }
+                float2 f[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) f[i] = add2(a[part % 4][i], minus_magic);
+                if (part + 4 < HEAD_DIM / 16) tmem_ld16_async(t_acc + (part + 4) * 16, a[part % 4]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) o[part * 8 + i] = fma2(beta2, f[i], o[part * 8 + i]);
+                if (part % 2 == 1) tmem_fill32(t_acc + (part - 1) * 16, MAGIC_BITS);
+            }
+            pending_acc = true;
+            TRACE(TR_FLUSH);
+            alpha = alpha_next;
+            beta = beta_next;
+        }
+        TRACE_END(g);
+
+        if (ok && q_row < n_queries) {
+            const float inv = 1.0f / den;
+            __nv_bfloat16* dst = out + out_layout.offset(head, q_row);
+#pragma unroll
+            for (int chunk = 0; chunk < HEAD_DIM / 8; ++chunk) {
+                uint32_t w[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int c0 = chunk * 8 + 2 * i;
+                    const float2 v = o[chunk * 4 + i];
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(v.x * v_scale[head * HEAD_DIM + c0] * inv,
+                                                                      v.y * v_scale[head * HEAD_DIM + c0 + 1] * inv);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pair);
                 }
-                if (valid_row) {
-                    *reinterpret_cast<uint4*>(dst + part * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(dst + part * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-                }
+                *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
 
-    if (lane == 0) MARK(10 + warp, 1);
     tc_fence_before();
     __syncthreads();
     if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLUMNS);
     }
-    if (threadIdx.x == 0) MARK(31, 1);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

@@ -211,6 +211,24 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float2 (&v)[8]) 
         : "memory");
 }
 
+// 16 consecutive columns issued without waiting; tmem_wait_ld() then reg_fence8() before the first use.
+__device__ __forceinline__ void tmem_ld16_async(uint32_t taddr, float2 (&v)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=f"(v[0].x), "=f"(v[0].y), "=f"(v[1].x), "=f"(v[1].y), "=f"(v[2].x), "=f"(v[2].y), "=f"(v[3].x), "=f"(v[3].y),
+          "=f"(v[4].x), "=f"(v[4].y), "=f"(v[5].x), "=f"(v[5].y), "=f"(v[6].x), "=f"(v[6].y), "=f"(v[7].x), "=f"(v[7].y)
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void reg_fence8(float2 (&v)[8]) {
+    asm volatile(""
+                 : "+f"(v[0].x), "+f"(v[0].y), "+f"(v[1].x), "+f"(v[1].y), "+f"(v[2].x), "+f"(v[2].y), "+f"(v[3].x), "+f"(v[3].y),
+                   "+f"(v[4].x), "+f"(v[4].y), "+f"(v[5].x), "+f"(v[5].y), "+f"(v[6].x), "+f"(v[6].y), "+f"(v[7].x), "+f"(v[7].y)
+                 :
+                 : "memory");
+}
+
 // 32 consecutive columns of this thread's lane set to one value.
 __device__ __forceinline__ void tmem_fill32(uint32_t taddr, uint32_t v) {
     asm volatile(
