@@ -74,15 +74,6 @@ __device__ long long g_trace[4][8];
 #endif
 enum { TR_WAIT_S = 0, TR_LOAD_S = 1, TR_SOFTMAX = 2, TR_STORE_P = 3, TR_WAIT_PV = 4, TR_FLUSH = 5, TR_OTHER = 6 };
 
-// EXPERIMENT: tcgen05 fences of the computing warps
-#ifdef UNICA_NO_COMPUTE_FENCES
-#define COMPUTE_FENCE_AFTER()
-#define COMPUTE_FENCE_BEFORE()
-#else
-#define COMPUTE_FENCE_AFTER() tc_fence_after()
-#define COMPUTE_FENCE_BEFORE() tc_fence_before()
-#endif
-
 constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
 constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM);
 
@@ -239,10 +230,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             return v;
         };
         float sk_reg = load_scale(sk);
-        // Tensor-memory refills are not waited for where they are issued: the buffer goes back to the MMA thread a
-        // little later, at a point where the refill has long completed (nobody needs it for another tile).
-        int pending_scores = -1;   // score buffer whose refill is in flight
-        bool pending_acc = false;  // accumulator refill in flight
         float2 o[HEAD_DIM / 2];
 #pragma unroll
         for (int i = 0; i < HEAD_DIM / 2; ++i) o[i] = make_float2(0.0f, 0.0f);
@@ -253,7 +240,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
         for (int c = 0; c < 256; c += 32) tmem_fill32(t_scores + c, MAGIC_BITS);
         tmem_wait_st();
-        COMPUTE_FENCE_BEFORE();
+        tc_fence_before();
         mbar_arrive(&sm.s_free[g][0]);
         mbar_arrive(&sm.s_free[g][1]);
         mbar_arrive(&sm.acc_free[g]);
@@ -270,101 +257,154 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             TRACE(TR_OTHER);
             if (!mbar_wait_warp(&sm.s_full[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
             if (V_TOKEN && !mbar_wait_warp(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
-            COMPUTE_FENCE_AFTER();
+            tc_fence_after();
             TRACE(TR_WAIT_S);
-            // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels already fill most
-            // of the register file, so pass 2 reads the scores again, 16 at a time.
-            const float2 c2 = make_float2(c, c);
-            float tile_max;
-            {
+            if constexpr (V_TOKEN) {
                 float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
                 tmem_ld64_sync(t_scores + buf * 64, x);
-                if (pending_acc || pending_scores >= 0) {
-                    tmem_wait_st();
-                    COMPUTE_FENCE_BEFORE();
-                    if (pending_acc) mbar_arrive(&sm.acc_free[g]);  // the accumulator the previous flush refilled
-                    if (pending_scores >= 0) mbar_arrive(&sm.s_free[g][pending_scores]);  // only between tiles 0 and 1
-                    pending_acc = false;
-                    pending_scores = -1;
-                }
-                if (V_TOKEN) {
+                tmem_fill32(t_scores + buf * 64, MAGIC_BITS);  // completes while the maximum is taken
+                tmem_fill32(t_scores + buf * 64 + 32, MAGIC_BITS);
+                TRACE(TR_LOAD_S);
+
+                const float2 c2 = make_float2(c, c);
+                if (!V_TOKEN) {
+                    if (valid < KEY_TILE) {  // keys past the end: below every real score (|score| < 2^21)
+    #pragma unroll
+                        for (int j = 0; j < KEY_TILE; ++j)
+                            if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = MAGIC - 4194303.0f;
+                    }
+                } else {
                     const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
-#pragma unroll
+    #pragma unroll
                     for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
+                    if (valid < KEY_TILE) {
+    #pragma unroll
+                        for (int j = 0; j < KEY_TILE; ++j)
+                            if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
+                    }
                 }
-                if (valid < KEY_TILE) {  // keys past the end: below every real score (|score| < 2^21)
-#pragma unroll
-                    for (int j = 0; j < KEY_TILE; ++j)
-                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
+                float tile_max;
+                {  // four independent chains, then a tree
+                    float top[4];
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
+    #pragma unroll
+                    for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
+                    tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
+                    if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
                 }
-                float top[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
-#pragma unroll
-                for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
-                tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-                if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
-            }
-            TRACE(TR_LOAD_S);
-            const float m_new = fmaxf(m, tile_max);
-            alpha = ex2(m - m_new);
-            beta = ex2(tile_max - m_new);
-            m = m_new;
-            const float offset = LOG2_255 - tile_max;
-            const float2 offset2 = make_float2(offset, offset);
-            uint8_t* p_row = sm.p[g][buf] + row * 16;
-            unsigned isum[2] = {0, 0};
-            float2 fsum = make_float2(0.0f, 0.0f);
-            // Pass 2: P^ = rint(255 * 2^(x - tile max)), 16 keys per step, the next 16 scores loading meanwhile.
-            float2 x[2][8];
-            tmem_ld16_async(t_scores + buf * 64, x[0]);
-#pragma unroll
-            for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
-                tmem_wait_ld();
-                reg_fence8(x[chunk % 2]);
-                if (chunk + 1 < KEY_TILE / 16) {
-                    tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
-                } else {  // every score has been read: the buffer goes back to the MMA thread, refilled
-                    tmem_fill32(t_scores + buf * 64, MAGIC_BITS);
-                    tmem_fill32(t_scores + buf * 64 + 32, MAGIC_BITS);
-                }
-                uint32_t w[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t half[2];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int j = chunk * 8 + i * 2 + h;  // a pair of keys
-                        float2 e = add2(x[chunk % 2][i * 2 + h], minus_magic);
-                        if (V_TOKEN) {
-                            e = add2(fma2(e, c2, reinterpret_cast<const float2*>(sm.tok[stage])[j]), offset2);
-                            if (valid < KEY_TILE) {
-                                if (2 * j >= valid) e.x = -INFINITY;
-                                if (2 * j + 1 >= valid) e.y = -INFINITY;
-                            }
-                        } else {
-                            e = fma2(e, c2, offset2);
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.s_free[g][buf]);
+                const float m_new = fmaxf(m, tile_max);
+                alpha = ex2(m - m_new);
+                beta = ex2(tile_max - m_new);
+                m = m_new;
+                const float offset = LOG2_255 - tile_max;
+                const float2 offset2 = make_float2(offset, offset);
+                uint8_t* p_row = sm.p[g][buf] + row * 16;
+                unsigned isum[2] = {0, 0};
+                float2 fsum = make_float2(0.0f, 0.0f);
+    #pragma unroll
+                for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
+                    uint32_t w[4];
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t half[2];
+    #pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const int j = chunk * 8 + i * 2 + h;  // a pair of keys
+                            const float2 e = V_TOKEN ? add2(x[j], offset2) : fma2(add2(x[j], minus_magic), c2, offset2);
+                            const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                            if (V_TOKEN) fsum = fma2(p, reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE)[j], fsum);
+                            const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
+                            half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
                         }
-                        const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                        if (V_TOKEN) fsum = fma2(p, reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE)[j], fsum);
-                        const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
-                        half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
+                        w[i] = __byte_perm(half[0], half[1], 0x5410);
+                        if (!V_TOKEN && valid < KEY_TILE) {  // keys past the end weigh nothing
+                            const int left = valid - (chunk * 16 + i * 4);
+                            w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
+                        }
+                        if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
                     }
-                    w[i] = __byte_perm(half[0], half[1], 0x5410);
-                    if (!V_TOKEN && valid < KEY_TILE) {  // keys past the end weigh nothing
-                        const int left = valid - (chunk * 16 + i * 4);
-                        w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
-                    }
-                    if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
+                    *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                TRACE(TR_SOFTMAX);
+                fence_proxy_async();
+                mbar_arrive(&sm.p_ready[g][buf]);
+                TRACE(TR_STORE_P);
+                den = den * alpha + (fsum.x + fsum.y) * beta;
+            } else {
+                const float2 c2 = make_float2(c, c);
+                float tile_max;
+                {   // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels already fill most
+                    // of the register file, so pass 2 reads the scores again, 16 at a time.
+                    float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
+                    tmem_ld64_sync(t_scores + buf * 64, x);
+                    if (valid < KEY_TILE) {  // keys past the end: below every real score (|score| < 2^21)
+    #pragma unroll
+                        for (int j = 0; j < KEY_TILE; ++j)
+                            if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = MAGIC - 4194303.0f;
+                    }
+                    float top[4];
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
+    #pragma unroll
+                    for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
+                    tile_max = (fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) - MAGIC) * c;
+                }
+                TRACE(TR_LOAD_S);
+                const float m_new = fmaxf(m, tile_max);
+                alpha = ex2(m - m_new);
+                beta = ex2(tile_max - m_new);
+                m = m_new;
+                const float offset = LOG2_255 - tile_max;
+                const float2 offset2 = make_float2(offset, offset);
+                uint8_t* p_row = sm.p[g][buf] + row * 16;
+                unsigned isum[2] = {0, 0};
+                float2 fsum = make_float2(0.0f, 0.0f);
+                // Pass 2: P^ = rint(255 * 2^(x - tile max)), 16 keys per step, the next 16 scores loading meanwhile.
+                float2 x[2][8];
+                tmem_ld16_async(t_scores + buf * 64, x[0]);
+    #pragma unroll
+                for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
+                    tmem_wait_ld();
+                    reg_fence8(x[chunk % 2]);
+                    if (chunk + 1 < KEY_TILE / 16) {
+                        tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
+                    } else {  // every score has been read: refill the buffer (the wait comes after this chunk's arithmetic)
+                        tmem_fill32(t_scores + buf * 64, MAGIC_BITS);
+                        tmem_fill32(t_scores + buf * 64 + 32, MAGIC_BITS);
+                    }
+                    uint32_t w[4];
+    #pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint32_t half[2];
+    #pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const float2 e = fma2(add2(x[chunk % 2][i * 2 + h], minus_magic), c2, offset2);
+                            const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                            const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
+                            half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
+                        }
+                        w[i] = __byte_perm(half[0], half[1], 0x5410);
+                        if (valid < KEY_TILE) {  // keys past the end weigh nothing
+                            const int left = valid - (chunk * 16 + i * 4);
+                            w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
+                        }
+                        isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
+                    }
+                    *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.s_free[g][buf]);
+                TRACE(TR_SOFTMAX);
+                fence_proxy_async();
+                mbar_arrive(&sm.p_ready[g][buf]);
+                TRACE(TR_STORE_P);
+                den = den * alpha + __uint2float_rn(isum[0] + isum[1]) * beta;
             }
-            pending_scores = buf;
-            TRACE(TR_SOFTMAX);
-            fence_proxy_async();
-            mbar_arrive(&sm.p_ready[g][buf]);
-            TRACE(TR_STORE_P);
-            den = den * alpha + (V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1])) * beta;
             return true;
         };
 
@@ -375,26 +415,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             if (t + 1 < k_tiles) ok = softmax(t + 1, alpha_next, beta_next);
             if (!ok) break;
             // flush of tile t: out = out * alpha + beta * float(acc)
-            if (pending_acc) {  // only on the last tile, which no softmax() precedes
-                tmem_wait_st();
-                COMPUTE_FENCE_BEFORE();
-                mbar_arrive(&sm.acc_free[g]);
-                pending_acc = false;
-            }
             TRACE(TR_OTHER);
             ok = mbar_wait_warp(&sm.acc_full[g], t & 1, abort_flag, status, STATUS_WAIT_PV);
             if (!ok) break;
-            COMPUTE_FENCE_AFTER();
+            tc_fence_after();
             TRACE(TR_WAIT_PV);
             float2 a[4][8];  // a ring of four 16-channel loads: tensor-memory latency (~180 cycles) hides behind the arithmetic
 #pragma unroll
             for (int i = 0; i < 4; ++i) tmem_ld16_async(t_acc + i * 16, a[i]);
-            if (pending_scores >= 0) {  // the score buffer the last softmax refilled
-                tmem_wait_st();
-                COMPUTE_FENCE_BEFORE();
-                mbar_arrive(&sm.s_free[g][pending_scores]);
-                pending_scores = -1;
-            }
             if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
                 const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
@@ -416,7 +444,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 for (int i = 0; i < 8; ++i) o[part * 8 + i] = fma2(beta2, f[i], o[part * 8 + i]);
                 if (part % 2 == 1) tmem_fill32(t_acc + (part - 1) * 16, MAGIC_BITS);
             }
-            pending_acc = true;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sm.acc_free[g]);
             TRACE(TR_FLUSH);
             alpha = alpha_next;
             beta = beta_next;
