@@ -86,6 +86,37 @@ int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8
                               unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
                               int* status, void* stream);
 
+/* ---- fast mode (NVFP4) ------------------------------------------------------------------------------------------
+ * Operand layouts, per head (two e2m1 codes per byte, the lower contraction index in the low nibble; one e4m3 scale
+ * byte per 16 elements along the contraction; keys of a 64-key tile in the reference's slot order, bench/emulate.py:116-119):
+ *   Q4  [q_tiles (even)][4 chunks of 32 channels][128 rows][16]  8 KB/tile   SFQ [q_tiles][2 halves of 64 channels][128][4]
+ *   K4  [k_tiles][4][64 slots][16]                               4 KB/tile   SFK [k_tiles][2][64][4]
+ *   V4  [k_tiles][2 chunks of 32 slots][144 rows][16]            4.5 KB      SFV [k_tiles][160][4]
+ *       rows 0..127 channels, rows 128..143 ones (their column of P.V is the softmax denominator)
+ *   bias [q_blocks][k_tiles * 64] float: the Q-smoothing term, already times log2(e)/sqrt(128), slot order */
+
+/* outer = max(max|x - mean| * (1/2688), 1e-30) per head from per-channel statistics (mean may be NULL; all
+ * [heads][groups][128]).  Replaces the torch lines of unica/__init__.py:485-492. */
+int unica_b200_nvfp4_outer(const float* mean, const float* low, const float* high, int heads, int groups, float* outer,
+                           void* stream);
+
+/* Replaces quantize_fp4_rows (csrc/flash.cu:1183-1216; unica/__init__.py:473-500).  rows_per_tile 128: Q (token
+ * order), 64: K (slot order).  mean: [heads][ceil(n_tokens / mean_tokens)][128] or NULL (mean_tokens <= 0: one mean
+ * per head).  outer: [heads] from unica_b200_nvfp4_outer. */
+int unica_b200_quantize_fp4_rows(const void* x, unica_token_layout layout, const float* mean, int mean_tokens,
+                                 const float* outer, int heads, int n_tokens, int rows_per_tile, int tiles,
+                                 uint8_t* codes, uint8_t* sf, void* stream);
+
+/* Replaces quantize_v4 and the torch aminmax before it (csrc/flash.cu:1021-1050; unica/__init__.py:452-466).
+ * low, high: per-channel min and max over the head; v_outer [heads][128] is written. */
+int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layout, const float* low, const float* high, int heads,
+                              int n_tokens, uint8_t* codes, uint8_t* sf, float* v_outer, void* stream);
+
+/* Replaces smooth_bias (csrc/flash.cu:1254-1322; unica/__init__.py:503-521): q_mean[block] . (k - k_mean) in FP32 for
+ * every block of smoothed queries and every key, times scale_log2.  q_mean [heads][q_blocks][128], k_mean [heads][128]. */
+int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean, int heads,
+                           int q_blocks, int n_keys, float scale_log2, float* bias, void* stream);
+
 /* Hardware self-test of the tensor-core path (the idea of the reference's tests/test_mma.py: small integers make every
  * result exact, so a wrong lane or layout cannot hide).  One tcgen05.mma kind::i8 chain D[128 x n] = A[128 x k] . B[n x k]^T
  * with A (u8 if a_unsigned, else s8) and B (s8) given as the shared-memory images described above

@@ -355,3 +355,7 @@ def sm_count(device: torch.device) -> int:
     if device not in _SM_COUNTS:
         _SM_COUNTS[device] = torch.cuda.get_device_properties(device).multi_processor_count
     return _SM_COUNTS[device]
+
+
+from unicaattention_b200.fp4 import (FP4V, FP4Rows, decode_fp4_rows, decode_v4, quantize_fp4_rows, quantize_v4,  # noqa: E402,F401
+                                     smooth_bias)

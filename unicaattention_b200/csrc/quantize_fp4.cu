@@ -1,0 +1,253 @@
+// NVFP4 quantization passes of the fast mode: e2m1 codes with one e4m3 scale per 16 elements along the contraction
+// and one FP32 "outer" scale (per head for Q and K, per channel for V), plus the exact Q-smoothing term.
+//
+// Numerics follow the reference bit for bit (bench/emulate.py:98-113 block_scaled "nvfp4"; csrc/flash.cu:1021-1050,
+// 1183-1216): outer = max(amax * (1/2688), 1e-30); scale byte = e4m3(amax16 * (1/6) / outer), saturating; element code =
+// e2m1(x / (e4m3 value * outer)), round to nearest even, saturating, 0 where the block scale is 0.
+//
+// Outputs are the operand images tcgen05.mma kind::mxf4nvf4 reads (K-major, no swizzle, two codes per byte, the lower
+// contraction index in the low nibble), and the scale bytes in the order the attention kernel copies them into tensor
+// memory.  Keys inside a 64-key tile are stored in the reference's slot order (bench/emulate.py:116-119): the 16-key
+// scale blocks of P and V are defined on that order, so it is part of the numerics.
+#include <cuda_fp8.h>
+
+#include "capi.h"
+
+namespace unica {
+
+constexpr int FP4_THREADS = 256;
+constexpr int V4_ROWS = 144;      // 128 channels + 16 rows of ones: their column of P.V is the running denominator
+constexpr int V4_SF_ROWS = 160;   // scale words: 5 tensor-memory columns of 32 rows
+
+__host__ __device__ __forceinline__ int slot_key(int k) { return 32 * (k / 32) + 8 * (k % 8 / 2) + 2 * (k % 32 / 8) + k % 2; }
+
+__device__ __forceinline__ uint32_t to_e4m3(float x) { return __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3); }
+__device__ __forceinline__ float from_e4m3(uint32_t byte) {
+    return __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3)));
+}
+
+// 8 floats -> 8 e2m1 codes, element i in nibble i.
+__device__ __forceinline__ uint32_t pack_e2m1x8(const float* v) {
+    uint32_t word;
+    asm("{\n\t"
+        ".reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+        "}"
+        : "=r"(word)
+        : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+    return word;
+}
+
+// One block of 16 values: scale byte and 16 codes (two words).
+__device__ __forceinline__ void quantize_block16(float (&v)[16], float outer, uint32_t& byte, uint2& codes) {
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+    byte = to_e4m3(__fdiv_rn(amax * (1.0f / 6.0f), outer));
+    const float scale = from_e4m3(byte) * outer;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = scale > 0.0f ? __fdiv_rn(v[i], scale) : 0.0f;
+    codes = make_uint2(pack_e2m1x8(v), pack_e2m1x8(v + 8));
+}
+
+// outer[head] = max(max |x - mean| * (1/2688), 1e-30) from the per-channel (and per mean group) min and max of x:
+// the extreme elements go through the same float subtraction as every element, so this is the head's exact maximum
+// (unica/__init__.py:485-492).  mean/low/high: [heads][groups][128] (mean may be null).  Grid: heads, 128 threads.
+__global__ void __launch_bounds__(HEAD_DIM) nvfp4_outer_rows_kernel(const float* __restrict__ mean, const float* __restrict__ low,
+                                                                    const float* __restrict__ high, int groups,
+                                                                    float* __restrict__ outer) {
+    __shared__ float part[HEAD_DIM / 32];
+    const int head = blockIdx.x, c = threadIdx.x;
+    float amax = 0.0f;
+    for (int g = 0; g < groups; ++g) {
+        const size_t i = (size_t(head) * groups + g) * HEAD_DIM + c;
+        const float m = mean ? mean[i] : 0.0f;
+        amax = fmaxf(amax, fmaxf(fabsf(high[i] - m), fabsf(low[i] - m)));
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d /= 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    if (c % 32 == 0) part[c / 32] = amax;
+    __syncthreads();
+    if (c == 0) outer[head] = fmaxf(fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) * (1.0f / 2688.0f), 1e-30f);
+}
+
+// Q or K minus its mean in NVFP4 along the channels, one block per tile of ROWS tokens (128: Q, 64: K).
+// SLOTS: row r of a tile holds token tile * 64 + slot_key(r) (K); else token tile * ROWS + r (Q).
+// mean: [heads][groups][128], one group per mean_tokens tokens, or null.
+// codes: [heads][tiles][4 chunks of 32 channels][ROWS][16] bytes; sf: [heads][tiles][2 halves of 64 channels][ROWS][4] bytes.
+template <int ROWS, bool SLOTS>
+__global__ void __launch_bounds__(FP4_THREADS) quantize_rows_fp4_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
+                                                                         const float* __restrict__ mean, int mean_tokens, int groups,
+                                                                         const float* __restrict__ outer, int n_tokens,
+                                                                         uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+    const int head = blockIdx.y, tile = blockIdx.x;
+    const float head_outer = outer[head];
+    uint8_t* tile_codes = codes + (size_t(head) * gridDim.x + tile) * (ROWS * HEAD_DIM / 2);
+    uint8_t* tile_sf = sf + (size_t(head) * gridDim.x + tile) * (ROWS * 8);
+#pragma unroll
+    for (int it = 0; it < ROWS * 8 / FP4_THREADS; ++it) {
+        const int item = it * FP4_THREADS + threadIdx.x, row = item % ROWS, block = item / ROWS;  // block of 16 channels
+        const int token = SLOTS ? tile * ROWS + slot_key(row) : tile * ROWS + row;
+        float v[16];
+        if (token < n_tokens) {
+            const uint4* src = reinterpret_cast<const uint4*>(x + in.offset(head, token) + block * 16);
+            const uint4 raw[2] = {src[0], src[1]};
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(raw);
+            const float* mu = mean ? mean + (size_t(head) * groups + token / mean_tokens) * HEAD_DIM + block * 16 : nullptr;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = __bfloat1622float2(pairs[i]);
+                v[2 * i] = f.x - (mu ? mu[2 * i] : 0.0f);
+                v[2 * i + 1] = f.y - (mu ? mu[2 * i + 1] : 0.0f);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = 0.0f;
+        }
+        uint32_t byte;
+        uint2 packed;
+        quantize_block16(v, head_outer, byte, packed);
+        *reinterpret_cast<uint2*>(tile_codes + ((block / 2) * ROWS + row) * 16 + (block % 2) * 8) = packed;
+        tile_sf[((block / 4) * ROWS + row) * 4 + block % 4] = uint8_t(byte);
+    }
+}
+
+// V in NVFP4 along the keys, per channel, one block per tile of 64 keys (slot order).  low/high: the channel's min and
+// max over the head ([heads][128]); v_outer [heads][128] is written by tile 0.
+// codes: [heads][tiles][2 chunks of 32 slots][144 rows][16] bytes, rows 128..143 all ones (code 0x2);
+// sf: [heads][tiles][160 rows][4] bytes, rows 128..143 ones (0x38), rows 144..159 zeros.
+__global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_bfloat16* __restrict__ v, TokenLayout in,
+                                                                      const float* __restrict__ low, const float* __restrict__ high,
+                                                                      int n_tokens, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
+                                                                      float* __restrict__ v_outer) {
+    __shared__ float tile[KEY_TILE][HEAD_DIM + 1];  // by slot
+    const int head = blockIdx.y, t = blockIdx.x;
+    for (int item = threadIdx.x; item < KEY_TILE * 16; item += FP4_THREADS) {
+        const int slot = item / 16, chunk = item % 16, key = t * KEY_TILE + slot_key(slot);
+        float f[8];
+        if (key < n_tokens) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(v + in.offset(head, key) + chunk * 8);
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 p = __bfloat1622float2(pairs[i]);
+                f[2 * i] = p.x, f[2 * i + 1] = p.y;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) tile[slot][chunk * 8 + i] = f[i];
+    }
+    __syncthreads();
+    uint8_t* tile_codes = codes + (size_t(head) * gridDim.x + t) * (V4_ROWS * 32);
+    uint8_t* tile_sf = sf + (size_t(head) * gridDim.x + t) * (V4_SF_ROWS * 4);
+    for (int item = threadIdx.x; item < HEAD_DIM * 4; item += FP4_THREADS) {
+        const int c = item % HEAD_DIM, block = item / HEAD_DIM;  // block of 16 slots
+        const int ci = head * HEAD_DIM + c;
+        const float outer = fmaxf(fmaxf(high[ci], -low[ci]) * (1.0f / 2688.0f), 1e-30f);
+        if (t == 0 && block == 0) v_outer[ci] = outer;
+        float x[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) x[i] = tile[block * 16 + i][c];
+        uint32_t byte;
+        uint2 packed;
+        quantize_block16(x, outer, byte, packed);
+        *reinterpret_cast<uint2*>(tile_codes + ((block / 2) * V4_ROWS + c) * 16 + (block % 2) * 8) = packed;
+        tile_sf[c * 4 + block] = uint8_t(byte);
+    }
+    for (int item = threadIdx.x; item < 2 * 16 * 4; item += FP4_THREADS) {  // the rows of ones: 2 chunks x 16 rows x 4 words
+        const int chunk = item / 64, row = 128 + item / 4 % 16, word = item % 4;
+        reinterpret_cast<uint32_t*>(tile_codes + (chunk * V4_ROWS + row) * 16)[word] = 0x22222222u;
+    }
+    if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(tile_sf)[128 + threadIdx.x] = threadIdx.x < 16 ? 0x38383838u : 0u;
+}
+
+// The part of the scores that Q smoothing took out, added back exactly (bench/emulate.py:308-309; the reference's
+// smooth_bias kernel, csrc/flash.cu:1254-1322, gets there with three bf16 MMAs): for every block of `mean_tokens`
+// queries and every key, q_mean[block] . (k - k_mean) in FP32, times scale_log2, keys of a tile in slot order, 0 past
+// the last key.  bias: [heads][q_blocks][k_tiles * 64].  Grid (k_tiles, heads).
+__global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfloat16* __restrict__ k, TokenLayout in,
+                                                                   const float* __restrict__ k_mean, const float* __restrict__ q_mean,
+                                                                   int q_blocks, int n_keys, float scale_log2, float* __restrict__ bias) {
+    __shared__ float centred[KEY_TILE][HEAD_DIM + 1];
+    __shared__ float qm[4][HEAD_DIM];
+    const int head = blockIdx.y, t = blockIdx.x, k_tiles = gridDim.x;
+    for (int item = threadIdx.x; item < KEY_TILE * HEAD_DIM; item += FP4_THREADS) {
+        const int slot = item / HEAD_DIM, c = item % HEAD_DIM, key = t * KEY_TILE + slot_key(slot);
+        centred[slot][c] = key < n_keys ? __bfloat162float(k[in.offset(head, key) + c]) - k_mean[head * HEAD_DIM + c] : 0.0f;
+    }
+    const int slot = threadIdx.x % KEY_TILE, lane_block = threadIdx.x / KEY_TILE;  // 4 query blocks at a time
+    for (int b0 = 0; b0 < q_blocks; b0 += 4) {
+        __syncthreads();
+        for (int item = threadIdx.x; item < 4 * HEAD_DIM; item += FP4_THREADS) {
+            const int b = b0 + item / HEAD_DIM;
+            qm[item / HEAD_DIM][item % HEAD_DIM] = b < q_blocks ? q_mean[(size_t(head) * q_blocks + b) * HEAD_DIM + item % HEAD_DIM] : 0.0f;
+        }
+        __syncthreads();
+        const int b = b0 + lane_block;
+        if (b < q_blocks) {
+            float dot = 0.0f;
+#pragma unroll 8
+            for (int c = 0; c < HEAD_DIM; ++c) dot = fmaf(qm[lane_block][c], centred[slot][c], dot);
+            bias[(size_t(head) * q_blocks + b) * (size_t(k_tiles) * KEY_TILE) + t * KEY_TILE + slot] = dot * scale_log2;
+        }
+    }
+}
+
+}  // namespace unica
+
+using namespace unica;
+
+extern "C" int unica_b200_nvfp4_outer(const float* mean, const float* low, const float* high, int heads, int groups,
+                                      float* outer, void* stream) {
+    if (!low || !high || !outer) return unica_fail(UNICA_B200_ERR_ARGUMENT, "nvfp4_outer: null pointer");
+    if (heads <= 0 || groups <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "nvfp4_outer: heads and groups must be positive");
+    nvfp4_outer_rows_kernel<<<heads, HEAD_DIM, 0, static_cast<cudaStream_t>(stream)>>>(mean, low, high, groups, outer);
+    return unica_check_launch("nvfp4_outer");
+}
+
+extern "C" int unica_b200_quantize_fp4_rows(const void* x, unica_token_layout layout, const float* mean, int mean_tokens,
+                                            const float* outer, int heads, int n_tokens, int rows_per_tile, int tiles,
+                                            uint8_t* codes, uint8_t* sf, void* stream) {
+    if (!x || !outer || !codes || !sf) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows: heads and n_tokens must be positive");
+    if (rows_per_tile != 128 && rows_per_tile != 64)
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows: rows_per_tile must be 128 (Q) or 64 (K, slot order)");
+    if (tiles < (n_tokens + rows_per_tile - 1) / rows_per_tile) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows: tiles does not cover n_tokens");
+    if (mean && mean_tokens <= 0) mean_tokens = n_tokens;
+    if (!mean) mean_tokens = n_tokens;
+    const int groups = (n_tokens + mean_tokens - 1) / mean_tokens;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    if (rows_per_tile == 128)
+        quantize_rows_fp4_kernel<128, false><<<dim3(tiles, heads), FP4_THREADS, 0, s>>>(xb, to_layout(layout), mean, mean_tokens, groups, outer, n_tokens, codes, sf);
+    else
+        quantize_rows_fp4_kernel<64, true><<<dim3(tiles, heads), FP4_THREADS, 0, s>>>(xb, to_layout(layout), mean, mean_tokens, groups, outer, n_tokens, codes, sf);
+    return unica_check_launch("quantize_fp4_rows");
+}
+
+extern "C" int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layout, const float* low, const float* high,
+                                         int heads, int n_tokens, uint8_t* codes, uint8_t* sf, float* v_outer, void* stream) {
+    if (!v || !low || !high || !codes || !sf || !v_outer) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_v_fp4: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_v_fp4: heads and n_tokens must be positive");
+    const int tiles = (n_tokens + KEY_TILE - 1) / KEY_TILE;
+    quantize_v_fp4_kernel<<<dim3(tiles, heads), FP4_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(v), to_layout(layout), low, high, n_tokens, codes, sf, v_outer);
+    return unica_check_launch("quantize_v_fp4");
+}
+
+extern "C" int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
+                                      int heads, int q_blocks, int n_keys, float scale_log2, float* bias, void* stream) {
+    if (!k || !k_mean || !q_mean || !bias) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: null pointer");
+    if (heads <= 0 || q_blocks <= 0 || n_keys <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: heads, q_blocks and n_keys must be positive");
+    const int tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
+    smooth_bias_kernel<<<dim3(tiles, heads), FP4_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias);
+    return unica_check_launch("smooth_bias");
+}
