@@ -126,6 +126,15 @@ int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float
 int unica_b200_selftest_mma_i8(const void* a_image, const void* b_image, int n, int k, int a_unsigned, int variant,
                                int32_t* d, void* stream);
 
+/* The same for the block-scaled FP4 path: D[128 x n] = (A . sfa) . (B . sfb)^T with one tcgen05.mma
+ * kind::mxf4nvf4.block_scale.scale_vec::4X per 64 elements of k (k = 64 or 128).  a_image [k / 32][128][16],
+ * b_image [k / 32][n][16] bytes (two e2m1 codes per byte, low nibble first); sfa uint32 [k / 64][128], sfb uint32
+ * [k / 64][n]: byte i of a word is the e4m3 scale of elements 16 i .. 16 i + 15 of that 64-element step.  d: float
+ * [128][n].  variant 0 places the scale bytes in tensor memory as the attention kernel does; 1 is a diagnostic.
+ * Allocates a status word and synchronises the stream: not for the hot path. */
+int unica_b200_selftest_mma_nvf4(const void* a_image, const void* b_image, const void* sfa, const void* sfb, int n, int k,
+                                 int variant, float* d, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
