@@ -126,6 +126,17 @@ int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float
 int unica_b200_selftest_mma_i8(const void* a_image, const void* b_image, int n, int k, int a_unsigned, int variant,
                                int32_t* d, void* stream);
 
+/* Replaces attention_fp4 with SMOOTH_Q (csrc/flash.cu:1380-1524; launched from unica/__init__.py:179-189).  The fast
+ * mode: both contractions on tcgen05 kind::mxf4nvf4 with block scales in tensor memory, running-max softmax, P in NVFP4
+ * (1024 * 2^(x - m), one e4m3 scale per 16 slots), the denominator taken from a column of ones in V4.
+ * qk_outer [heads] = max(q_outer * k_outer, 1e-30); v_outer [heads][128]; bias: the table of unica_b200_smooth_bias or
+ * NULL (no Q smoothing), q_blocks = ceil(n_queries / smooth_q) its rows per head, smooth_q a multiple of 256.
+ * out, out_layout, scale_log2, status as for unica_b200_attention_int8. */
+int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
+                             const void* sfv, const float* qk_outer, const float* v_outer, const float* bias, int q_blocks,
+                             int smooth_q, void* out, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
+                             float scale_log2, int* status, void* stream);
+
 /* The same for the block-scaled FP4 path: D[128 x n] = (A . sfa) . (B . sfb)^T with one tcgen05.mma
  * kind::mxf4nvf4.block_scale.scale_vec::4X per 64 elements of k (k = 64 or 128).  a_image [k / 32][128][16],
  * b_image [k / 32][n][16] bytes (two e2m1 codes per byte, low nibble first); sfa uint32 [k / 64][128], sfb uint32

@@ -232,10 +232,24 @@ def kernel_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str
     separately (unica/__init__.py:288-356)."""
     _no_rope(rope)
     settings = _settings(kernel, tile)
-    if kernel == "attention_fp4":
-        raise NotImplementedError("the fast mode (attention_fp4) is not built yet in the B200 library")
     q, k, v = readable(q), readable(k), readable(v)
-    q_tiles = 2 * math.ceil(q.shape[2] / (2 * Q_SCALE_BLOCK))  # the kernel takes query tiles in pairs
+    q_tiles = 2 * math.ceil(q.shape[2] / (2 * Q_SCALE_BLOCK))  # the kernels take query tiles in pairs
+    if kernel == "attention_fp4":  # Q and K in NVFP4 along d, V along the keys; Q smoothed per block of SMOOTH_Q queries
+        smooth = settings["SMOOTH_Q"]
+        if smooth % 256:
+            raise ValueError(f"SMOOTH_Q must be a multiple of 256, got {smooth}")
+        k_mean, k_low, k_high = rope_stats(k)
+        if smooth:
+            q_mean, q_low, q_high = rope_stats(q, None, smooth)
+            q4, q_outer = quantize_fp4_rows(q, q_mean, 1, None, (q_low, q_high), smooth, tiles=q_tiles)
+            bias = smooth_bias(k, k_mean, q_mean)
+        else:
+            q4, q_outer = quantize_fp4_rows(q, None, tiles=q_tiles)
+            bias = None
+        k4, k_outer = quantize_fp4_rows(k, k_mean, 64, None, (k_low, k_high))
+        qk_outer = (q_outer * k_outer).clamp_min(1e-30).contiguous()
+        v4, v_outer = quantize_v4(v)
+        return q4, k4, v4, qk_outer, v_outer, bias, smooth
     q8, q_scale = quantize_int8(q, None, Q_SCALE_BLOCK, tiles=q_tiles)
     k_mean = rope_stats(k)[0]  # softmax cancels the mean
     k8, k_scale = quantize_int8(k, k_mean, K_SCALE_BLOCK)
@@ -292,7 +306,12 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
     if inputs is None:
         inputs = kernel_inputs(q, k, v, kernel, rope, **tile)
     if kernel == "attention_fp4":
-        raise NotImplementedError("the fast mode (attention_fp4) is not built yet in the B200 library")
+        q4, k4, v4, qk_outer, v_outer, bias, smooth = inputs
+        lib.call("unica_b200_attention_fp4", lib.ptr(q4.codes), lib.ptr(q4.sf), lib.ptr(k4.codes), lib.ptr(k4.sf), lib.ptr(v4.codes),
+                 lib.ptr(v4.sf), lib.ptr(qk_outer), lib.ptr(v_outer), lib.ptr(bias), 0 if bias is None else bias.shape[2], smooth,
+                 lib.ptr(out), token_layout(out), batch * heads, n_queries, n_keys, HEAD_DIM**-0.5 * LOG2E,
+                 lib.ptr(status_word(q.device)), lib.stream())
+        return out
     q8, q_scale, k8, k_scale, v8, v_scale, v_token, v_mode = inputs
     lib.call("unica_b200_attention_int8", lib.ptr(q8), lib.ptr(q_scale), lib.ptr(k8), lib.ptr(k_scale), lib.ptr(v8),
              lib.ptr(v_scale), lib.ptr(v_token), v_mode, lib.ptr(out), token_layout(out), batch * heads, n_queries,

@@ -1,0 +1,390 @@
+// The fast mode's flash-attention loop on tcgen05 (replaces the reference's attention_fp4, csrc/flash.cu:1380-1524).
+//
+// Both contractions run as tcgen05.mma kind::mxf4nvf4.block_scale.scale_vec::4X (e2m1 codes, one ue4m3 scale per 16
+// elements of the contraction, FP32 accumulators in tensor memory):
+//   S[g]  = Q4[g] . K4(t)^T     128 x 64,  2 instructions of K = 64 channels
+//   O[g] += P4[g](t) . V4(t)    128 x 144, 1 instruction of K = 64 keys; columns 0..127 are the output channels, column
+//                               128 multiplies P by a row of ones: the running softmax denominator, rescaled with O
+// One block = 256 query rows of one head = two tiles of 128 rows (warpgroups g = 0, 1; thread = query row = tensor-
+// memory lane) sharing every K and V tile; a third warpgroup holds the producer warp (bulk TMA copies) and the MMA warp.
+//
+// Numerics (bench/emulate.py:298-369 with the fast contract): scores x = S * (q_outer k_outer log2(e)/sqrt(d)) + bias,
+// bias the exact q_mean . (k - k_mean) term of Q smoothing; running maximum m; P = 1024 * 2^(x - m) in NVFP4 along the
+// keys of the tile in slot order with a fixed outer scale of 1: per 16 slots sp = e4m3(max P / 6), codes e2m1(P / sp);
+// O = O * 2^(m_old - m) + P^ . V^; out = O / (sum of P^) * v_outer.  The exponentials are ex2.approx, so a code of P
+// can land on the other side of a rounding tie than the emulation's: results agree to rounding, not bit for bit.
+//
+// Scale bytes live in tensor memory, row r of an operand in lane r % 32 of column r / 32 of every 32-lane quarter.  The
+// computing warps put them there with tcgen05.st: Q's once, K's and V's from the tile's shared-memory stage, P's after
+// exchanging the four bytes of each row through shared memory.
+//
+// Tensor memory per query tile (256 columns): S 0..63 | O 64..207 | SF of Q 208..215, K 216..219, P 220..223, V 224..228.
+// All waits are bounded (common.cuh).
+#include <cuda_fp8.h>
+
+#include "capi.h"
+#include "fp4_common.cuh"
+
+namespace unica {
+
+constexpr int F4_THREADS = 384;
+constexpr int F4_PRODUCER_WARP = 8, F4_MMA_WARP = 9;
+constexpr int F4_STAGES = 3;
+constexpr int Q4_BYTES = QUERY_TILE * HEAD_DIM / 2;  // 8192
+constexpr int SFQ_BYTES = 2 * QUERY_TILE * 4;        // 1024
+constexpr int K4_BYTES = KEY_TILE * HEAD_DIM / 2;    // 4096
+constexpr int SFK_BYTES = 2 * KEY_TILE * 4;          // 512
+constexpr int V4_TILE_ROWS = 144, V4_BYTES = 2 * V4_TILE_ROWS * 16;  // 4608
+constexpr int SFV_BYTES = 160 * 4;                   // 640
+constexpr int BIAS_BYTES = KEY_TILE * 4;             // 256
+constexpr int P4_BYTES = QUERY_TILE * KEY_TILE / 2;  // 4096
+constexpr int F4_TMEM_COLUMNS = 512;
+constexpr int F4_S = 0, F4_O = 64, F4_SFQ = 208, F4_SFK = 216, F4_SFP = 220, F4_SFV = 224;
+constexpr float P_LOG2_GAIN = 10.0f;  // P is taken times 2^10: its block scales (up to 1024 / 6) stay below e4m3's 448
+
+struct __align__(128) Fp4Smem {
+    uint8_t q[2][Q4_BYTES];
+    uint32_t sfq[2][2][QUERY_TILE];
+    uint8_t k[F4_STAGES][K4_BYTES];
+    uint32_t sfk[F4_STAGES][2][KEY_TILE];
+    uint8_t v[F4_STAGES][V4_BYTES];
+    uint32_t sfv[F4_STAGES][160];
+    float bias[F4_STAGES][KEY_TILE];
+    uint8_t p[2][P4_BYTES];
+    uint32_t sfp[2][QUERY_TILE];
+    uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
+    uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], sfp_ready[2], drain;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+constexpr uint32_t IDESC_F4_QK = idesc_nvf4(QUERY_TILE, KEY_TILE);
+constexpr uint32_t IDESC_F4_PV = idesc_nvf4(QUERY_TILE, V4_TILE_ROWS);
+
+__device__ __forceinline__ float lg2(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// two floats -> one byte of two e2m1 codes, `lo` in the low nibble
+__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
+    uint32_t byte;
+    asm("{ .reg .b8 b; cvt.rn.satfinite.e2m1x2.f32 b, %2, %1; cvt.u32.u8 %0, b; }" : "=r"(byte) : "f"(lo), "f"(hi));
+    return byte;
+}
+
+__global__ void __launch_bounds__(F4_THREADS, 1)
+    attention_fp4_kernel(const uint8_t* __restrict__ q4, const uint32_t* __restrict__ sfq, const uint8_t* __restrict__ k4,
+                         const uint32_t* __restrict__ sfk, const uint8_t* __restrict__ v4, const uint32_t* __restrict__ sfv,
+                         const float* __restrict__ qk_outer, const float* __restrict__ v_outer, const float* __restrict__ bias,
+                         int q_blocks, int smooth_q, __nv_bfloat16* __restrict__ out, TokenLayout out_layout, int n_queries,
+                         int n_keys, float scale_log2, int* status) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Fp4Smem& sm = *reinterpret_cast<Fp4Smem*>(smem_raw);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int head = blockIdx.y;
+    const int q_tiles = 2 * gridDim.x;
+    const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (threadIdx.x == 0) {
+        sm.abort_flag = 0;
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < F4_STAGES; ++s) {
+            mbar_init(&sm.k_full[s], 1);
+            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1);
+            mbar_init(&sm.v_empty[s], 1);
+        }
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(&sm.s_full[g], 1);
+            mbar_init(&sm.s_free[g], 128);
+            mbar_init(&sm.p_ready[g], 128);
+            mbar_init(&sm.o_full[g], 1);
+            mbar_init(&sm.sfp_ready[g], 128);
+        }
+        mbar_init(&sm.drain, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == F4_MMA_WARP) tmem_alloc(&sm.tmem_base, F4_TMEM_COLUMNS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+
+    if (warp == F4_PRODUCER_WARP) {
+        // ------------------------------------------------------------------------------------------------ producer
+        if (lane == 0) {
+            const size_t q_first = size_t(head) * q_tiles + 2 * blockIdx.x;
+            mbar_expect_tx(&sm.q_full, 2 * (Q4_BYTES + SFQ_BYTES));
+            bulk_load(sm.q[0], q4 + q_first * Q4_BYTES, 2 * Q4_BYTES, &sm.q_full);
+            bulk_load(sm.sfq[0], sfq + q_first * (SFQ_BYTES / 4), 2 * SFQ_BYTES, &sm.q_full);
+            const float* bias_row = bias ? bias + (size_t(head) * q_blocks + (2 * blockIdx.x * QUERY_TILE) / smooth_q) * (size_t(k_tiles) * KEY_TILE) : nullptr;
+            int issued = 0;
+            for (int t = 0; t < k_tiles; ++t) {
+                const int s = t % F4_STAGES, use = t / F4_STAGES;
+                const size_t tile = size_t(head) * k_tiles + t;
+                if (use > 0 && !mbar_wait(&sm.k_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) break;
+                mbar_expect_tx(&sm.k_full[s], K4_BYTES + SFK_BYTES);
+                bulk_load(sm.k[s], k4 + tile * K4_BYTES, K4_BYTES, &sm.k_full[s]);
+                bulk_load(sm.sfk[s], sfk + tile * (SFK_BYTES / 4), SFK_BYTES, &sm.k_full[s]);
+                if (use > 0 && !mbar_wait(&sm.v_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) {
+                    issued = t + 1;
+                    break;
+                }
+                mbar_expect_tx(&sm.v_full[s], V4_BYTES + SFV_BYTES + (bias_row ? BIAS_BYTES : 0));
+                bulk_load(sm.v[s], v4 + tile * V4_BYTES, V4_BYTES, &sm.v_full[s]);
+                bulk_load(sm.sfv[s], sfv + tile * (SFV_BYTES / 4), SFV_BYTES, &sm.v_full[s]);
+                if (bias_row) bulk_load(sm.bias[s], bias_row + size_t(t) * KEY_TILE, BIAS_BYTES, &sm.v_full[s]);
+                issued = t + 1;
+            }
+            if (*abort_flag) {
+                int never = 0;
+                for (int t = max(0, issued - F4_STAGES); t < issued; ++t)
+                    mbar_wait(&sm.k_full[t % F4_STAGES], (t / F4_STAGES) & 1, &never, nullptr, 0);
+                mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
+            }
+        }
+    } else if (warp == F4_MMA_WARP) {
+        // ------------------------------------------------------------------------------------------------ MMA issue
+        // One thread polls what is ready, per query tile: the scores of key tile n once the softmax threads have taken
+        // the previous scores and put K(n)'s scale bytes in tensor memory; P.V of tile t once P4(t) and the scale bytes
+        // of P and V are in place.
+        if (lane == 0) {
+            const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
+            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE);
+            int s_next[2] = {0, 0}, pv_next[2] = {0, 0};
+            long long idle_since = clock64();
+            while (ok && (s_next[0] < k_tiles || s_next[1] < k_tiles || pv_next[0] < k_tiles || pv_next[1] < k_tiles)) {
+                bool progress = false;
+#pragma unroll
+                for (int g = 0; g < 2; ++g) {
+                    const int n = s_next[g];
+                    if (n < k_tiles && mbar_test(&sm.s_free[g], n & 1) && mbar_test(&sm.k_full[n % F4_STAGES], (n / F4_STAGES) & 1)) {
+                        tc_fence_after();
+                        const uint32_t k_addr = smem_u32(sm.k[n % F4_STAGES]), base = tmem + g * 256;
+#pragma unroll
+                        for (int ks = 0; ks < 2; ++ks)
+                            mma_nvf4_ss(base + F4_S, smem_desc(q_addr[g] + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                                        smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_F4_QK,
+                                        base + F4_SFQ + 4 * ks, base + F4_SFK + 2 * ks, ks > 0);
+                        mma_commit(&sm.s_full[g]);
+                        s_next[g] = n + 1;
+                        if (s_next[1 - g] > n) mma_commit(&sm.k_empty[n % F4_STAGES]);
+                        progress = true;
+                    }
+                    const int t = pv_next[g];
+                    if (t < k_tiles && mbar_test(&sm.p_ready[g], t & 1) && mbar_test(&sm.v_full[t % F4_STAGES], (t / F4_STAGES) & 1)) {
+                        tc_fence_after();
+                        const uint32_t base = tmem + g * 256;
+                        mma_nvf4_ss(base + F4_O, smem_desc(smem_u32(sm.p[g]), QUERY_TILE * 16, 128),
+                                    smem_desc(smem_u32(sm.v[t % F4_STAGES]), V4_TILE_ROWS * 16, 128), IDESC_F4_PV, base + F4_SFP,
+                                    base + F4_SFV, t > 0);
+                        mma_commit(&sm.o_full[g]);
+                        pv_next[g] = t + 1;
+                        if (pv_next[1 - g] > t) mma_commit(&sm.v_empty[t % F4_STAGES]);
+                        progress = true;
+                    }
+                }
+                if (progress) {
+                    idle_since = clock64();
+                } else if (*abort_flag) {
+                    ok = false;
+                } else if (clock64() - idle_since > WAIT_LIMIT_CYCLES) {
+                    *abort_flag = 1;
+                    if (status) atomicCAS(status, 0, STATUS_WAIT_P);
+                    ok = false;
+                }
+            }
+            if (!ok) {
+                int never = 0;
+                mma_commit(&sm.drain);
+                mbar_wait(&sm.drain, 0, &never, nullptr, 0);
+            }
+        }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------------------------------------------ softmax
+        const int g = warp / 4, row = threadIdx.x % 128;
+        const int q_row = (2 * blockIdx.x + g) * QUERY_TILE + row;
+        const uint32_t my = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256;
+        const float c = qk_outer[head] * scale_log2;
+        const float2 c2 = make_float2(c, c);
+        const bool smoothed = bias != nullptr;
+        float m = -INFINITY;
+        bool ok = mbar_wait_warp(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
+                  mbar_wait_warp(&sm.k_full[0], 0, abort_flag, status, STATUS_WAIT_TILE);
+        if (ok) {  // scale bytes of Q (for the whole loop) and of the first K tile
+#pragma unroll
+            for (int s = 0; s < 2; ++s)
+                tmem_st4(my + F4_SFQ + 4 * s, sm.sfq[g][s][lane], sm.sfq[g][s][32 + lane], sm.sfq[g][s][64 + lane], sm.sfq[g][s][96 + lane]);
+            tmem_st4(my + F4_SFK, sm.sfk[0][0][lane], sm.sfk[0][0][32 + lane], sm.sfk[0][1][lane], sm.sfk[0][1][32 + lane]);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sm.s_free[g]);
+        }
+
+        for (int t = 0; ok && t < k_tiles; ++t) {
+            const int stage = t % F4_STAGES;
+            ok = mbar_wait_warp(&sm.s_full[g], t & 1, abort_flag, status, STATUS_WAIT_SCORES) &&
+                 mbar_wait_warp(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+            if (!ok) break;
+            tc_fence_after();
+            float2 x[KEY_TILE / 2];
+            tmem_ld64_sync(my + F4_S, x);
+            if (t + 1 < k_tiles) {  // the next K tile's scale bytes, then the scores buffer goes back
+                const int next = (t + 1) % F4_STAGES;
+                ok = mbar_wait_warp(&sm.k_full[next], ((t + 1) / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+                if (!ok) break;
+                tmem_st4(my + F4_SFK, sm.sfk[next][0][lane], sm.sfk[next][0][32 + lane], sm.sfk[next][1][lane], sm.sfk[next][1][32 + lane]);
+                tmem_wait_st();
+            }
+            tc_fence_before();
+            mbar_arrive(&sm.s_free[g]);
+
+            // scores in the log2 domain, the smoothing term added back, slots past the last key out of the maximum
+            if (smoothed) {
+                const float2* b2 = reinterpret_cast<const float2*>(sm.bias[stage]);
+#pragma unroll
+                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(x[j], c2, b2[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = mul2(x[j], c2);
+            }
+            if ((t + 1) * KEY_TILE > n_keys) {
+#pragma unroll
+                for (int j = 0; j < KEY_TILE; ++j) {
+                    const int key = t * KEY_TILE + 32 * (j / 32) + 8 * (j % 8 / 2) + 2 * (j % 32 / 8) + j % 2;  // slot -> key
+                    if (key >= n_keys) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
+                }
+            }
+            float block_max[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                float top = fmaxf(x[8 * b].x, x[8 * b].y);
+#pragma unroll
+                for (int i = 1; i < 8; ++i) top = max3(top, x[8 * b + i].x, x[8 * b + i].y);
+                block_max[b] = top;
+            }
+            const float m_new = fmaxf(m, fmaxf(fmaxf(block_max[0], block_max[1]), fmaxf(block_max[2], block_max[3])));
+            const float alpha = ex2(m - m_new);
+            m = m_new;
+
+            // P in NVFP4: per 16 slots a scale byte e4m3(max P / 6), then the codes straight out of the exponent
+            uint32_t codes[8], sf_word = 0;
+            const float2 gain2 = make_float2(P_LOG2_GAIN - m_new, P_LOG2_GAIN - m_new);
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const float top = ex2(block_max[b] - m_new + P_LOG2_GAIN) * (1.0f / 6.0f);
+                const uint32_t byte = __nv_cvt_float_to_fp8(top, __NV_SATFINITE, __NV_E4M3);
+                const float sp = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3)));
+                // P / sp as the emulation takes it, 1024 * 2^(x - m) times 1 / sp: a product of two correctly rounded
+                // factors lands on the other side of an e2m1 tie far less often than 2^(x - m + 10 - log2 sp) does
+                const float inv = sp > 0.0f ? __fdiv_rn(1.0f, sp) : 0.0f;
+                const float2 inv2 = make_float2(inv, inv);
+                sf_word |= byte << (8 * b);
+#pragma unroll
+                for (int w = 0; w < 2; ++w) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 e = add2(x[8 * b + 4 * w + i], gain2);
+                        const float2 r = mul2(make_float2(ex2(e.x), ex2(e.y)), inv2);
+                        word |= e2m1x2(r.x, r.y) << (8 * i);
+                    }
+                    codes[2 * b + w] = word;
+                }
+            }
+
+            if (t > 0) {  // P.V of the previous tile must have read P, its scales and V's, and written O
+                ok = mbar_wait_warp(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
+                if (!ok) break;
+                tc_fence_after();
+                if (!__all_sync(0xffffffffu, alpha == 1.0f)) {  // the maximum moved: O and the denominator shrink
+                    const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+                    for (int part = 0; part < V4_TILE_ROWS / 16; ++part) {
+                        float2 o[8];
+                        tmem_ld16_sync(my + F4_O + part * 16, o);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = mul2(o[i], alpha2);
+                        tmem_st16(my + F4_O + part * 16, o);
+                    }
+                }
+            }
+            uint8_t* p_row = sm.p[g] + row * 16;
+            *reinterpret_cast<uint4*>(p_row) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+            *reinterpret_cast<uint4*>(p_row + QUERY_TILE * 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+            // every 32-lane quarter of tensor memory needs the scale bytes of all 128 rows: exchange them through shared memory
+            sm.sfp[g][row] = sf_word;
+            mbar_arrive(&sm.sfp_ready[g]);  // an mbarrier, not bar.sync: its wait is bounded like every other
+            ok = mbar_wait_warp(&sm.sfp_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
+            if (!ok) break;
+            tmem_st4(my + F4_SFP, sm.sfp[g][lane], sm.sfp[g][32 + lane], sm.sfp[g][64 + lane], sm.sfp[g][96 + lane]);
+            tmem_st4(my + F4_SFV, sm.sfv[stage][lane], sm.sfv[stage][32 + lane], sm.sfv[stage][64 + lane], sm.sfv[stage][96 + lane]);
+            tmem_st1(my + F4_SFV + 4, sm.sfv[stage][128 + lane]);
+            tmem_wait_st();
+            tc_fence_before();
+            fence_proxy_async();
+            mbar_arrive(&sm.p_ready[g]);
+        }
+
+        if (ok) ok = mbar_wait_warp(&sm.o_full[g], (k_tiles - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
+        if (ok) {
+            tc_fence_after();
+            const bool valid_row = q_row < n_queries;
+            __nv_bfloat16* dst = out + out_layout.offset(head, valid_row ? q_row : 0);
+            float2 last[8];
+            tmem_ld16_sync(my + F4_O + HEAD_DIM, last);  // column 128: the sum of P^
+            const float inv = 1.0f / last[0].x;
+#pragma unroll
+            for (int part = 0; part < HEAD_DIM / 16; ++part) {
+                float2 o[8];
+                tmem_ld16_sync(my + F4_O + part * 16, o);
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int c0 = part * 16 + 2 * i;
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i].x * v_outer[head * HEAD_DIM + c0] * inv,
+                                                                      o[i].y * v_outer[head * HEAD_DIM + c0 + 1] * inv);
+                    w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                }
+                if (valid_row) {
+                    *reinterpret_cast<uint4*>(dst + part * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(dst + part * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == F4_MMA_WARP) {
+        tc_fence_after();
+        tmem_dealloc(tmem, F4_TMEM_COLUMNS);
+    }
+}
+
+}  // namespace unica
+
+using namespace unica;
+
+extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
+                                        const void* sfv, const float* qk_outer, const float* v_outer, const float* bias,
+                                        int q_blocks, int smooth_q, void* out, unica_token_layout out_layout, int heads,
+                                        int n_queries, int n_keys, float scale_log2, int* status, void* stream) {
+    if (!q4 || !sfq || !k4 || !sfk || !v4 || !sfv || !qk_outer || !v_outer || !out) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: null pointer");
+    if (heads <= 0 || heads > 65535 || n_queries <= 0 || n_keys <= 0)
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: heads must be in 1..65535, n_queries and n_keys positive");
+    if (bias && (smooth_q <= 0 || smooth_q % 256 || q_blocks != (n_queries + smooth_q - 1) / smooth_q))
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: with a smoothing term, smooth_q must be a multiple of 256 and q_blocks = ceil(n_queries / smooth_q)");
+    if (int e = unica_check_device()) return e;
+    const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE), heads);
+    const size_t smem = sizeof(Fp4Smem) + 128;
+    if (cudaFuncSetAttribute(attention_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+        return unica_check_launch("attention_fp4 (shared memory size)");
+    attention_fp4_kernel<<<grid, F4_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
+        q4, static_cast<const uint32_t*>(sfq), k4, static_cast<const uint32_t*>(sfk), v4, static_cast<const uint32_t*>(sfv), qk_outer,
+        v_outer, bias, q_blocks, smooth_q > 0 ? smooth_q : 1, static_cast<__nv_bfloat16*>(out), to_layout(out_layout), n_queries, n_keys,
+        scale_log2, status);
+    return unica_check_launch("attention_fp4");
+}
