@@ -60,6 +60,22 @@ int unica_b200_version(void);
 int unica_b200_channel_stats(const void* x, unica_token_layout layout, int heads, int n_tokens, int per, float* partial,
                              float* mean, float* low, float* high, void* stream);
 
+/* No counterpart in the reference.  unica_b200_channel_stats for callers that cannot provide the `partial` scratch:
+ * code running where device memory cannot be had (a hook inside a pipeline that keeps the card full, a C host without
+ * an allocator of its own) or must not be asked for (cudaMalloc / cudaFree stall the device).  The partial sums go to
+ * a 9 MiB array built into the library, which each GPU that loads the library holds until the process exits.
+ *   - limit: heads * ceil(n_tokens / 256) <= 6144 (40 heads x 32760 tokens need 5120); larger calls are refused with
+ *     UNICA_B200_ERR_ARGUMENT and should use unica_b200_channel_stats;
+ *   - allocates and frees nothing, here or in anything it calls; mean, low, high are still the caller's;
+ *   - the first call on each device also looks the array's device address up (the device must be current): make that
+ *     first call before starting any stream capture;
+ *   - all calls on a device share the one array, which keeps whatever the last call left in it (nothing in it needs
+ *     clearing between calls); two calls whose kernels may run at the same time, e.g. on different streams, race on
+ *     it and give wrong statistics: keep them ordered.
+ * Results are bit for bit those of unica_b200_channel_stats. */
+int unica_b200_channel_stats_static(const void* x, unica_token_layout layout, int heads, int n_tokens, int per, float* mean,
+                                    float* low, float* high, void* stream);
+
 /* Replaces quantize_int8 (csrc/flash.cu:334-372; unica/__init__.py:363-378).  x - mean (mean float [heads][128] or
  * NULL) in INT8 with one scale per block_tokens tokens: 128 for Q, 64 for K.  `tiles` >= ceil(n_tokens /
  * block_tokens) tiles are written (the extra ones zeros): the attention kernel wants Q8 with an even tile count.

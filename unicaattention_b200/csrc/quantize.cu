@@ -253,6 +253,62 @@ extern "C" int unica_b200_channel_stats(const void* x, unica_token_layout layout
     return unica_check_launch("channel_stats");
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The statistics pass for callers that cannot hand over scratch memory.
+//
+// unica_b200_channel_stats wants a `partial` buffer from its caller.  Some callers have none to give and no way to get
+// one: an attention hook that runs inside a sampler whose memory manager has already filled the card with staged
+// weights (an allocation there fails, or pushes something else out), a host written in C that owns no device
+// allocator, or a latency-critical loop that must not enter the CUDA allocator because cudaMalloc and cudaFree stall
+// the whole device.  For them the partial sums live in the array below, which is part of the library image: every GPU
+// that loads the library sets these bytes aside once, at load, and keeps them until the process ends.
+constexpr int STATIC_STATS_RECORDS = 6144;  // (head, 256-token block) pairs: 40 heads x 32760 tokens need 5120
+static __device__ __align__(256) float g_stats_scratch[size_t(STATIC_STATS_RECORDS) * 3 * HEAD_DIM];  // 9 MiB
+
+// In host code `g_stats_scratch` is only a handle for the symbol, not an address a kernel could use: the device address
+// has to be asked for, per device, with that device current.
+static float* stats_scratch_of_current_device(int* error) {
+    constexpr int MAX_DEVICES = 64;
+    static float* address[MAX_DEVICES] = {};
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= MAX_DEVICES) {
+        *error = unica_fail(UNICA_B200_ERR_CUDA, "channel_stats_static: cannot tell the current device");
+        return nullptr;
+    }
+    if (!address[device]) {  // first call on this device
+        float* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_stats_scratch);
+        if (e != cudaSuccess || !p) {
+            *error = unica_fail(UNICA_B200_ERR_CUDA, cudaGetErrorString(e));
+            return nullptr;
+        }
+        address[device] = p;  // the same value whichever thread gets here first
+    }
+    return address[device];
+}
+
+extern "C" int unica_b200_channel_stats_static(const void* x, unica_token_layout layout, int heads, int n_tokens, int per,
+                                               float* mean, float* low, float* high, void* stream) {
+    if (!x || !mean || !low || !high) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats_static: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats_static: heads and n_tokens must be positive");
+    if (per != 0 && (per < 0 || per % STATS_TOKENS)) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats_static: per must be 0 or a multiple of 256");
+    const int blocks = (n_tokens + STATS_TOKENS - 1) / STATS_TOKENS;
+    if (static_cast<long long>(heads) * blocks > STATIC_STATS_RECORDS)
+        return unica_fail(UNICA_B200_ERR_ARGUMENT,
+                          "channel_stats_static: heads * ceil(n_tokens / 256) exceeds the built-in scratch of 6144 records; "
+                          "use unica_b200_channel_stats with a buffer of your own");
+    int error = UNICA_B200_OK;
+    float* partial = stats_scratch_of_current_device(&error);
+    if (!partial) return error;
+    const int per_group = per ? per / STATS_TOKENS : blocks;
+    const int groups = (blocks + per_group - 1) / per_group;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Nothing in the scratch has to start at zero: every record the second kernel reads is written whole by the first.
+    channel_stats_kernel<<<dim3(blocks, heads), THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(x), to_layout(layout), n_tokens, partial);
+    channel_stats_finish_kernel<<<dim3(groups, heads), HEAD_DIM, 0, s>>>(partial, blocks, per_group, n_tokens, mean, low, high);
+    return unica_check_launch("channel_stats_static");
+}
+
 extern "C" int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const float* mean, int heads, int n_tokens,
                                         int block_tokens, int tiles, int8_t* codes, float* scales, void* stream) {
     if (!x || !codes || !scales) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: null pointer");

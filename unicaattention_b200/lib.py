@@ -36,6 +36,7 @@ SIGNATURES = {
     # name: argument types (every entry point returns int)
     "unica_b200_version": [],
     "unica_b200_channel_stats": [_P, TokenLayout, _I, _I, _I, _P, _P, _P, _P, _P],
+    "unica_b200_channel_stats_static": [_P, TokenLayout, _I, _I, _I, _P, _P, _P, _P],
     "unica_b200_quantize_int8": [_P, TokenLayout, _P, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_v_int8": [_P, TokenLayout, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
     "unica_b200_attention_int8": [_P, _P, _P, _P, _P, _P, _P, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
