@@ -293,19 +293,28 @@ def main():
         qs, ks, vs = q_host[:, :1], k_host[:, :1], v_host[:, :1]
         ref = oracle.reference_fp32(qs, ks, vs, 0, rows)
         k_mean = unica.rope_stats(k[:, :1])[0].cpu()
-        emu = (oracle.attention_fast(qs, ks, vs, 512, recip=True, k_mean=k_mean, q_count=rows) if args.mode == "fast" else
+        q_mean = unica.rope_stats(q[:, :1], None, 512)[0].cpu() if args.mode == "fast" else None
+        emu = (oracle.attention_fast(qs, ks, vs, 512, recip=True, k_mean=k_mean, q_mean=q_mean, q_count=rows) if args.mode == "fast" else
                oracle.attention_accurate(qs, ks, vs, oracle.V_TOKEN if args.mode == "per_token" else oracle.V_CHANNEL, recip=True,
                                          k_mean=k_mean, q_count=rows))
-        launches_per_step = 8 if args.mode != "per_token" else 6
+        # this library's launches per call: statistics (2 per pass), quantizers, (outer scales, smoothing term), attention
+        launches_per_step = {"per_channel": 8, "per_token": 6, "fast": 13}[args.mode]
+        kernel_name = "attention_fp4_kernel" if args.mode == "fast" else "attention_int8_kernel"
+        # bytes the quantization passes must move per head and token: bf16 read of Q, K, V + the operands written
+        written = {"per_channel": 3 * 128, "per_token": 3 * 128 + 8, "fast": 72 + 72 + 82}[args.mode]
+        reads = {"per_channel": 5 * 256, "per_token": 4 * 256, "fast": 7 * 256}[args.mode]  # statistics passes read again
+        # DRAM traffic of the attention kernel per launch: ncu on 40 heads x 8192 tokens (profiles/), scaled by heads x tokens
+        traffic = 544.3 * batch * heads * tokens / world if args.mode == "per_channel" else None
         line = {
             "metric": metric_name(args, batch, heads, tokens), "value": value, "unit": "TOPS", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": dtype_of(args.mode), "data": "synthetic", "config": config_of(args, batch, heads, tokens),
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
-            "roofline": {"bound": "tensor", "kernel": "attention_int8_kernel", "achieved": achieved, "peak": peak, "unit": "TOP/s (x1e12)",
-                         "frac": achieved / peak, "traffic": None, "ms_per_launch": ms_kernel, "peak_source": peak_source,
-                         "frac_of_nominal": achieved / (NOMINAL_PEAK_TOPS[args.mode] * world)},
-            "quantization": {"ms": ms_quant, "algorithmic_gbs": (3 * 256 + 3 * 128) * batch * heads * tokens / world / (ms_quant * 1e-3) / 1e9,
+            "roofline": {"bound": "tensor", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "TOP/s (x1e12)",
+                         "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch per GPU", "ms_per_launch": ms_kernel,
+                         "peak_source": peak_source, "frac_of_nominal": achieved / (NOMINAL_PEAK_TOPS[args.mode] * world)},
+            "quantization": {"ms": ms_quant, "algorithmic_gbs": (3 * 256 + written) * batch * heads * tokens / world / (ms_quant * 1e-3) / 1e9,
+                             "moved_gbs": (reads + written) * batch * heads * tokens / world / (ms_quant * 1e-3) / 1e9,
                              "hbm_peak_gbs": peaks.get("hbm_gbs")},
             "accuracy": {"sample": f"head {my_heads[0]}, first {rows} queries, all keys", "rel_l2_vs_fp32": oracle.rel_l2(out, ref),
                          "emulation_rel_l2_vs_fp32": oracle.rel_l2(emu, ref), "rel_l2_vs_emulation": oracle.rel_l2(out, emu)},

@@ -30,14 +30,14 @@ def gather_heads(local: torch.Tensor, out: torch.Tensor, heads: int, rank: int, 
     if heads % world == 0 and batch == 1 and out.is_contiguous() and local.is_contiguous():
         dist.all_gather_into_tensor(out.view(-1), local.view(-1), group=group)  # one collective, no staging copy
         return out
-    pieces = [out[:, head_slice(heads, r, world)] for r in range(world)]
-    if all(p.is_contiguous() for p in pieces) and local.is_contiguous():
-        dist.all_gather(pieces, local, group=group)
-    else:  # uneven or strided slices: gather into staging buffers, then place
-        staged = [torch.empty(p.shape, dtype=out.dtype, device=out.device) for p in pieces]
-        dist.all_gather(staged, local.contiguous(), group=group)
-        for p, s_ in zip(pieces, staged):
-            p.copy_(s_)
+    # uneven slices or a batch dimension: equal-sized staging buffers (the smaller slices padded), then placement
+    most = -(-heads // world)
+    padded = local if local.shape[1] == most else torch.cat([local, local.new_zeros(batch, most - local.shape[1], *local.shape[2:])], 1)
+    staged = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(staged, padded.contiguous(), group=group)
+    for r, piece in enumerate(staged):
+        s_ = head_slice(heads, r, world)
+        out[:, s_].copy_(piece[:, : s_.stop - s_.start])
     return out
 
 
