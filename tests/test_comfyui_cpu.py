@@ -1,0 +1,141 @@
+"""The ComfyUI boundary with stand-ins (no ComfyUI, no GPU): call conventions of the attention override, pass-through
+reasons, fallback after a failure, re-patching, the WanVideoWrapper wrapper (the reference's tests/test_comfyui.py)."""
+
+import sys
+import types
+
+import pytest
+import torch
+
+import unicaattention_b200 as unica
+from unicaattention_b200 import comfyui as nodes
+
+
+class Patcher:
+    """What the nodes use of ComfyUI's ModelPatcher."""
+
+    def __init__(self, options=None):
+        self.model_options = options if options is not None else {"transformer_options": {}}
+
+    def clone(self):
+        return Patcher({"transformer_options": dict(self.model_options["transformer_options"])})
+
+
+@pytest.fixture
+def fake_unica(monkeypatch):
+    """unica.attention replaced by exact attention on whatever device, recording its settings; tensors claim to be on
+    the GPU so that the routing rules can be exercised on the CPU."""
+    calls = []
+
+    def attention(q, k, v, **settings):
+        calls.append(settings)
+        return torch.nn.functional.scaled_dot_product_attention(q.float(), k.float(), v.float()).to(q.dtype)
+
+    monkeypatch.setattr(unica, "attention", attention)
+    monkeypatch.setattr(nodes, "checked", lambda: unica.Compatibility(unica.OK, ()))
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    nodes.FAILED.clear()
+    yield calls
+    nodes.FAILED.clear()
+
+
+def model_attention(q, k, v, *args, **kwargs):
+    return "model's own"
+
+
+def test_native_override_conventions(fake_unica):
+    (patched,) = nodes.UnicaAttentionNative().patch(Patcher(), True, v_scale="per_channel")
+    override = patched.model_options["transformer_options"]["optimized_attention_override"]
+    q = torch.randn(2, 50, 3 * 128)
+    exact = torch.nn.functional.scaled_dot_product_attention(*(x.view(2, 50, 3, 128).transpose(1, 2) for x in (q, q, q)))
+    out = override(model_attention, q, q, q, heads=3)  # heads by name (WAN)
+    assert out.shape == q.shape and torch.allclose(out.view(2, 50, 3, 128).transpose(1, 2), exact, atol=3e-2)
+    assert fake_unica[-1] == unica.PRESETS["per_channel"]
+    assert override(model_attention, q, q, q, 3).shape == q.shape  # heads by position (Flux, ...)
+    bhnd = q.view(2, 50, 3, 128).transpose(1, 2)
+    out = override(model_attention, bhnd, bhnd, bhnd, 3, skip_reshape=True, skip_output_reshape=True)
+    assert out.shape == bhnd.shape and torch.allclose(out, exact, atol=3e-2)
+    out = override(model_attention, bhnd, bhnd, bhnd, 3, skip_reshape=True)
+    assert out.shape == q.shape
+
+
+def test_native_override_passes_other_calls_through(fake_unica):
+    (patched,) = nodes.UnicaAttentionNative().patch(Patcher(), True)
+    override = patched.model_options["transformer_options"]["optimized_attention_override"]
+    q = torch.randn(1, 20, 2 * 128)
+    cases = [((q, q, q), dict(heads=2, mask=torch.ones(20, 20)), "mask"),
+             ((q, q[:, :7], q[:, :7]), dict(heads=2), "cross-attention"),
+             ((torch.randn(1, 20, 2 * 64),) * 3, dict(heads=2), "head size 64"),
+             ((q, q, q), dict(), "no heads"),
+             ((q, q, q), dict(heads=2, scale=0.5), "scale"),
+             ((q, q, torch.randn(1, 20, 128)), dict(heads=2), "q, k, v shapes differ")]
+    for tensors, kwargs, reason in cases:
+        assert override(model_attention, *tensors, **kwargs) == "model's own"
+        assert override.last_reason == reason
+    assert not fake_unica
+    assert override(model_attention, q, q, q, 2, None, None, False, False, "extra") == "model's own"
+    assert override.last_reason == "positional arguments"
+
+
+def test_previous_override_and_repatching(fake_unica):
+    def previous(func, q, k, v, *args, **kwargs):
+        return "previous override"
+
+    model = Patcher({"transformer_options": {"optimized_attention_override": previous}})
+    (once,) = nodes.UnicaAttentionNative().patch(model, True, v_scale="per_token")
+    (twice,) = nodes.UnicaAttentionNative().patch(once, True, mode="fast")
+    override = twice.model_options["transformer_options"]["optimized_attention_override"]
+    assert override.unica and override.previous is previous  # not stacked on the first patch
+    q = torch.randn(1, 20, 2 * 128)
+    assert override(model_attention, q, q[:, :5], q[:, :5], heads=2) == "previous override"
+    override(model_attention, q, q, q, heads=2)
+    assert fake_unica[-1] == unica.PRESETS["fast"]
+    first = once.model_options["transformer_options"]["optimized_attention_override"]
+    first(model_attention, q, q, q, heads=2)
+    assert fake_unica[-1] == unica.PRESETS["per_token"]  # each patched model keeps its own settings
+    assert model.model_options["transformer_options"]["optimized_attention_override"] is previous  # the original is untouched
+    (off,) = nodes.UnicaAttentionNative().patch(model, False)
+    assert off is model
+
+
+def test_failure_falls_back_for_good(fake_unica, monkeypatch):
+    def broken(q, k, v, **settings):
+        raise RuntimeError("no library")
+
+    monkeypatch.setattr(unica, "attention", broken)
+    (patched,) = nodes.UnicaAttentionNative().patch(Patcher(), True)
+    override = patched.model_options["transformer_options"]["optimized_attention_override"]
+    q = torch.randn(1, 20, 2 * 128)
+    assert override(model_attention, q, q, q, heads=2) == "model's own" and len(nodes.FAILED) == 1
+    assert override(model_attention, q, q, q, heads=2) == "model's own" and override.last_reason == "unica failed"
+
+
+def test_wanvideo_wrapper_routes_modes(fake_unica):
+    module = types.ModuleType("custom_nodes.wrapper.wanvideo.modules.model")
+    module.attention = lambda q, k, v, *args, attention_mode="sdpa", **kwargs: f"original {attention_mode}"
+    sys.modules[module.__name__] = module
+    try:
+        (patched,) = nodes.UnicaAttentionWanVideo().patch(Patcher(), True, v_scale="per_channel", vram_reserve_mb=2048)
+        assert patched.model_options["transformer_options"]["attention_mode_override"]["mode"] == "unica_per_channel"
+        assert unica.VRAM_RESERVE == 2048 * 2**20
+        assert nodes.wrap_attention() == 0  # wrapped once
+        q = torch.randn(1, 30, 2, 128)
+        assert module.attention(q, q, q, attention_mode="sageattn") == "original sageattn"
+        out = module.attention(q, q, q, attention_mode="unica_fast")
+        assert out.shape == q.shape and fake_unica[-1] == unica.PRESETS["fast"]
+        module.attention(q, q, q, attention_mode="unica")
+        assert fake_unica[-1] == unica.PRESETS["per_token"]
+        assert module.attention(q, q, q, attention_mode="unica_nonsense") == "original unica_nonsense"
+        nodes.FAILED.append(RuntimeError("earlier"))
+        assert module.attention(q, q, q, attention_mode="unica_fast") == "original sdpa"
+    finally:
+        del sys.modules[module.__name__]
+        unica.VRAM_RESERVE = None
+
+
+def test_mode_names_round_trip():
+    for v_scale in nodes.V_SCALES:
+        assert nodes.mode_settings(nodes.mode_name(v_scale, "accurate")) == unica.PRESETS[v_scale]
+    assert nodes.mode_settings(nodes.mode_name("per_token", "fast")) == unica.PRESETS["fast"]
+    assert nodes.mode_settings("sdpa") is None and nodes.mode_settings("unica") == unica.PRESETS["per_token"]
+    assert set(nodes.NODE_CLASS_MAPPINGS) == set(nodes.NODE_DISPLAY_NAME_MAPPINGS)
