@@ -162,6 +162,13 @@ int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* 
 int unica_b200_selftest_mma_nvf4(const void* a_image, const void* b_image, const void* sfa, const void* sfb, int n, int k,
                                  int variant, float* d, void* stream);
 
+/* Peak-rate micro-benchmark (the reference's csrc/peak.cu + bench/peak.py, for the instructions used here): cycles per
+ * instruction on one SM, median over `blocks` blocks.  kind 0: tcgen05.mma kind::i8 128 x n x 32; 1: kind::mxf4nvf4
+ * 128 x n x 64 (both on shared-memory operands in this library's layout; per MMA); 2..7: ex2.approx, fma.f32x2, fma.f32,
+ * prmt, cvt s32->f32, cvt f32->u32 (per warp instruction per scheduler; n unused).  count: instructions in the chain.
+ * Allocates scratch and synchronises the stream: a measurement tool. */
+int unica_b200_peak(int kind, int n, int count, int blocks, double* cycles_per_instruction, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

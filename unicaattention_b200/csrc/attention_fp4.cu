@@ -6,7 +6,8 @@
 //   O[g] += P4[g](t) . V4(t)    128 x 144, 1 instruction of K = 64 keys; columns 0..127 are the output channels, column
 //                               128 multiplies P by a row of ones: the running softmax denominator, rescaled with O
 // One block = 256 query rows of one head = two tiles of 128 rows (warpgroups g = 0, 1; thread = query row = tensor-
-// memory lane) sharing every K and V tile; a third warpgroup holds the producer warp (bulk TMA copies) and the MMA warp.
+// memory lane) sharing every K and V tile; a third warpgroup holds the producer warp (bulk TMA copies) and two MMA warps, one
+// elected thread of each issuing one query tile's instructions.
 //
 // Numerics (bench/emulate.py:298-369 with the fast contract): scores x = S * (q_outer k_outer log2(e)/sqrt(d)) + bias,
 // bias the exact q_mean . (k - k_mean) term of Q smoothing; running maximum m; P = 1024 * 2^(x - m) in NVFP4 along the
@@ -53,7 +54,7 @@ struct __align__(128) Fp4Smem {
     uint8_t p[2][P4_BYTES];
     uint32_t sfp[2][QUERY_TILE];
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
-    uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], sfp_ready[2], drain;
+    uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], sfp_ready[2], drain[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -92,9 +93,9 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         mbar_init(&sm.q_full, 1);
         for (int s = 0; s < F4_STAGES; ++s) {
             mbar_init(&sm.k_full[s], 1);
-            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.k_empty[s], 2);  // both query tiles' MMA threads commit to it
             mbar_init(&sm.v_full[s], 1);
-            mbar_init(&sm.v_empty[s], 1);
+            mbar_init(&sm.v_empty[s], 2);
         }
         for (int g = 0; g < 2; ++g) {
             mbar_init(&sm.s_full[g], 1);
@@ -103,7 +104,8 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             mbar_init(&sm.o_full[g], 1);
             mbar_init(&sm.sfp_ready[g], 128);
         }
-        mbar_init(&sm.drain, 1);
+        mbar_init(&sm.drain[0], 1);
+        mbar_init(&sm.drain[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == F4_MMA_WARP) tmem_alloc(&sm.tmem_base, F4_TMEM_COLUMNS);
@@ -114,7 +116,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 
     if (warp == F4_PRODUCER_WARP) {
         // ------------------------------------------------------------------------------------------------ producer
-        if (lane == 0) {
+        if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
             const size_t q_first = size_t(head) * q_tiles + 2 * blockIdx.x;
             mbar_expect_tx(&sm.q_full, 2 * (Q4_BYTES + SFQ_BYTES));
             bulk_load(sm.q[0], q4 + q_first * Q4_BYTES, 2 * Q4_BYTES, &sm.q_full);
@@ -145,61 +147,46 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
-    } else if (warp == F4_MMA_WARP) {
+    } else if (warp == F4_MMA_WARP || warp == F4_MMA_WARP + 1) {
         // ------------------------------------------------------------------------------------------------ MMA issue
-        // One thread polls what is ready, per query tile: the scores of key tile n once the softmax threads have taken
-        // the previous scores and put K(n)'s scale bytes in tensor memory; P.V of tile t once P4(t) and the scale bytes
-        // of P and V are in place.
-        if (lane == 0) {
-            const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
-            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE);
-            int s_next[2] = {0, 0}, pv_next[2] = {0, 0};
-            long long idle_since = clock64();
-            while (ok && (s_next[0] < k_tiles || s_next[1] < k_tiles || pv_next[0] < k_tiles || pv_next[1] < k_tiles)) {
-                bool progress = false;
+        // One elected thread per query tile (warp 9: tile 0, warp 10: tile 1), blocking on each operand in the order they
+        // become ready: the scores of key tile t + 1 once the softmax threads have taken those of tile t and put K(t + 1)'s
+        // scale bytes in tensor memory; then P.V of tile t once P4(t) and the scale bytes of P and V are in place.
+        if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
+            const int g = warp - F4_MMA_WARP;
+            const uint32_t q_addr = smem_u32(sm.q[g]), base = tmem + g * 256;
+            auto scores = [&](int n) -> bool {
+                const int stage = n % F4_STAGES;
+                if (!mbar_wait(&sm.k_full[stage], (n / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+                if (!mbar_wait(&sm.s_free[g], n & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sm.k[stage]);
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    const int n = s_next[g];
-                    if (n < k_tiles && mbar_test(&sm.s_free[g], n & 1) && mbar_test(&sm.k_full[n % F4_STAGES], (n / F4_STAGES) & 1)) {
-                        tc_fence_after();
-                        const uint32_t k_addr = smem_u32(sm.k[n % F4_STAGES]), base = tmem + g * 256;
-#pragma unroll
-                        for (int ks = 0; ks < 2; ++ks)
-                            mma_nvf4_ss(base + F4_S, smem_desc(q_addr[g] + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                                        smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_F4_QK,
-                                        base + F4_SFQ + 4 * ks, base + F4_SFK + 2 * ks, ks > 0);
-                        mma_commit(&sm.s_full[g]);
-                        s_next[g] = n + 1;
-                        if (s_next[1 - g] > n) mma_commit(&sm.k_empty[n % F4_STAGES]);
-                        progress = true;
-                    }
-                    const int t = pv_next[g];
-                    if (t < k_tiles && mbar_test(&sm.p_ready[g], t & 1) && mbar_test(&sm.v_full[t % F4_STAGES], (t / F4_STAGES) & 1)) {
-                        tc_fence_after();
-                        const uint32_t base = tmem + g * 256;
-                        mma_nvf4_ss(base + F4_O, smem_desc(smem_u32(sm.p[g]), QUERY_TILE * 16, 128),
-                                    smem_desc(smem_u32(sm.v[t % F4_STAGES]), V4_TILE_ROWS * 16, 128), IDESC_F4_PV, base + F4_SFP,
-                                    base + F4_SFV, t > 0);
-                        mma_commit(&sm.o_full[g]);
-                        pv_next[g] = t + 1;
-                        if (pv_next[1 - g] > t) mma_commit(&sm.v_empty[t % F4_STAGES]);
-                        progress = true;
-                    }
-                }
-                if (progress) {
-                    idle_since = clock64();
-                } else if (*abort_flag) {
-                    ok = false;
-                } else if (clock64() - idle_since > WAIT_LIMIT_CYCLES) {
-                    *abort_flag = 1;
-                    if (status) atomicCAS(status, 0, STATUS_WAIT_P);
-                    ok = false;
-                }
+                for (int ks = 0; ks < 2; ++ks)
+                    mma_nvf4_ss(base + F4_S, smem_desc(q_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                                smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_F4_QK, base + F4_SFQ + 4 * ks,
+                                base + F4_SFK + 2 * ks, ks > 0);
+                mma_commit(&sm.s_full[g]);
+                mma_commit(&sm.k_empty[stage]);
+                return true;
+            };
+            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) && scores(0);
+            for (int t = 0; ok && t < k_tiles; ++t) {
+                if (t + 1 < k_tiles) ok = scores(t + 1);
+                const int stage = t % F4_STAGES;
+                ok = ok && mbar_wait(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE) &&
+                     mbar_wait(&sm.p_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
+                if (!ok) break;
+                tc_fence_after();
+                mma_nvf4_ss(base + F4_O, smem_desc(smem_u32(sm.p[g]), QUERY_TILE * 16, 128),
+                            smem_desc(smem_u32(sm.v[stage]), V4_TILE_ROWS * 16, 128), IDESC_F4_PV, base + F4_SFP, base + F4_SFV, t > 0);
+                mma_commit(&sm.o_full[g]);
+                mma_commit(&sm.v_empty[stage]);
             }
             if (!ok) {
                 int never = 0;
-                mma_commit(&sm.drain);
-                mbar_wait(&sm.drain, 0, &never, nullptr, 0);
+                mma_commit(&sm.drain[g]);
+                mbar_wait(&sm.drain[g], 0, &never, nullptr, 0);
             }
         }
     } else if (warp < 8) {

@@ -4,7 +4,7 @@
 // thread owns one query row (tensor-memory lane = row, so row maxima and sums need no shuffles) and keeps that row's
 // 128 output channels in registers.  Both warpgroups share every K and V tile.  A third warpgroup holds warp 8, which
 // streams K8 / V8 tiles (contiguous 8 KB images written by the quantizers) into a ring of shared-memory stages with
-// bulk TMA copies, and warp 9, one thread of which polls what is ready and issues every tcgen05.mma:
+// bulk TMA copies, and warps 9 and 10, one elected thread of each issuing one query tile's tcgen05.mma:
 //
 //   S[g]   = Q8[g] . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, double-buffered in tensor memory
 //   acc[g] = P^[g](t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, one accumulator per tile
@@ -43,7 +43,7 @@ struct __align__(128) AttSmem {
     float tok[STAGES][2 * KEY_TILE];
     uint8_t p[2][2][P_BYTES];
     uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], drain;
+    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], drain[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -96,9 +96,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         mbar_init(&sm.q_full, 1);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&sm.k_full[s], 1);
-            mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.k_empty[s], 2);  // both query tiles' MMA threads commit to it
             mbar_init(&sm.v_full[s], 1);
-            mbar_init(&sm.v_empty[s], 1);
+            mbar_init(&sm.v_empty[s], 2);
         }
         for (int g = 0; g < 2; ++g) {
             for (int b = 0; b < 2; ++b) {
@@ -109,7 +109,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_init(&sm.acc_full[g], 1);
             mbar_init(&sm.acc_free[g], 128);
         }
-        mbar_init(&sm.drain, 1);
+        mbar_init(&sm.drain[0], 1);
+        mbar_init(&sm.drain[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MMA_WARP) tmem_alloc(&sm.tmem_base, TMEM_COLUMNS);
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SERVICE_REGISTERS));
       if (warp == PRODUCER_WARP) {
         // ------------------------------------------------------------------------------------------------ producer
-        if (lane == 0) {
+        if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
             const int8_t* q_src = q8 + (size_t(head) * q_tiles + 2 * blockIdx.x) * Q_BYTES;
             mbar_expect_tx(&sm.q_full, 2 * Q_BYTES);
             bulk_load(sm.q[0], q_src, Q_BYTES, &sm.q_full);
@@ -149,65 +150,52 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
-      } else if (warp == MMA_WARP) {
+      } else if (warp == MMA_WARP || warp == MMA_WARP + 1) {
         // ------------------------------------------------------------------------------------------------ MMA issue
-        // One thread polls what is ready and issues it, per query tile: the scores of key tile n as soon as its K tile
-        // has landed and the softmax threads have taken the scores of tile n - 2 out of that buffer; P.V of tile t as
-        // soon as P^(t) is written, V(t) has landed and the flush of tile t - 1 has read the accumulator.
-        if (lane == 0) {
-            const uint32_t q_addr[2] = {smem_u32(sm.q[0]), smem_u32(sm.q[1])};
+        // One elected thread per query tile (warp 9: tile 0, warp 10: tile 1) issues that tile's tcgen05.mma in the order
+        // its operands become ready: P.V of key tile t once P^(t) is written, V(t) has landed and the flush of tile t - 1
+        // has read the accumulator; then the scores of tile t + 2 into the buffer the softmax of tile t has emptied.
+        // Each wait blocks in hardware (mbarrier.try_wait) and wakes as the phase completes; a stage of K or V is
+        // released by the second of the two threads' commits.
+        if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
+            const int g = warp - MMA_WARP;
+            const uint32_t q_addr = smem_u32(sm.q[g]), base = tmem + g * 256;
+            auto scores = [&](int n) -> bool {
+                const int stage = n % STAGES, buf = n & 1;
+                if (!mbar_wait(&sm.k_full[stage], (n / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+                if (!mbar_wait(&sm.s_free[g][buf], (n >> 1) & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sm.k[stage]);
+#pragma unroll
+                for (int ks = 0; ks < HEAD_DIM / 32; ++ks)
+                    mma_i8_ss(base + COL_S + buf * 64, smem_desc(q_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                              smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_QK, true);
+                mma_commit(&sm.s_full[g][buf]);
+                mma_commit(&sm.k_empty[stage]);
+                return true;
+            };
             bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE);
-            int s_next[2] = {0, 0};   // next key tile whose scores to issue
-            int pv_next[2] = {0, 0};  // next key tile whose P.V to issue
-            long long idle_since = clock64();
-            while (ok && (s_next[0] < k_tiles || s_next[1] < k_tiles || pv_next[0] < k_tiles || pv_next[1] < k_tiles)) {
-                bool progress = false;
+            for (int n = 0; ok && n < min(2, k_tiles); ++n) ok = scores(n);
+            for (int t = 0; ok && t < k_tiles; ++t) {
+                const int stage = t % STAGES, buf = t & 1;
+                ok = mbar_wait(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE) &&
+                     mbar_wait(&sm.p_ready[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P) &&
+                     mbar_wait(&sm.acc_free[g], t & 1, abort_flag, status, STATUS_WAIT_FREE);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t p_addr = smem_u32(sm.p[g][buf]), v_addr = smem_u32(sm.v[stage]);
 #pragma unroll
-                for (int g = 0; g < 2; ++g) {
-                    const int n = s_next[g];
-                    if (n < k_tiles && mbar_test(&sm.k_full[n % STAGES], (n / STAGES) & 1) &&
-                        mbar_test(&sm.s_free[g][n & 1], (n >> 1) & 1)) {
-                        tc_fence_after();
-                        const uint32_t k_addr = smem_u32(sm.k[n % STAGES]);
-#pragma unroll
-                        for (int ks = 0; ks < HEAD_DIM / 32; ++ks)
-                            mma_i8_ss(tmem + g * 256 + COL_S + (n & 1) * 64,
-                                      smem_desc(q_addr[g] + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                                      smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_QK, true);
-                        mma_commit(&sm.s_full[g][n & 1]);
-                        s_next[g] = n + 1;
-                        if (s_next[1 - g] > n) mma_commit(&sm.k_empty[n % STAGES]);  // both query tiles have read it
-                        progress = true;
-                    }
-                    const int t = pv_next[g];
-                    if (t < k_tiles && mbar_test(&sm.v_full[t % STAGES], (t / STAGES) & 1) &&
-                        mbar_test(&sm.p_ready[g][t & 1], (t >> 1) & 1) && mbar_test(&sm.acc_free[g], t & 1)) {
-                        tc_fence_after();
-                        const uint32_t p_addr = smem_u32(sm.p[g][t & 1]), v_addr = smem_u32(sm.v[t % STAGES]);
-#pragma unroll
-                        for (int ks = 0; ks < KEY_TILE / 32; ++ks)
-                            mma_i8_ss(tmem + g * 256 + COL_ACC, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                                      smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, true);
-                        mma_commit(&sm.acc_full[g]);
-                        pv_next[g] = t + 1;
-                        if (pv_next[1 - g] > t) mma_commit(&sm.v_empty[t % STAGES]);
-                        progress = true;
-                    }
-                }
-                if (progress) {
-                    idle_since = clock64();
-                } else if (*abort_flag) {
-                    ok = false;
-                } else if (clock64() - idle_since > WAIT_LIMIT_CYCLES) {
-                    *abort_flag = 1;
-                    if (status) atomicCAS(status, 0, STATUS_WAIT_P);
-                    ok = false;
-                }
+                for (int ks = 0; ks < KEY_TILE / 32; ++ks)
+                    mma_i8_ss(base + COL_ACC, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
+                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, true);
+                mma_commit(&sm.acc_full[g]);
+                mma_commit(&sm.v_empty[stage]);
+                if (t + 2 < k_tiles) ok = scores(t + 2);
             }
             if (!ok) {  // whatever was issued must finish before tensor memory is freed
                 int never = 0;
-                mma_commit(&sm.drain);
-                mbar_wait(&sm.drain, 0, &never, nullptr, 0);
+                mma_commit(&sm.drain[g]);
+                mbar_wait(&sm.drain[g], 0, &never, nullptr, 0);
             }
         }
       }

@@ -280,6 +280,16 @@ __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint
         : "memory");
 }
 
+// True in exactly one lane of a converged warp.  tcgen05.mma and tcgen05.commit take their operands from uniform
+// registers: issued under `if (elect_one())` by a warp whose control flow is otherwise uniform they cost a few cycles;
+// issued by one lane of a diverged warp (`if (lane == 0) { loop }`) each costs ~190 cycles (measured), because every
+// operand is then moved into the uniform file the slow way.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{ .reg .b32 r; .reg .pred p; elect.sync r|p, 0xffffffff; selp.b32 %0, 1, 0, p; }" : "=r"(pred));
+    return pred != 0;
+}
+
 // The mbarrier gets one arrival once every tcgen05.mma this thread issued before has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");

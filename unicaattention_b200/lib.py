@@ -43,6 +43,7 @@ SIGNATURES = {
     "unica_b200_selftest_mma_i8": [_P, _P, _I, _I, _I, _I, _P, _P],
     "unica_b200_attention_fp4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
     "unica_b200_selftest_mma_nvf4": [_P, _P, _P, _P, _I, _I, _I, _P, _P],
+    "unica_b200_peak": [_I, _I, _I, _I, _P, _P],
     "unica_b200_nvfp4_outer": [_P, _P, _P, _I, _I, _P, _P],
     "unica_b200_quantize_fp4_rows": [_P, TokenLayout, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_v_fp4": [_P, TokenLayout, _P, _P, _I, _I, _P, _P, _P, _P],
