@@ -1,6 +1,6 @@
 """Benchmark of the quantized-attention forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode per_channel|per_token|fast] [--workload wan|hires|image|small]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--mode per_channel|per_token|outliers|fast] [--workload wan|hires|image|small]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
     python bench.py --impl reference ...      # the CPU oracle port timed on the host cores, same config and metric
 
@@ -41,7 +41,7 @@ WORKLOADS = {  # (batch, heads, tokens): BASELINE.json configs
     "small": (1, 4, 1024),  # configs[0]
 }
 PUBLISHED_RTX5080_TOPS = {"per_channel": 288.0}  # 76.3 ms on an RTX 5080, other hardware: not a baseline for B200
-NOMINAL_PEAK_TOPS = {"per_channel": 4500.0, "per_token": 4500.0, "fast": 9000.0}  # dense INT8 / NVFP4, datasheet
+NOMINAL_PEAK_TOPS = {"per_channel": 4500.0, "per_token": 4500.0, "outliers": 4500.0, "fast": 9000.0}  # dense INT8 / NVFP4, datasheet
 
 
 def ops(batch, heads, nq, nk):
@@ -118,7 +118,7 @@ def cpu_baseline(mode: str, tokens: int, sample_rows: int = 2048) -> dict:
     if mode == "fast":
         oracle.attention_fast(q, k, v, 512, recip=True, q_first=0, q_count=rows)
     else:
-        oracle.attention_accurate(q, k, v, oracle.V_TOKEN if mode == "per_token" else oracle.V_CHANNEL, recip=True,
+        oracle.attention_accurate(q, k, v, {"per_token": oracle.V_TOKEN, "outliers": oracle.V_OUTLIERS}.get(mode, oracle.V_CHANNEL), recip=True,
                                   q_first=0, q_count=rows)
     seconds = time.perf_counter() - start
     return {"value": ops(1, 1, rows, tokens) / seconds / 1e12, "unit": "TOPS", "cores": oracle.threads(), "kind": "port",
@@ -170,7 +170,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--mode", default="per_channel", choices=["per_channel", "per_token", "fast"])
+    ap.add_argument("--mode", default="per_channel", choices=["per_channel", "per_token", "outliers", "fast"])
     ap.add_argument("--workload", default="wan", choices=list(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-rows", type=int, default=2048, help="query rows of the CPU baseline's sample")
@@ -295,14 +295,14 @@ def main():
         k_mean = unica.rope_stats(k[:, :1])[0].cpu()
         q_mean = unica.rope_stats(q[:, :1], None, 512)[0].cpu() if args.mode == "fast" else None
         emu = (oracle.attention_fast(qs, ks, vs, 512, recip=True, k_mean=k_mean, q_mean=q_mean, q_count=rows) if args.mode == "fast" else
-               oracle.attention_accurate(qs, ks, vs, oracle.V_TOKEN if args.mode == "per_token" else oracle.V_CHANNEL, recip=True,
+               oracle.attention_accurate(qs, ks, vs, {"per_token": oracle.V_TOKEN, "outliers": oracle.V_OUTLIERS}.get(args.mode, oracle.V_CHANNEL), recip=True,
                                          k_mean=k_mean, q_count=rows))
         # this library's launches per call: statistics (2 per pass), quantizers, (outer scales, smoothing term), attention
-        launches_per_step = {"per_channel": 8, "per_token": 6, "fast": 13}[args.mode]
+        launches_per_step = {"per_channel": 8, "per_token": 6, "outliers": 8, "fast": 13}[args.mode]
         kernel_name = "attention_fp4_kernel" if args.mode == "fast" else "attention_int8_kernel"
         # bytes the quantization passes must move per head and token: bf16 read of Q, K, V + the operands written
-        written = {"per_channel": 3 * 128, "per_token": 3 * 128 + 8, "fast": 72 + 72 + 82}[args.mode]
-        reads = {"per_channel": 5 * 256, "per_token": 4 * 256, "fast": 7 * 256}[args.mode]  # statistics passes read again
+        written = {"per_channel": 3 * 128, "per_token": 3 * 128 + 8, "outliers": 3 * 128, "fast": 72 + 72 + 82}[args.mode]
+        reads = {"per_channel": 5 * 256, "per_token": 4 * 256, "outliers": 6 * 256, "fast": 7 * 256}[args.mode]  # statistics passes read again
         # DRAM traffic of the attention kernel per launch: ncu on 40 heads x 8192 tokens (profiles/), scaled by heads x tokens
         traffic = 544.3 * batch * heads * tokens / world if args.mode == "per_channel" else None
         line = {

@@ -48,7 +48,7 @@ enum {
 };
 
 /* V scale modes of the accurate kernel (the reference's V_TOKEN / V_OUTLIERS build settings, unica/__init__.py:88-89) */
-enum { UNICA_B200_V_CHANNEL = 0, UNICA_B200_V_TOKEN = 1 };
+enum { UNICA_B200_V_CHANNEL = 0, UNICA_B200_V_TOKEN = 1, UNICA_B200_V_OUTLIERS = 2 };
 
 const char* unica_b200_last_error(void);
 int unica_b200_version(void);
@@ -59,6 +59,12 @@ int unica_b200_version(void);
  * fixed order, so results do not depend on how many heads a call holds. */
 int unica_b200_channel_stats(const void* x, unica_token_layout layout, int heads, int n_tokens, int per, float* partial,
                              float* mean, float* low, float* high, void* stream);
+
+/* unica_b200_channel_stats over the whole head without the tokens whose byte in skip [heads][n_tokens] is 1: min and
+ * max of V without its outlier keys (the second pass of v_outliers, unica/__init__.py:384-399).  The mean divides by
+ * n_tokens and is of no use here. */
+int unica_b200_channel_stats_masked(const void* x, unica_token_layout layout, const uint8_t* skip, int heads, int n_tokens,
+                                    float* partial, float* mean, float* low, float* high, void* stream);
 
 /* No counterpart in the reference.  unica_b200_channel_stats for callers that cannot provide the `partial` scratch:
  * code running where device memory cannot be had (a hook inside a pipeline that keeps the card full, a C host without
@@ -96,9 +102,14 @@ int unica_b200_quantize_v_int8(const void* v, unica_token_layout layout, const f
  * S = Q8.K8^T on tcgen05 kind::i8, softmax in the log2 domain against each 64-key tile's own maximum, P as u8,
  * P.V8 on kind::i8 (u8 x s8), flushed into a float accumulator with alpha / beta every tile.
  * out: bf16 in out_layout.  scale_log2 = log2(e) / sqrt(128).  status: device int the kernel leaves non-zero if one
- * of its bounded waits gave up (must be 0 on entry), or NULL. */
+ * of its bounded waits gave up (must be 0 on entry), or NULL.
+ * v_mode UNICA_B200_V_OUTLIERS (the reference's V_OUTLIERS, csrc/flash.cu:748-790): V8 per channel with each head's
+ * n_outliers (<= 8) outlier keys written as zeros; their share of P.V is added exactly at the end from outlier_keys
+ * int [heads][n_outliers] (-1: none) and outlier_rows float [heads][n_outliers][128] = their V rows over v_scale.
+ * Both are NULL / 0 in the other modes. */
 int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
-                              const int8_t* v8, const float* v_scale, const float* v_token, int v_mode, void* out,
+                              const int8_t* v8, const float* v_scale, const float* v_token, int v_mode,
+                              const int* outlier_keys, const float* outlier_rows, int n_outliers, void* out,
                               unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
                               int* status, void* stream);
 

@@ -13,7 +13,7 @@ from gpu_common import EDGE_SHAPES, out_heads, qkv, rel_l2
 
 pytestmark = pytest.mark.gpu
 FROM_EMULATION = 2e-3
-MODES = {"per_channel": oracle.V_CHANNEL, "per_token": oracle.V_TOKEN}
+MODES = {"per_channel": oracle.V_CHANNEL, "per_token": oracle.V_TOKEN, "outliers": oracle.V_OUTLIERS}
 
 
 def run(q, k, v, preset):
@@ -76,6 +76,7 @@ def test_outlier_tokens_need_the_per_token_scale(golden):
         assert rel_l2(out_heads(out), want) < FROM_EMULATION
         errors[preset] = rel_l2(out_heads(out), ref)
     assert errors["per_token"] < errors["per_channel"] / 2
+    assert errors["outliers"] < errors["per_channel"] / 2  # tests/test_v_outliers.py: the exact add-back does as well
 
 
 def test_layout_dtype_and_pieces():

@@ -76,6 +76,36 @@ def test_v_bit_for_bit(shape):
     assert not got_log[:, n:].any() and not got_inv[:, n:].any()
 
 
+@pytest.mark.parametrize("shape", SHAPES)
+def test_v_without_its_outlier_keys_bit_for_bit(shape):
+    """The outliers scale: the 8 keys with the largest max |v| are zeros in V8 and take no part in the scale
+    (the reference's tests/test_v_outliers.py compares its quantize_v(outliers=8) with its emulator the same way)."""
+    import unicaattention_b200 as unica
+
+    v = randn_bf16(shape, 5, channel_scale=True)
+    n = shape[2]
+    v[:, :, min(3, n - 1)] *= 40  # one key that would own the scale
+    v8, scale, keys, rows = unica.quantize_v(v.cuda(), outliers=8)
+    want_keys = oracle.v_outlier_keys(v, 8)
+    got_keys = keys.cpu().numpy().reshape(-1, 8)
+    assert np.array_equal(np.sort(got_keys, -1), np.sort(want_keys, -1))
+    skip = np.zeros((want_keys.shape[0], n), dtype=np.uint8)
+    for head, head_keys in enumerate(want_keys):
+        skip[head, head_keys[head_keys >= 0]] = 1
+    codes, scales = oracle.quantize_v_channel(v, skip, recip=True)
+    assert np.array_equal(np_heads(scale), scales)
+    assert np.array_equal(np_heads(unica.decode_v8(v8, n)), codes)
+    vf = np_heads(v)
+    for head in range(got_keys.shape[0]):
+        for i, key in enumerate(got_keys[head]):
+            want = vf[head, key] / scales[head] if key >= 0 else np.zeros(128, dtype=np.float32)
+            assert np.array_equal(rows.cpu().numpy().reshape(-1, 8, 128)[head, i], want.astype(np.float32))
+    with pytest.raises(ValueError):
+        unica.quantize_v(v.cuda(), outliers=9)
+    with pytest.raises(ValueError):
+        unica.quantize_v(v.cuda(), per_token=True, outliers=8)
+
+
 def test_strided_layout_is_read_in_place():
     """[batch, tokens, heads, 128] seen as [batch, heads, tokens, 128] (ComfyUI's layout) gives the same bytes
     (the reference's tests/test_attention.py:273-284, tests/test_v_token.py:62-68)."""

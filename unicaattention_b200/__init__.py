@@ -35,6 +35,7 @@ KEYS_PER_TILE = 64
 V8_PAD_KEYS = 64  # V8 is padded to whole tiles
 FP4_TILE = 64
 STATS_TOKENS = 256
+MAX_OUTLIERS = 8  # outlier keys per head the accurate kernel adds back
 LOG2E = 1.4426950408889634
 
 # The two production modes, under the reference's kernel names (unica/__init__.py:34-40, 88-89).
@@ -196,23 +197,50 @@ def quantize_v(v: torch.Tensor, layout: int = 2, per_token: bool = False, outlie
     tokens, float32 [batch, heads, 128].  per_token: one scale per token over its channels; returns v8, a scale of ones
     and float32 [batch, heads, tiles, 2, 64] = log2 s then 1 / s of each tile's keys (zeros past N).
     v8: int8 [batch, heads, tiles, 4, 128, 16] (tile, 16-key chunk, channel, key: the K-major operand of P.V);
-    `decode_v8` gives [batch, heads, N, 128].  `layout` is accepted for compatibility: there is one layout here."""
-    if outliers:
-        raise NotImplementedError("outliers= (V_OUTLIERS) is not built yet in the B200 library")
+    `decode_v8` gives [batch, heads, N, 128].  `layout` is accepted for compatibility: there is one layout here.
+    outliers: the per-channel scale without the `outliers` (<= 8) keys of each head with the largest max |v|, which are
+    written as zeros; returns v8, scale, those keys (int32 [batch, heads, outliers], -1: none) and their rows over the
+    scale (float32 [batch, heads, outliers, 128]) for the kernel to add exactly."""
+    if outliers and per_token:
+        raise ValueError("per_token and outliers are two different V scales: pick one")
+    if not 0 <= outliers <= MAX_OUTLIERS:
+        raise ValueError(f"outliers must be in 0..{MAX_OUTLIERS}, got {outliers}")
     _check_input(v, "v")
     v = readable(v)
     batch, heads, n, _ = v.shape
     tiles = math.ceil(n / V8_PAD_KEYS)
     v8 = torch.empty(batch, heads, tiles, 4, HEAD_DIM, 16, dtype=torch.int8, device=v.device)
     scale = torch.empty(batch, heads, HEAD_DIM, device=v.device)
-    low = high = tokens = None
+    low = high = tokens = skip = None
     if per_token:
         tokens = torch.empty(batch, heads, tiles, 2, V8_PAD_KEYS, device=v.device)
+    elif outliers:
+        keys = v_outliers(v, outliers)
+        skip = torch.zeros(batch, heads, n, dtype=torch.uint8, device=v.device).scatter_(-1, keys, 1)
+        partial = torch.empty(batch * heads, math.ceil(n / STATS_TOKENS), 3, HEAD_DIM, device=v.device)
+        _, low, high = (torch.empty(batch, heads, HEAD_DIM, device=v.device) for _ in range(3))
+        lib.call("unica_b200_channel_stats_masked", lib.ptr(v), token_layout(v), lib.ptr(skip), batch * heads, n,
+                 lib.ptr(partial), lib.ptr(_), lib.ptr(low), lib.ptr(high), lib.stream())
     else:
         _, low, high = _stats(v, 0)
-    lib.call("unica_b200_quantize_v_int8", lib.ptr(v), token_layout(v), lib.ptr(low), lib.ptr(high), lib.ptr(None),
+    lib.call("unica_b200_quantize_v_int8", lib.ptr(v), token_layout(v), lib.ptr(low), lib.ptr(high), lib.ptr(skip),
              int(per_token), batch * heads, n, lib.ptr(v8), lib.ptr(scale), lib.ptr(tokens), lib.stream())
-    return (v8, scale, tokens) if per_token else (v8, scale)
+    if per_token:
+        return v8, scale, tokens
+    if outliers:
+        rows = v.gather(-2, keys[..., None].expand(-1, -1, -1, HEAD_DIM)).float() / scale[..., None, :]
+        missing = outliers - keys.shape[-1]  # fewer keys than outliers: the rest are none (-1) and zeros
+        keys = torch.nn.functional.pad(keys, (0, missing), value=-1)
+        rows = torch.nn.functional.pad(rows, (0, 0, 0, missing))
+        return v8, scale, keys.int().contiguous(), rows.contiguous()
+    return v8, scale
+
+
+def v_outliers(v: torch.Tensor, count: int) -> torch.Tensor:
+    """The `count` keys of each head with the largest max |v|, int64 [batch, heads, min(count, N)]
+    (unica/__init__.py:384-390; the scale of the other keys comes from unica_b200_channel_stats_masked)."""
+    low, high = torch.aminmax(v, dim=-1)  # per token, no copy of v
+    return torch.maximum(high, -low).float().topk(min(count, v.shape[-2]), -1).indices
 
 
 def decode_v8(v8: torch.Tensor, n: int) -> torch.Tensor:
@@ -257,7 +285,8 @@ def kernel_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str
         v8, v_scale, v_token = quantize_v(v, per_token=True)
         return q8, q_scale, k8, k_scale, v8, v_scale, v_token, lib.V_TOKEN
     if settings["V_OUTLIERS"]:
-        raise NotImplementedError("V_OUTLIERS is not built yet in the B200 library")
+        v8, v_scale, keys, rows = quantize_v(v, outliers=settings["V_OUTLIERS"])
+        return q8, q_scale, k8, k_scale, v8, v_scale, (keys, rows), lib.V_OUTLIERS
     v8, v_scale = quantize_v(v)
     return q8, q_scale, k8, k_scale, v8, v_scale, None, lib.V_CHANNEL
 
@@ -313,8 +342,10 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
                  lib.ptr(status_word(q.device)), lib.stream())
         return out
     q8, q_scale, k8, k_scale, v8, v_scale, v_token, v_mode = inputs
+    keys, rows = v_token if v_mode == lib.V_OUTLIERS else (None, None)
     lib.call("unica_b200_attention_int8", lib.ptr(q8), lib.ptr(q_scale), lib.ptr(k8), lib.ptr(k_scale), lib.ptr(v8),
-             lib.ptr(v_scale), lib.ptr(v_token), v_mode, lib.ptr(out), token_layout(out), batch * heads, n_queries,
+             lib.ptr(v_scale), lib.ptr(v_token if v_mode == lib.V_TOKEN else None), v_mode, lib.ptr(keys), lib.ptr(rows),
+             0 if keys is None else keys.shape[-1], lib.ptr(out), token_layout(out), batch * heads, n_queries,
              n_keys, HEAD_DIM**-0.5 * LOG2E, lib.ptr(status_word(q.device)), lib.stream())
     del settings
     return out

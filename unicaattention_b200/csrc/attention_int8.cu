@@ -77,15 +77,16 @@ enum { TR_WAIT_S = 0, TR_LOAD_S = 1, TR_SOFTMAX = 2, TR_STORE_P = 3, TR_WAIT_PV 
 constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
 constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM);
 
-template <bool V_TOKEN>
+template <bool V_TOKEN, bool OUTLIERS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attention_int8_kernel(const int8_t* __restrict__ q8, const float* __restrict__ q_scale, const int8_t* __restrict__ k8,
                           const float* __restrict__ k_scale, const int8_t* __restrict__ v8, const float* __restrict__ v_scale,
-                          const float* __restrict__ v_token, __nv_bfloat16* __restrict__ out, TokenLayout out_layout,
-                          int n_queries, int n_keys, float scale_log2, int* status) {
+                          const float* __restrict__ v_token, const int* __restrict__ outlier_keys,
+                          const float* __restrict__ outlier_rows, int n_outliers, __nv_bfloat16* __restrict__ out,
+                          TokenLayout out_layout, int n_queries, int n_keys, float scale_log2, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     AttSmem& sm = *reinterpret_cast<AttSmem*>(smem_raw);
-    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int warp = threadIdx.x / 32;
     const int head = blockIdx.y;
     const int q_tiles = 2 * gridDim.x;  // allocated Q tiles per head (even)
     const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
@@ -441,6 +442,34 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         }
         TRACE_END(g);
 
+        if constexpr (OUTLIERS) {
+            // The outlier keys were zeros in V8: their exact share p * v / v_scale, with p = 255 * 2^(score - final max),
+            // from this row's Q^ (still in shared memory) and the key's K^ row and scale (csrc/flash.cu:748-790).
+            if (ok) ok = mbar_wait_warp(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE);
+            if (ok) {
+                const uint4* q_row8 = reinterpret_cast<const uint4*>(sm.q[g] + row * 16);  // chunk c: QUERY_TILE uint4 further
+                for (int i = 0; i < n_outliers; ++i) {
+                    const int key = outlier_keys[size_t(head) * n_outliers + i];
+                    if (key < 0 || key >= n_keys) continue;
+                    const uint4* k_row8 = reinterpret_cast<const uint4*>(k8 + (size_t(head) * k_tiles + key / KEY_TILE) * K_BYTES + (key % KEY_TILE) * 16);
+                    int dot = 0;
+#pragma unroll
+                    for (int c = 0; c < HEAD_DIM / 16; ++c) {
+                        const uint4 qv = q_row8[c * QUERY_TILE], kv = k_row8[c * KEY_TILE];
+                        dot = __dp4a(int(qv.x), int(kv.x), dot);
+                        dot = __dp4a(int(qv.y), int(kv.y), dot);
+                        dot = __dp4a(int(qv.z), int(kv.z), dot);
+                        dot = __dp4a(int(qv.w), int(kv.w), dot);
+                    }
+                    const float p = ex2(__int2float_rn(dot) * ((sq * sk[key / KEY_TILE]) * scale_log2) - m) * 255.0f;
+                    const float2 p2 = make_float2(p, p);
+                    const float2* v_row = reinterpret_cast<const float2*>(outlier_rows + (size_t(head) * n_outliers + i) * HEAD_DIM);
+#pragma unroll
+                    for (int j = 0; j < HEAD_DIM / 2; ++j) o[j] = fma2(p2, v_row[j], o[j]);
+                }
+            }
+        }
+
         if (ok && q_row < n_queries) {
             const float inv = 1.0f / den;
             __nv_bfloat16* dst = out + out_layout.offset(head, q_row);
@@ -533,13 +562,17 @@ __global__ void __launch_bounds__(128) selftest_mma_i8_kernel(const uint8_t* __r
 using namespace unica;
 
 extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
-                                         const int8_t* v8, const float* v_scale, const float* v_token, int v_mode, void* out,
+                                         const int8_t* v8, const float* v_scale, const float* v_token, int v_mode,
+                                         const int* outlier_keys, const float* outlier_rows, int n_outliers, void* out,
                                          unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
                                          int* status, void* stream) {
     if (!q8 || !q_scale || !k8 || !k_scale || !v8 || !v_scale || !out) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: null pointer");
     if (heads <= 0 || heads > 65535 || n_queries <= 0 || n_keys <= 0)
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: heads must be in 1..65535, n_queries and n_keys positive");
-    if (v_mode != UNICA_B200_V_CHANNEL && v_mode != UNICA_B200_V_TOKEN) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: unknown v_mode");
+    if (v_mode != UNICA_B200_V_CHANNEL && v_mode != UNICA_B200_V_TOKEN && v_mode != UNICA_B200_V_OUTLIERS)
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: unknown v_mode");
+    if (v_mode == UNICA_B200_V_OUTLIERS && (!outlier_keys || !outlier_rows || n_outliers < 1 || n_outliers > 8))
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: the outliers mode needs outlier_keys, outlier_rows and 1..8 outliers");
     if (v_mode == UNICA_B200_V_TOKEN && !v_token) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: per-token mode needs v_token");
     if (int e = unica_check_device()) return e;
     const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE), heads);
@@ -548,11 +581,14 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
     auto launch = [&](auto kernel) -> int {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
             return unica_check_launch("attention_int8 (shared memory size)");
-        kernel<<<grid, ATT_THREADS, smem, s>>>(q8, q_scale, k8, k_scale, v8, v_scale, v_token, static_cast<__nv_bfloat16*>(out),
-                                               to_layout(out_layout), n_queries, n_keys, scale_log2, status);
+        kernel<<<grid, ATT_THREADS, smem, s>>>(q8, q_scale, k8, k_scale, v8, v_scale, v_token, outlier_keys, outlier_rows, n_outliers,
+                                               static_cast<__nv_bfloat16*>(out), to_layout(out_layout), n_queries, n_keys, scale_log2,
+                                               status);
         return unica_check_launch("attention_int8");
     };
-    return v_mode == UNICA_B200_V_TOKEN ? launch(attention_int8_kernel<true>) : launch(attention_int8_kernel<false>);
+    return v_mode == UNICA_B200_V_TOKEN      ? launch(attention_int8_kernel<true, false>)
+           : v_mode == UNICA_B200_V_OUTLIERS ? launch(attention_int8_kernel<false, true>)
+                                             : launch(attention_int8_kernel<false, false>);
 }
 
 #ifdef UNICA_TRACE

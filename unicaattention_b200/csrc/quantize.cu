@@ -28,8 +28,10 @@ __device__ __forceinline__ void load8(float (&v)[8], const __nv_bfloat16* src) {
 // Sum, min and max per channel over a block of 256 tokens of one head (the reference's rope_stats, csrc/flash.cu:287-327,
 // without RoPE): thread = (lane of 16 tokens, chunk of 8 channels); lane l adds tokens l, l + 16, ... in order, then
 // the 16 lanes are added in order.  partial: [heads][blocks][3][128].  Grid (blocks, heads).
+// skip: [heads][n_tokens] bytes, 1 = the token takes no part (the outlier keys of V), or null.
 __global__ void __launch_bounds__(THREADS) channel_stats_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
-                                                                 int n_tokens, float* __restrict__ partial) {
+                                                                 int n_tokens, float* __restrict__ partial,
+                                                                 const uint8_t* __restrict__ skip = nullptr) {
     const int chunk = threadIdx.x % 16, lane = threadIdx.x / 16;
     const int head = blockIdx.y, token0 = blockIdx.x * STATS_TOKENS;
     float sum[8], low[8], high[8];
@@ -38,6 +40,7 @@ __global__ void __launch_bounds__(THREADS) channel_stats_kernel(const __nv_bfloa
     const int end = min(token0 + STATS_TOKENS, n_tokens);
 #pragma unroll 4
     for (int token = token0 + lane; token < end; token += STATS_LANES) {
+        if (skip && skip[size_t(head) * n_tokens + token]) continue;
         float v[8];
         load8(v, x + in.offset(head, token) + chunk * 8);
 #pragma unroll
@@ -307,6 +310,17 @@ extern "C" int unica_b200_channel_stats_static(const void* x, unica_token_layout
     channel_stats_kernel<<<dim3(blocks, heads), THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(x), to_layout(layout), n_tokens, partial);
     channel_stats_finish_kernel<<<dim3(groups, heads), HEAD_DIM, 0, s>>>(partial, blocks, per_group, n_tokens, mean, low, high);
     return unica_check_launch("channel_stats_static");
+}
+
+extern "C" int unica_b200_channel_stats_masked(const void* x, unica_token_layout layout, const uint8_t* skip, int heads, int n_tokens,
+                                               float* partial, float* mean, float* low, float* high, void* stream) {
+    if (!x || !skip || !partial || !mean || !low || !high) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats_masked: null pointer");
+    if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats_masked: heads and n_tokens must be positive");
+    const int blocks = (n_tokens + STATS_TOKENS - 1) / STATS_TOKENS;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    channel_stats_kernel<<<dim3(blocks, heads), THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(x), to_layout(layout), n_tokens, partial, skip);
+    channel_stats_finish_kernel<<<dim3(1, heads), HEAD_DIM, 0, s>>>(partial, blocks, blocks, n_tokens, mean, low, high);
+    return unica_check_launch("channel_stats_masked");
 }
 
 extern "C" int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const float* mean, int heads, int n_tokens,

@@ -20,7 +20,7 @@ import os  # noqa: E402
 LIB_PATH = Path(os.environ["UNICA_B200_LIB"]) if "UNICA_B200_LIB" in os.environ else HERE / "libunica_b200.so"
 
 ERR_ARGUMENT, ERR_CUDA, ERR_DEVICE, ERR_KERNEL = 1, 2, 3, 4
-V_CHANNEL, V_TOKEN = 0, 1
+V_CHANNEL, V_TOKEN, V_OUTLIERS = 0, 1, 2
 
 
 class TokenLayout(ctypes.Structure):
@@ -39,7 +39,8 @@ SIGNATURES = {
     "unica_b200_channel_stats_static": [_P, TokenLayout, _I, _I, _I, _P, _P, _P, _P],
     "unica_b200_quantize_int8": [_P, TokenLayout, _P, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_v_int8": [_P, TokenLayout, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
-    "unica_b200_attention_int8": [_P, _P, _P, _P, _P, _P, _P, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
+    "unica_b200_attention_int8": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
+    "unica_b200_channel_stats_masked": [_P, TokenLayout, _P, _I, _I, _P, _P, _P, _P, _P],
     "unica_b200_selftest_mma_i8": [_P, _P, _I, _I, _I, _I, _P, _P],
     "unica_b200_attention_fp4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
     "unica_b200_selftest_mma_nvf4": [_P, _P, _P, _P, _I, _I, _I, _P, _P],
