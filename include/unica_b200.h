@@ -144,6 +144,26 @@ int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layout, const fl
 int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean, int heads,
                            int q_blocks, int n_keys, float scale_log2, float* bias, void* stream);
 
+/* ---- RoPE inside the quantizers -----------------------------------------------------------------------------------
+ * Replace the reference's `freqs, freqs_batch` kernel arguments (rope_chunk / load_chunk_rope, csrc/flash.cu:250-279;
+ * rope_args, unica/__init__.py:571-577): x is rotated in float before anything else is done with it, so the rotated
+ * tensor is never written.  rope: (cos, sin) per pair of channels in fp16, [batch or 1][n_tokens][64][2];
+ * rope_batch_stride: halves between the tables of two batches, 0 when one table serves all.  out[2i] = c x[2i] - s x[2i+1],
+ * out[2i+1] = s x[2i] + c x[2i+1], products rounded before the sum (bench/emulate.py:122-130).  The other arguments
+ * are those of the entry point without the suffix; a mean passed in is the rotated x's. */
+int unica_b200_channel_stats_rope(const void* x, unica_token_layout layout, const void* rope, long long rope_batch_stride,
+                                  int heads, int n_tokens, int per, float* partial, float* mean, float* low, float* high,
+                                  void* stream);
+int unica_b200_quantize_int8_rope(const void* x, unica_token_layout layout, const float* mean, const void* rope,
+                                  long long rope_batch_stride, int heads, int n_tokens, int block_tokens, int tiles,
+                                  int8_t* codes, float* scales, void* stream);
+int unica_b200_quantize_fp4_rows_rope(const void* x, unica_token_layout layout, const float* mean, int mean_tokens,
+                                      const void* rope, long long rope_batch_stride, const float* outer, int heads,
+                                      int n_tokens, int rows_per_tile, int tiles, uint8_t* codes, uint8_t* sf, void* stream);
+int unica_b200_smooth_bias_rope(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
+                                const void* rope, long long rope_batch_stride, int heads, int q_blocks, int n_keys,
+                                float scale_log2, float* bias, void* stream);
+
 /* Hardware self-test of the tensor-core path (the idea of the reference's tests/test_mma.py: small integers make every
  * result exact, so a wrong lane or layout cannot hide).  One tcgen05.mma kind::i8 chain D[128 x n] = A[128 x k] . B[n x k]^T
  * with A (u8 if a_unsigned, else s8) and B (s8) given as the shared-memory images described above

@@ -91,28 +91,68 @@ def _f32(a, shape=None):
     return a if shape is None else a.reshape(shape)
 
 
+def wan_rope_table(t: int, h: int, w: int, dim: int = D, theta: float = 10000.0) -> np.ndarray:
+    """The RoPE table of a t x h x w video latent as WAN models get it from ComfyUI (axes of 44, 42 and 42 channels for
+    d = 128; the reference's tests use bench/emulate.py:133-143): float32 [1, t * h * w, 1, 64, 2, 2], a rotation
+    [[cos, -sin], [sin, cos]] per pair of channels."""
+    axes = [dim - 4 * (dim // 6), 2 * (dim // 6), 2 * (dim // 6)]
+    ids = np.stack(np.meshgrid(np.arange(t), np.arange(h), np.arange(w), indexing="ij"), -1).reshape(-1, 3)
+    tables = []
+    for axis, size in enumerate(axes):
+        omega = 1.0 / theta ** np.linspace(0, (size - 2) / size, size // 2, dtype=np.float64)
+        angle = ids[:, axis, None].astype(np.float64) * omega  # [tokens, size / 2]
+        tables.append(np.stack([np.cos(angle), -np.sin(angle), np.sin(angle), np.cos(angle)], -1).reshape(-1, size // 2, 2, 2))
+    return np.concatenate(tables, 1).astype(np.float32)[None, :, None]
+
+
+def _rope(rope, heads: int):
+    """(cos, sin) float32 [tables, n, 64, 2] rounded to fp16, and how many heads share a table; (None, 1) without rope.
+    rope: ComfyUI's table [batch or 1, n, 1, 64, 2, 2] (torch or numpy)."""
+    if rope is None:
+        return None, 1
+    if hasattr(rope, "detach"):
+        rope = rope.detach().float().cpu().numpy()
+    rope = np.asarray(rope, dtype=np.float32)
+    compact = np.stack([rope[:, :, 0, :, 0, 0], rope[:, :, 0, :, 1, 0]], -1)  # [tables, n, 64, 2]
+    compact = np.ascontiguousarray(compact.astype(np.float16).astype(np.float32))
+    assert heads % compact.shape[0] == 0
+    return compact, heads // compact.shape[0]
+
+
+def rope_rotate(x, rope) -> np.ndarray:
+    """x rotated in float as the quantizers do it: float32 [heads, n, 128], not rounded to bf16."""
+    x = bf16_bits(x)
+    heads, n, _ = x.shape
+    table, per = _rope(rope, heads)
+    out = np.empty((heads, n, D), np.float32)
+    lib().uo_rope(_p(x), _p(table), per, heads, n, _p(out))
+    return out
+
+
 def slot_key() -> np.ndarray:
     """slot -> key inside a 64-key tile (the fast mode's key order)."""
     return np.array([lib().uo_slot_key(s) for s in range(TILE)], dtype=np.int64)
 
 
-def channel_stats(x, per: int = 0):
+def channel_stats(x, per: int = 0, rope=None):
     """mean, min, max per channel over each group of `per` tokens (0: the head): float32 [heads, groups, 128]."""
     x = bf16_bits(x)
     heads, n, _ = x.shape
     groups = 1 if per <= 0 else -(-n // per)
     mean, low, high = (np.empty((heads, groups, D), np.float32) for _ in range(3))
-    lib().uo_channel_stats(_p(x), heads, n, per, _p(mean), _p(low), _p(high))
+    table, shared = _rope(rope, heads)
+    lib().uo_channel_stats_rope(_p(x), _p(table), shared, heads, n, per, _p(mean), _p(low), _p(high))
     return mean, low, high
 
 
-def quantize_int8(x, mean, block: int, recip: bool = True):
+def quantize_int8(x, mean, block: int, recip: bool = True, rope=None):
     x = bf16_bits(x)
     heads, n, _ = x.shape
     mean = _f32(mean, (heads, D))
     codes = np.empty((heads, n, D), np.int8)
     scales = np.empty((heads, -(-n // block)), np.float32)
-    lib().uo_quantize_int8(_p(x), _p(mean), heads, n, block, int(recip), _p(codes), _p(scales))
+    table, shared = _rope(rope, heads)
+    lib().uo_quantize_int8_rope(_p(x), _p(mean), _p(table), shared, heads, n, block, int(recip), _p(codes), _p(scales))
     return codes, scales
 
 
@@ -144,7 +184,7 @@ def v_outlier_keys(v, count: int):
     return keys
 
 
-def nvfp4_rows(x, mean=None, mean_tokens: int = 0, recip: bool = True):
+def nvfp4_rows(x, mean=None, mean_tokens: int = 0, recip: bool = True, rope=None):
     """codes uint8 [heads, n, 128] (4-bit codes), e4m3 scale bytes [heads, n, 8], outer float32 [heads]."""
     x = bf16_bits(x)
     heads, n, _ = x.shape
@@ -153,7 +193,8 @@ def nvfp4_rows(x, mean=None, mean_tokens: int = 0, recip: bool = True):
     codes = np.empty((heads, n, D), np.uint8)
     sf = np.empty((heads, n, 8), np.uint8)
     outer = np.empty((heads,), np.float32)
-    lib().uo_nvfp4_rows(_p(x), _p(mean), mean_tokens, heads, n, int(recip), _p(codes), _p(sf), _p(outer))
+    table, shared = _rope(rope, heads)
+    lib().uo_nvfp4_rows_rope(_p(x), _p(mean), mean_tokens, _p(table), shared, heads, n, int(recip), _p(codes), _p(sf), _p(outer))
     return codes, sf, outer
 
 
@@ -176,31 +217,33 @@ def _rows(nq, q_first, q_count):
     return q_first, q_count
 
 
-def reference_fp32(q, k, v, q_first: int = 0, q_count: int | None = None) -> np.ndarray:
+def reference_fp32(q, k, v, q_first: int = 0, q_count: int | None = None, rope=None) -> np.ndarray:
     """softmax(q k^T / sqrt(d)) v in float (double accumulation): float32 [heads, q_count, 128], not rounded."""
     q, k, v = bf16_bits(q), bf16_bits(k), bf16_bits(v)
     heads, nq, _ = q.shape
     q_first, q_count = _rows(nq, q_first, q_count)
     out = np.empty((heads, q_count, D), np.float32)
-    lib().uo_reference_fp32(_p(q), _p(k), _p(v), heads, nq, k.shape[1], q_first, q_count, _p(out))
+    table, shared = _rope(rope, heads)
+    lib().uo_reference_fp32_rope(_p(q), _p(k), _p(v), _p(table), shared, heads, nq, k.shape[1], q_first, q_count, _p(out))
     return out
 
 
 def attention_accurate(q, k, v, v_mode: int = V_CHANNEL, outliers: int = 8, recip: bool = True, k_mean=None,
-                       q_first: int = 0, q_count: int | None = None) -> np.ndarray:
+                       q_first: int = 0, q_count: int | None = None, rope=None) -> np.ndarray:
     """The accurate mode's contract; float32 [heads, q_count, 128] already rounded to bf16."""
     q, k, v = bf16_bits(q), bf16_bits(k), bf16_bits(v)
     heads, nq, _ = q.shape
     q_first, q_count = _rows(nq, q_first, q_count)
     k_mean = _f32(k_mean, (heads, D))
     out = np.empty((heads, q_count, D), np.float32)
-    lib().uo_attention_accurate(_p(q), _p(k), _p(v), heads, nq, k.shape[1], v_mode, outliers, int(recip), _p(k_mean),
-                                q_first, q_count, _p(out))
+    table, shared = _rope(rope, heads)
+    lib().uo_attention_accurate_rope(_p(q), _p(k), _p(v), _p(table), shared, heads, nq, k.shape[1], v_mode, outliers, int(recip),
+                                     _p(k_mean), q_first, q_count, _p(out))
     return out
 
 
 def attention_fast(q, k, v, smooth_q: int = 512, recip: bool = True, k_mean=None, q_mean=None, q_first: int = 0,
-                   q_count: int | None = None) -> np.ndarray:
+                   q_count: int | None = None, rope=None) -> np.ndarray:
     """The fast mode's contract; float32 [heads, q_count, 128] already rounded to bf16."""
     q, k, v = bf16_bits(q), bf16_bits(k), bf16_bits(v)
     heads, nq, _ = q.shape
@@ -209,8 +252,9 @@ def attention_fast(q, k, v, smooth_q: int = 512, recip: bool = True, k_mean=None
     if q_mean is not None:
         q_mean = _f32(q_mean, (heads, -(-nq // smooth_q), D))
     out = np.empty((heads, q_count, D), np.float32)
-    lib().uo_attention_fast(_p(q), _p(k), _p(v), heads, nq, k.shape[1], smooth_q, int(recip), _p(k_mean), _p(q_mean),
-                            q_first, q_count, _p(out))
+    table, shared = _rope(rope, heads)
+    lib().uo_attention_fast_rope(_p(q), _p(k), _p(v), _p(table), shared, heads, nq, k.shape[1], smooth_q, int(recip), _p(k_mean),
+                                 _p(q_mean), q_first, q_count, _p(out))
     return out
 
 

@@ -107,6 +107,41 @@ static inline int slot_key(int k) { return 32 * (k / 32) + 8 * (k % 8 / 2) + 2 *
 int uo_slot_key(int slot) { return slot_key(slot); }
 
 /* ------------------------------------------------------------------------------------------------------------ */
+/* RoPE (bench/emulate.py:122-130)                                                                                */
+
+/* x [heads][n][128] bf16 as float, rotated when rope is given: rope float [tables][n][64][2] = (cos, sin) per pair of
+ * channels, already rounded to fp16; head h uses table h / heads_per_table.  out[2i] = c x[2i] - s x[2i+1],
+ * out[2i+1] = s x[2i] + c x[2i+1], each product rounded, then the difference or sum (this file is compiled with
+ * -ffp-contract=off).  The caller frees the result. */
+static float* to_float_rotated(const uint16_t* x, const float* rope, int heads_per_table, int heads, int n) {
+    float* out = (float*)malloc(sizeof(float) * (size_t)heads * n * D);
+#pragma omp parallel for collapse(2) schedule(static)
+    for (int h = 0; h < heads; ++h)
+        for (int t = 0; t < n; ++t) {
+            const uint16_t* src = x + ((size_t)h * n + t) * D;
+            float* dst = out + ((size_t)h * n + t) * D;
+            if (!rope) {
+                for (int c = 0; c < D; ++c) dst[c] = bf16_to_float(src[c]);
+                continue;
+            }
+            const float* f = rope + ((size_t)(h / heads_per_table) * n + t) * D;
+            for (int i = 0; i < D / 2; ++i) {
+                float c = f[2 * i], s = f[2 * i + 1], x0 = bf16_to_float(src[2 * i]), x1 = bf16_to_float(src[2 * i + 1]);
+                float a = c * x0, b = s * x1, d = s * x0, e = c * x1;
+                dst[2 * i] = a - b;
+                dst[2 * i + 1] = d + e;
+            }
+        }
+    return out;
+}
+
+void uo_rope(const uint16_t* x, const float* rope, int heads_per_table, int heads, int n, float* out) {
+    float* r = to_float_rotated(x, rope, heads_per_table, heads, n);
+    memcpy(out, r, sizeof(float) * (size_t)heads * n * D);
+    free(r);
+}
+
+/* ------------------------------------------------------------------------------------------------------------ */
 /* statistics                                                                                                     */
 
 /* Per channel of each head: mean, min and max over each group of `per` tokens (per <= 0: the whole head).
@@ -114,13 +149,13 @@ int uo_slot_key(int slot) { return slot_key(slot); }
  * and the 16 lanes are added in order; the blocks of a group are then added in order and divided by the group's true
  * token count (unica/__init__.py:603-612; torch's own order over the partials is not specified, hence the reference
  * tests' 1e-6).  mean/low/high: [heads][groups][128], groups = ceil(n / per). */
-void uo_channel_stats(const uint16_t* x, int heads, int n, int per, float* mean, float* low, float* high) {
+static void channel_stats_f(const float* x, int heads, int n, int per, float* mean, float* low, float* high) {
     if (per <= 0) per = (n + STATS_TOKENS - 1) / STATS_TOKENS * STATS_TOKENS;
     int groups = (n + per - 1) / per;
 #pragma omp parallel for collapse(2) schedule(static)
     for (int h = 0; h < heads; ++h)
         for (int g = 0; g < groups; ++g) {
-            const uint16_t* xh = x + (size_t)h * n * D;
+            const float* xh = x + (size_t)h * n * D;
             int t0 = g * per, t1 = t0 + per < n ? t0 + per : n;
             float gs[D], glo[D], ghi[D];
             for (int c = 0; c < D; ++c) gs[c] = 0.0f, glo[c] = INFINITY, ghi[c] = -INFINITY;
@@ -133,7 +168,7 @@ void uo_channel_stats(const uint16_t* x, int heads, int n, int per, float* mean,
                     for (int c = 0; c < D; ++c) ls[c] = 0.0f;
                     for (int t = b0 + l; t < b1; t += STATS_LANES)
                         for (int c = 0; c < D; ++c) {
-                            float v = bf16_to_float(xh[(size_t)t * D + c]);
+                            float v = xh[(size_t)t * D + c];
                             ls[c] += v;
                             glo[c] = fminf(glo[c], v);
                             ghi[c] = fmaxf(ghi[c], v);
@@ -151,13 +186,24 @@ void uo_channel_stats(const uint16_t* x, int heads, int n, int per, float* mean,
         }
 }
 
+void uo_channel_stats_rope(const uint16_t* x, const float* rope, int heads_per_table, int heads, int n, int per, float* mean,
+                           float* low, float* high) {
+    float* xf = to_float_rotated(x, rope, heads_per_table, heads, n);
+    channel_stats_f(xf, heads, n, per, mean, low, high);
+    free(xf);
+}
+
+void uo_channel_stats(const uint16_t* x, int heads, int n, int per, float* mean, float* low, float* high) {
+    uo_channel_stats_rope(x, NULL, 1, heads, n, per, mean, low, high);
+}
+
 /* ------------------------------------------------------------------------------------------------------------ */
 /* INT8 quantizers                                                                                                */
 
 /* x - mean ~ code * scale, one scale per `block` tokens over all channels.  mean: [heads][128] or NULL.
  * codes [heads][n][128], scales [heads][ceil(n / block)]. */
-void uo_quantize_int8(const uint16_t* x, const float* mean, int heads, int n, int block, int recip, int8_t* codes,
-                      float* scales) {
+static void quantize_int8_f(const float* x, const float* mean, int heads, int n, int block, int recip, int8_t* codes,
+                            float* scales) {
     int blocks = (n + block - 1) / block;
 #pragma omp parallel for collapse(2) schedule(static)
     for (int h = 0; h < heads; ++h)
@@ -167,17 +213,29 @@ void uo_quantize_int8(const uint16_t* x, const float* mean, int heads, int n, in
             float amax = 0.0f;
             for (int t = t0; t < t1; ++t)
                 for (int c = 0; c < D; ++c) {
-                    float v = bf16_to_float(x[((size_t)h * n + t) * D + c]) - (mu ? mu[c] : 0.0f);
+                    float v = x[((size_t)h * n + t) * D + c] - (mu ? mu[c] : 0.0f);
                     amax = fmaxf(amax, fabsf(v));
                 }
             float s = fmaxf(scalar_div(amax, 127.0f, recip), 1e-12f);
             scales[(size_t)h * blocks + b] = s;
             for (int t = t0; t < t1; ++t)
                 for (int c = 0; c < D; ++c) {
-                    float v = bf16_to_float(x[((size_t)h * n + t) * D + c]) - (mu ? mu[c] : 0.0f);
+                    float v = x[((size_t)h * n + t) * D + c] - (mu ? mu[c] : 0.0f);
                     codes[((size_t)h * n + t) * D + c] = (int8_t)fminf(fmaxf(rintf(v / s), -127.0f), 127.0f);
                 }
         }
+}
+
+void uo_quantize_int8_rope(const uint16_t* x, const float* mean, const float* rope, int heads_per_table, int heads, int n,
+                           int block, int recip, int8_t* codes, float* scales) {
+    float* xf = to_float_rotated(x, rope, heads_per_table, heads, n);
+    quantize_int8_f(xf, mean, heads, n, block, recip, codes, scales);
+    free(xf);
+}
+
+void uo_quantize_int8(const uint16_t* x, const float* mean, int heads, int n, int block, int recip, int8_t* codes,
+                      float* scales) {
+    uo_quantize_int8_rope(x, mean, NULL, 1, heads, n, block, recip, codes, scales);
 }
 
 /* V with one scale per channel over all tokens of a head.  skip: [heads][n] bytes, 1 = the key is written as zeros
@@ -246,8 +304,8 @@ void uo_v_outlier_keys(const uint16_t* v, int heads, int n, int count, int* keys
 /* x - mean in NVFP4 along the channels: one float `outer` per head, an e4m3 scale per 16 channels, e2m1 codes.
  * mean: [heads][groups][128] (one mean per `mean_tokens` tokens; mean_tokens <= 0: one per head) or NULL.
  * codes [heads][n][128] (4-bit codes, one per byte), sf [heads][n][8] (e4m3 bytes), outer [heads]. */
-void uo_nvfp4_rows(const uint16_t* x, const float* mean, int mean_tokens, int heads, int n, int recip, uint8_t* codes,
-                   uint8_t* sf, float* outer) {
+static void nvfp4_rows_f(const float* x, const float* mean, int mean_tokens, int heads, int n, int recip, uint8_t* codes,
+                         uint8_t* sf, float* outer) {
     if (mean_tokens <= 0) mean_tokens = n;
     int groups = (n + mean_tokens - 1) / mean_tokens;
 #pragma omp parallel for schedule(static)
@@ -256,7 +314,7 @@ void uo_nvfp4_rows(const uint16_t* x, const float* mean, int mean_tokens, int he
         for (int t = 0; t < n; ++t) {
             const float* mu = mean ? mean + ((size_t)h * groups + t / mean_tokens) * D : NULL;
             for (int c = 0; c < D; ++c)
-                amax = fmaxf(amax, fabsf(bf16_to_float(x[((size_t)h * n + t) * D + c]) - (mu ? mu[c] : 0.0f)));
+                amax = fmaxf(amax, fabsf(x[((size_t)h * n + t) * D + c] - (mu ? mu[c] : 0.0f)));
         }
         float o = fmaxf(scalar_div(amax, 6.0f * 448.0f, recip), 1e-30f);
         outer[h] = o;
@@ -266,7 +324,7 @@ void uo_nvfp4_rows(const uint16_t* x, const float* mean, int mean_tokens, int he
                 float val[16], a16 = 0.0f;
                 for (int i = 0; i < 16; ++i) {
                     int c = 16 * b + i;
-                    val[i] = bf16_to_float(x[((size_t)h * n + t) * D + c]) - (mu ? mu[c] : 0.0f);
+                    val[i] = x[((size_t)h * n + t) * D + c] - (mu ? mu[c] : 0.0f);
                     a16 = fmaxf(a16, fabsf(val[i]));
                 }
                 uint8_t byte = float_to_e4m3(fminf(scalar_div(a16, 6.0f, recip) / o, 448.0f));
@@ -277,6 +335,18 @@ void uo_nvfp4_rows(const uint16_t* x, const float* mean, int mean_tokens, int he
             }
         }
     }
+}
+
+void uo_nvfp4_rows_rope(const uint16_t* x, const float* mean, int mean_tokens, const float* rope, int heads_per_table,
+                        int heads, int n, int recip, uint8_t* codes, uint8_t* sf, float* outer) {
+    float* xf = to_float_rotated(x, rope, heads_per_table, heads, n);
+    nvfp4_rows_f(xf, mean, mean_tokens, heads, n, recip, codes, sf, outer);
+    free(xf);
+}
+
+void uo_nvfp4_rows(const uint16_t* x, const float* mean, int mean_tokens, int heads, int n, int recip, uint8_t* codes,
+                   uint8_t* sf, float* outer) {
+    uo_nvfp4_rows_rope(x, mean, mean_tokens, NULL, 1, heads, n, recip, codes, sf, outer);
 }
 
 /* V in NVFP4 along the keys, per channel: outer [heads][128] = max|v| / (6 * 448); inside each tile of 64 keys the
@@ -314,23 +384,23 @@ void uo_nvfp4_v(const uint16_t* v, int heads, int n, int recip, uint8_t* codes, 
 /* ------------------------------------------------------------------------------------------------------------ */
 /* FP32 reference                                                                                                 */
 
-void uo_reference_fp32(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk,
-                       int q_first, int q_count, float* out) {
+void uo_reference_fp32_rope(const uint16_t* q, const uint16_t* k, const uint16_t* v, const float* rope, int heads_per_table,
+                            int heads, int nq, int nk, int q_first, int q_count, float* out) {
     const float scale = 1.0f / sqrtf((float)D);
+    float* q_rot = to_float_rotated(q, rope, heads_per_table, heads, nq);
+    float* k_rot = to_float_rotated(k, rope, heads_per_table, heads, nk);
 #pragma omp parallel
     {
         float* s = (float*)malloc(sizeof(float) * (size_t)nk);
 #pragma omp for collapse(2) schedule(dynamic, 16)
         for (int h = 0; h < heads; ++h)
             for (int r = 0; r < q_count; ++r) {
-                const uint16_t* qr = q + ((size_t)h * nq + q_first + r) * D;
-                float qf[D];
-                for (int c = 0; c < D; ++c) qf[c] = bf16_to_float(qr[c]);
+                const float* qf = q_rot + ((size_t)h * nq + q_first + r) * D;
                 float m = -INFINITY;
                 for (int j = 0; j < nk; ++j) {
-                    const uint16_t* kr = k + ((size_t)h * nk + j) * D;
+                    const float* kr = k_rot + ((size_t)h * nk + j) * D;
                     float dot = 0.0f;
-                    for (int c = 0; c < D; ++c) dot += qf[c] * bf16_to_float(kr[c]);
+                    for (int c = 0; c < D; ++c) dot += qf[c] * kr[c];
                     s[j] = dot * scale;
                     m = fmaxf(m, s[j]);
                 }
@@ -348,6 +418,13 @@ void uo_reference_fp32(const uint16_t* q, const uint16_t* k, const uint16_t* v, 
             }
         free(s);
     }
+    free(q_rot);
+    free(k_rot);
+}
+
+void uo_reference_fp32(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk,
+                       int q_first, int q_count, float* out) {
+    uo_reference_fp32_rope(q, k, v, NULL, 1, heads, nq, nk, q_first, q_count, out);
 }
 
 /* ------------------------------------------------------------------------------------------------------------ */
@@ -358,9 +435,9 @@ enum { UO_V_CHANNEL = 0, UO_V_TOKEN = 1, UO_V_OUTLIERS = 2 };
 /* Rows [q_first, q_first + q_count) of every head.  k_mean: [heads][128], or NULL to take uo_channel_stats's.
  * out: float [heads][q_count][128], already rounded to bf16 (bench/emulate.py:369).  Statistics (K mean, every
  * scale) come from the whole head whatever the row range, as in one whole call. */
-void uo_attention_accurate(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk,
-                           int v_mode, int n_outliers, int recip, const float* k_mean, int q_first, int q_count,
-                           float* out) {
+void uo_attention_accurate_rope(const uint16_t* q, const uint16_t* k, const uint16_t* v, const float* rope, int heads_per_table,
+                                int heads, int nq, int nk, int v_mode, int n_outliers, int recip, const float* k_mean,
+                                int q_first, int q_count, float* out) {
     const float scale = (float)(1.0 / sqrt((double)D) * LOG2E); /* python double, then float32 tensor multiply */
     int q_blocks = (nq + 127) / 128, k_blocks = (nk + TILE - 1) / TILE;
     float* mean = (float*)malloc(sizeof(float) * (size_t)heads * D);
@@ -368,7 +445,7 @@ void uo_attention_accurate(const uint16_t* q, const uint16_t* k, const uint16_t*
         memcpy(mean, k_mean, sizeof(float) * (size_t)heads * D);
     else {
         float* lo = (float*)malloc(sizeof(float) * (size_t)heads * D * 2);
-        uo_channel_stats(k, heads, nk, 0, mean, lo, lo + (size_t)heads * D);
+        uo_channel_stats_rope(k, rope, heads_per_table, heads, nk, 0, mean, lo, lo + (size_t)heads * D);
         free(lo);
     }
     int8_t* q8 = (int8_t*)malloc((size_t)heads * nq * D);
@@ -380,8 +457,8 @@ void uo_attention_accurate(const uint16_t* q, const uint16_t* k, const uint16_t*
     float *s_tok = NULL, *log_s = NULL, *inv_s = NULL;
     uint8_t* skip = NULL;
     int* okeys = NULL;
-    uo_quantize_int8(q, NULL, heads, nq, 128, recip, q8, sq);
-    uo_quantize_int8(k, mean, heads, nk, TILE, recip, k8, sk);
+    uo_quantize_int8_rope(q, NULL, rope, heads_per_table, heads, nq, 128, recip, q8, sq);
+    uo_quantize_int8_rope(k, mean, rope, heads_per_table, heads, nk, TILE, recip, k8, sk);
     if (v_mode == UO_V_TOKEN) {
         s_tok = (float*)malloc(sizeof(float) * (size_t)heads * nk * 3);
         log_s = s_tok + (size_t)heads * nk;
@@ -456,16 +533,24 @@ void uo_attention_accurate(const uint16_t* q, const uint16_t* k, const uint16_t*
     free(mean); free(q8); free(k8); free(v8); free(sq); free(sk); free(sv); free(s_tok); free(skip); free(okeys);
 }
 
+void uo_attention_accurate(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk,
+                           int v_mode, int n_outliers, int recip, const float* k_mean, int q_first, int q_count,
+                           float* out) {
+    uo_attention_accurate_rope(q, k, v, NULL, 1, heads, nq, nk, v_mode, n_outliers, recip, k_mean, q_first, q_count, out);
+}
+
 /* ------------------------------------------------------------------------------------------------------------ */
 /* fast mode                                                                                                      */
 
 /* NVFP4 Q.K^T and P.V, Q mean-smoothed per `smooth_q` queries (0: no smoothing), keys in slot order, P in NVFP4
  * with outer scale 1 against p_mul = 1024.  k_mean [heads][128] / q_mean [heads][ceil(nq / smooth_q)][128] or NULL
  * (then uo_channel_stats's). */
-void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk, int smooth_q,
-                       int recip, const float* k_mean, const float* q_mean, int q_first, int q_count, float* out) {
+void uo_attention_fast_rope(const uint16_t* q, const uint16_t* k, const uint16_t* v, const float* rope, int heads_per_table,
+                            int heads, int nq, int nk, int smooth_q, int recip, const float* k_mean, const float* q_mean,
+                            int q_first, int q_count, float* out) {
     const float scale = (float)(1.0 / sqrt((double)D) * LOG2E);
     const float p_mul = 1024.0f;
+    float* k_rot = to_float_rotated(k, rope, heads_per_table, heads, nk); /* the smoothing term takes k in float */
     int tiles = (nk + TILE - 1) / TILE, npad = tiles * TILE;
     int q_groups = smooth_q ? (nq + smooth_q - 1) / smooth_q : 1;
     float* kmean = (float*)malloc(sizeof(float) * (size_t)heads * D);
@@ -474,7 +559,7 @@ void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, 
         memcpy(kmean, k_mean, sizeof(float) * (size_t)heads * D);
     else {
         float* lo = (float*)malloc(sizeof(float) * (size_t)heads * D * 2);
-        uo_channel_stats(k, heads, nk, 0, kmean, lo, lo + (size_t)heads * D);
+        uo_channel_stats_rope(k, rope, heads_per_table, heads, nk, 0, kmean, lo, lo + (size_t)heads * D);
         free(lo);
     }
     float* qmean = NULL;
@@ -483,7 +568,7 @@ void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, 
         if (q_mean)
             memcpy(qmean, q_mean, sizeof(float) * (size_t)heads * q_groups * D);
         else
-            uo_channel_stats(q, heads, nq, smooth_q, qmean, scratch, scratch + (size_t)heads * q_groups * D);
+            uo_channel_stats_rope(q, rope, heads_per_table, heads, nq, smooth_q, qmean, scratch, scratch + (size_t)heads * q_groups * D);
     }
     uint8_t* qc = (uint8_t*)malloc((size_t)heads * nq * D);
     uint8_t* kc = (uint8_t*)malloc((size_t)heads * nk * D);
@@ -494,8 +579,8 @@ void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, 
     float* qo = (float*)malloc(sizeof(float) * heads);
     float* ko = (float*)malloc(sizeof(float) * heads);
     float* vo = (float*)malloc(sizeof(float) * (size_t)heads * D);
-    uo_nvfp4_rows(q, qmean, smooth_q, heads, nq, recip, qc, qsf, qo);
-    uo_nvfp4_rows(k, kmean, 0, heads, nk, recip, kc, ksf, ko);
+    uo_nvfp4_rows_rope(q, qmean, smooth_q, rope, heads_per_table, heads, nq, recip, qc, qsf, qo);
+    uo_nvfp4_rows_rope(k, kmean, 0, rope, heads_per_table, heads, nk, recip, kc, ksf, ko);
     uo_nvfp4_v(v, heads, nk, recip, vc, vsf, vo);
     /* dequantized K (x^ * s) and V, and the exact centred K for the smoothing term */
     float* kd = (float*)malloc(sizeof(float) * (size_t)heads * nk * D);
@@ -541,7 +626,7 @@ void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, 
                     s[slot] = dot * scale;
                     if (smooth_q) { /* q_mean . (k - k_mean), unquantized (bench/emulate.py:308-309) */
                         for (int c = 0; c < D; ++c)
-                            bias += qbar[c] * (bf16_to_float(k[((size_t)h * nk + key) * D + c]) - kmean[(size_t)h * D + c]);
+                            bias += qbar[c] * (k_rot[((size_t)h * nk + key) * D + c] - kmean[(size_t)h * D + c]);
                         s[slot] += bias * scale;
                     }
                     m_new = fmaxf(m_new, s[slot]);
@@ -573,5 +658,10 @@ void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, 
             for (int c = 0; c < D; ++c) dst[c] = round_bf16(o[c] * (1.0f / p_mul) / den);
         }
     free(kmean); free(scratch); free(qmean); free(qc); free(kc); free(vc); free(qsf); free(ksf); free(vsf);
-    free(qo); free(ko); free(vo); free(kd); free(vd);
+    free(qo); free(ko); free(vo); free(kd); free(vd); free(k_rot);
+}
+
+void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk, int smooth_q,
+                       int recip, const float* k_mean, const float* q_mean, int q_first, int q_count, float* out) {
+    uo_attention_fast_rope(q, k, v, NULL, 1, heads, nq, nk, smooth_q, recip, k_mean, q_mean, q_first, q_count, out);
 }

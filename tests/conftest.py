@@ -19,3 +19,10 @@ def golden():
     import numpy as np
 
     return np.load(ROOT / "tests" / "golden" / "golden.npz")
+
+
+@pytest.fixture(scope="session")
+def golden_rope():
+    import numpy as np
+
+    return np.load(ROOT / "tests" / "golden" / "golden_rope.npz")

@@ -21,6 +21,7 @@ import functools
 import math
 import os
 import warnings
+import weakref
 
 import torch
 
@@ -35,6 +36,7 @@ KEYS_PER_TILE = 64
 V8_PAD_KEYS = 64  # V8 is padded to whole tiles
 FP4_TILE = 64
 STATS_TOKENS = 256
+ROPE_PAIRS = HEAD_DIM // 2
 MAX_OUTLIERS = 8  # outlier keys per head the accurate kernel adds back
 LOG2E = 1.4426950408889634
 
@@ -131,14 +133,14 @@ def check_status(device=None) -> None:
 # statistics
 
 
-def _stats(x: torch.Tensor, per: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+def _stats(x: torch.Tensor, per: int, rope: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     batch, heads, n, _ = x.shape
     blocks = math.ceil(n / STATS_TOKENS)
     groups = 1 if per == 0 else math.ceil(n / per)
     partial = torch.empty(batch * heads, blocks, 3, HEAD_DIM, device=x.device)
     mean, low, high = (torch.empty(batch, heads, groups, HEAD_DIM, device=x.device) for _ in range(3))
-    lib.call("unica_b200_channel_stats", lib.ptr(x), token_layout(x), batch * heads, n, per, lib.ptr(partial),
-             lib.ptr(mean), lib.ptr(low), lib.ptr(high), lib.stream())
+    lib.call("unica_b200_channel_stats" + ("_rope" if rope is not None else ""), lib.ptr(x), token_layout(x), *rope_args(rope, x),
+             batch * heads, n, per, lib.ptr(partial), lib.ptr(mean), lib.ptr(low), lib.ptr(high), lib.stream())
     return mean, low, high
 
 
@@ -146,18 +148,60 @@ def _stats(x: torch.Tensor, per: int) -> tuple[torch.Tensor, torch.Tensor, torch
 def rope_stats(x: torch.Tensor, rope: torch.Tensor | None = None, per: int | None = None):
     """Per channel of each head over all tokens of x: mean, min, max, float32 [batch, heads, 128]; with per (a multiple
     of 256) over each block of that many tokens, [batch, heads, blocks, 128] (unica/__init__.py:592-612).  One pass
-    over x; sums in a fixed order, so the mean does not depend on how many heads the call holds."""
-    _no_rope(rope)
+    over x; sums in a fixed order, so the mean does not depend on how many heads the call holds.
+    rope: ComfyUI's table (see rope_table); the statistics are then those of x rotated, which is never written."""
     _check_input(x, "x")
     if per is not None and per % STATS_TOKENS:
         raise ValueError(f"per must be a multiple of {STATS_TOKENS}, got {per}")
-    mean, low, high = _stats(readable(x), per or 0)
+    mean, low, high = _stats(readable(x), per or 0, rope)
     return (mean, low, high) if per else (mean[:, :, 0], low[:, :, 0], high[:, :, 0])
 
 
-def _no_rope(rope) -> None:
-    if rope is not None:
-        raise NotImplementedError("rope= (RoPE fused into the quantizers) is not built yet in the B200 library")
+# ----------------------------------------------------------------------------------------------------------------------
+# RoPE inside the quantizers (unica/__init__.py:536-577)
+
+
+def rope_table(rope: torch.Tensor, batch: int, n_queries: int, n_keys: int) -> torch.Tensor:
+    """ComfyUI's RoPE table checked: float32 [batch or 1, tokens, 1, 64, 2, 2], self-attention."""
+    if n_queries != n_keys:
+        raise ValueError(f"rope= is for self-attention, got {n_queries} queries and {n_keys} keys")
+    if (rope.dtype != torch.float32 or rope.dim() != 6 or rope.shape[1] != n_queries or rope.shape[2] != 1
+            or rope.shape[3:] != (ROPE_PAIRS, 2, 2) or rope.shape[0] not in (1, batch)):
+        raise ValueError(f"rope must be float32 [{batch} or 1, {n_queries}, 1, {ROPE_PAIRS}, 2, 2], "
+                         f"got {rope.dtype} {tuple(rope.shape)}")
+    return rope
+
+
+# The table compacted last: (weak reference to it, its version, the compact table).  The blocks of a sampling step share
+# one table, so it is converted once; a weak reference rather than an address, because the next step's table may be
+# given the old one's memory.
+_compact_rope: tuple = (lambda: None, -1, None)
+
+
+def compact_rope(rope: torch.Tensor) -> torch.Tensor:
+    """The table as the kernels read it: (cos, sin) per pair in fp16, [batch or 1, tokens, 64, 2].  The table must hold
+    rotations [[c, -s], [s, c]].  Kept while the same table object, unmodified, comes back."""
+    global _compact_rope
+    version = None if rope.is_inference() else rope._version  # inference tensors have no version counter
+    kept, kept_version, compact = _compact_rope
+    if kept() is rope and kept_version == version:
+        return compact
+    cos, sin = rope[..., 0, 0], rope[..., 1, 0]
+    if not (torch.equal(rope[..., 1, 1], cos) and torch.equal(rope[..., 0, 1], -sin)):
+        raise ValueError("rope must hold rotations [[cos, -sin], [sin, cos]], as WAN's table does")
+    compact = torch.stack([cos, sin], -1)[:, :, 0].half().contiguous()
+    _compact_rope = (weakref.ref(rope), version, compact)
+    return compact
+
+
+def rope_args(rope: torch.Tensor | None, x: torch.Tensor) -> tuple:
+    """The (table, batch stride) arguments of the *_rope entry points for x [batch, heads, tokens, 128]; () without rope."""
+    if rope is None:
+        return ()
+    compact = compact_rope(rope_table(rope, x.shape[0], x.shape[2], x.shape[2]))
+    if compact.device != x.device:
+        raise ValueError(f"rope is on {compact.device}, the tensors on {x.device}")
+    return lib.ptr(compact), compact.stride(0) if compact.shape[0] > 1 else 0
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -168,10 +212,10 @@ def _no_rope(rope) -> None:
 def quantize_int8(x: torch.Tensor, mean: torch.Tensor | None, block: int, rope: torch.Tensor | None = None,
                   tiles: int | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """x - mean ~ x8 * scale with one scale per `block` tokens over all of d (128: Q, 64: K); bit for bit the
-    reference's quant() (unica/__init__.py:363-378).  mean: float32 [batch, heads, 128] or None.
+    reference's quant() (unica/__init__.py:363-378).  mean: float32 [batch, heads, 128] or None.  rope: x is rotated
+    first (mean is then the rotated x's).
     Returns int8 [batch, heads, tiles, 8, block, 16] (tile, 16-channel chunk, token, channel: the tcgen05 operand
     image; `decode_int8` gives [batch, heads, N, 128]) and float32 scales [batch, heads, tiles]."""
-    _no_rope(rope)
     _check_input(x, "x")
     x = readable(x)
     batch, heads, n, _ = x.shape
@@ -180,8 +224,8 @@ def quantize_int8(x: torch.Tensor, mean: torch.Tensor | None, block: int, rope: 
     x8 = torch.empty(batch, heads, tiles, HEAD_DIM // 16, block, 16, dtype=torch.int8, device=x.device)
     scale = torch.empty(batch, heads, tiles, device=x.device)
     mean = None if mean is None else mean.float().contiguous()
-    lib.call("unica_b200_quantize_int8", lib.ptr(x), token_layout(x), lib.ptr(mean), batch * heads, n, block, tiles,
-             lib.ptr(x8), lib.ptr(scale), lib.stream())
+    lib.call("unica_b200_quantize_int8" + ("_rope" if rope is not None else ""), lib.ptr(x), token_layout(x), lib.ptr(mean),
+             *rope_args(rope, x), batch * heads, n, block, tiles, lib.ptr(x8), lib.ptr(scale), lib.stream())
     return x8, scale
 
 
@@ -258,29 +302,30 @@ def kernel_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str
                   rope: torch.Tensor | None = None, **tile: int) -> tuple:
     """The quantized operands `kernel` takes, apart from attention() so that quantization and kernel can be timed
     separately (unica/__init__.py:288-356)."""
-    _no_rope(rope)
     settings = _settings(kernel, tile)
     q, k, v = readable(q), readable(k), readable(v)
+    if rope is not None:
+        rope_table(rope, q.shape[0], q.shape[2], k.shape[2])
     q_tiles = 2 * math.ceil(q.shape[2] / (2 * Q_SCALE_BLOCK))  # the kernels take query tiles in pairs
     if kernel == "attention_fp4":  # Q and K in NVFP4 along d, V along the keys; Q smoothed per block of SMOOTH_Q queries
         smooth = settings["SMOOTH_Q"]
         if smooth % 256:
             raise ValueError(f"SMOOTH_Q must be a multiple of 256, got {smooth}")
-        k_mean, k_low, k_high = rope_stats(k)
+        k_mean, k_low, k_high = rope_stats(k, rope)
         if smooth:
-            q_mean, q_low, q_high = rope_stats(q, None, smooth)
-            q4, q_outer = quantize_fp4_rows(q, q_mean, 1, None, (q_low, q_high), smooth, tiles=q_tiles)
-            bias = smooth_bias(k, k_mean, q_mean)
+            q_mean, q_low, q_high = rope_stats(q, rope, smooth)
+            q4, q_outer = quantize_fp4_rows(q, q_mean, 1, rope, (q_low, q_high), smooth, tiles=q_tiles)
+            bias = smooth_bias(k, k_mean, q_mean, rope=rope)
         else:
-            q4, q_outer = quantize_fp4_rows(q, None, tiles=q_tiles)
+            q4, q_outer = quantize_fp4_rows(q, None, 1, rope, tiles=q_tiles)
             bias = None
-        k4, k_outer = quantize_fp4_rows(k, k_mean, 64, None, (k_low, k_high))
+        k4, k_outer = quantize_fp4_rows(k, k_mean, 64, rope, (k_low, k_high))
         qk_outer = (q_outer * k_outer).clamp_min(1e-30).contiguous()
         v4, v_outer = quantize_v4(v)
         return q4, k4, v4, qk_outer, v_outer, bias, smooth
-    q8, q_scale = quantize_int8(q, None, Q_SCALE_BLOCK, tiles=q_tiles)
-    k_mean = rope_stats(k)[0]  # softmax cancels the mean
-    k8, k_scale = quantize_int8(k, k_mean, K_SCALE_BLOCK)
+    q8, q_scale = quantize_int8(q, None, Q_SCALE_BLOCK, rope, tiles=q_tiles)
+    k_mean = rope_stats(k, rope)[0]  # softmax cancels the mean
+    k8, k_scale = quantize_int8(k, k_mean, K_SCALE_BLOCK, rope)
     if settings["V_TOKEN"]:
         v8, v_scale, v_token = quantize_v(v, per_token=True)
         return q8, q_scale, k8, k_scale, v8, v_scale, v_token, lib.V_TOKEN
@@ -325,7 +370,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
     n_keys = k.shape[2]
     if n_keys == 0:
         raise ValueError("k and v must hold at least one token")
-    _no_rope(rope)
+    if rope is not None:
+        rope_table(rope, batch, n_queries, n_keys)
     if inputs is None and (q.dtype != torch.bfloat16 or heads_per_call(q, k, kernel, tile) < heads):
         return in_pieces(q, k, v, kernel, rope, tile)
     q, k, v = readable(q), readable(k), readable(v)

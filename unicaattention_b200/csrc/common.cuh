@@ -29,6 +29,31 @@ struct TokenLayout {
     }
 };
 
+// RoPE inside the quantizers (the reference's rope_chunk, csrc/flash.cu:250-268): (cos, sin) per pair of channels in fp16,
+// [batch or 1][n_tokens][64][2]; batch_stride in halves, 0 when one table serves every batch.  table null: no rotation.
+struct RopeTable {
+    const __half* table;
+    long long batch_stride;
+    __device__ __forceinline__ const __half* row(const TokenLayout& in, int head_index, int token_index) const {
+        return table + size_t(head_index / in.heads) * batch_stride + size_t(token_index) * 128;
+    }
+};
+
+// Eight channels starting at channel `dim` (a multiple of 8) of one token, rotated: out[2i] = c x[2i] - s x[2i+1],
+// out[2i+1] = s x[2i] + c x[2i+1], each product rounded, then the difference or sum: no fused multiply-add, as the
+// emulator computes it (bench/emulate.py:122-130).
+__device__ __forceinline__ void rope8(float (&v)[8], const __half* token_row, int dim) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(token_row + dim);
+    const __half2* cs = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 r = __half22float2(cs[j]);  // (cos, sin)
+        const float x0 = v[2 * j], x1 = v[2 * j + 1];
+        v[2 * j] = __fsub_rn(__fmul_rn(r.x, x0), __fmul_rn(r.y, x1));
+        v[2 * j + 1] = __fadd_rn(__fmul_rn(r.y, x0), __fmul_rn(r.x, x1));
+    }
+}
+
 // status codes a kernel leaves in its status word (0: fine)
 enum Status : int {
     STATUS_OK = 0,

@@ -29,9 +29,11 @@ __device__ __forceinline__ void load8(float (&v)[8], const __nv_bfloat16* src) {
 // without RoPE): thread = (lane of 16 tokens, chunk of 8 channels); lane l adds tokens l, l + 16, ... in order, then
 // the 16 lanes are added in order.  partial: [heads][blocks][3][128].  Grid (blocks, heads).
 // skip: [heads][n_tokens] bytes, 1 = the token takes no part (the outlier keys of V), or null.
+// rope: x is rotated first (the rotated values exist nowhere in memory).
 __global__ void __launch_bounds__(THREADS) channel_stats_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
                                                                  int n_tokens, float* __restrict__ partial,
-                                                                 const uint8_t* __restrict__ skip = nullptr) {
+                                                                 const uint8_t* __restrict__ skip = nullptr,
+                                                                 RopeTable rope = RopeTable{nullptr, 0}) {
     const int chunk = threadIdx.x % 16, lane = threadIdx.x / 16;
     const int head = blockIdx.y, token0 = blockIdx.x * STATS_TOKENS;
     float sum[8], low[8], high[8];
@@ -43,6 +45,7 @@ __global__ void __launch_bounds__(THREADS) channel_stats_kernel(const __nv_bfloa
         if (skip && skip[size_t(head) * n_tokens + token]) continue;
         float v[8];
         load8(v, x + in.offset(head, token) + chunk * 8);
+        if (rope.table) rope8(v, rope.row(in, head, token), chunk * 8);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             sum[i] += v[i];
@@ -122,7 +125,8 @@ __device__ __forceinline__ uint32_t pack4(const float* v, float scale) {
 template <int ROWS>
 __global__ void __launch_bounds__(THREADS) quantize_rows_int8_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
                                                                       const float* __restrict__ mean, int n_tokens,
-                                                                      int8_t* __restrict__ codes, float* __restrict__ scales) {
+                                                                      int8_t* __restrict__ codes, float* __restrict__ scales,
+                                                                      RopeTable rope) {
     constexpr int ITEMS = ROWS * 8 / THREADS;  // (row, 16-channel chunk) items per thread
     __shared__ float scratch[THREADS / 32];
     const int head = blockIdx.y, tile = blockIdx.x, token0 = tile * ROWS;
@@ -136,6 +140,11 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_int8_kernel(const __nv_
             float a[8], b[8];
             load8(a, src);
             load8(b, src + 8);
+            if (rope.table) {  // rotate first, then take the mean (of the rotated x) away
+                const __half* f = rope.row(in, head, token0 + row);
+                rope8(a, f, chunk * 16);
+                rope8(b, f, chunk * 16 + 8);
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float m0 = mean ? mean[head * HEAD_DIM + chunk * 16 + i] : 0.0f;
@@ -242,8 +251,8 @@ __global__ void __launch_bounds__(THREADS) quantize_v_int8_kernel(const __nv_bfl
 
 using namespace unica;
 
-extern "C" int unica_b200_channel_stats(const void* x, unica_token_layout layout, int heads, int n_tokens, int per,
-                                        float* partial, float* mean, float* low, float* high, void* stream) {
+static int channel_stats(const void* x, unica_token_layout layout, RopeTable rope, int heads, int n_tokens, int per, float* partial,
+                         float* mean, float* low, float* high, void* stream) {
     if (!x || !partial || !mean || !low || !high) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats: null pointer");
     if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats: heads and n_tokens must be positive");
     if (per != 0 && (per < 0 || per % STATS_TOKENS)) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats: per must be 0 or a multiple of 256");
@@ -251,9 +260,23 @@ extern "C" int unica_b200_channel_stats(const void* x, unica_token_layout layout
     const int per_group = per ? per / STATS_TOKENS : blocks;
     const int groups = (blocks + per_group - 1) / per_group;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    channel_stats_kernel<<<dim3(blocks, heads), THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(x), to_layout(layout), n_tokens, partial);
+    channel_stats_kernel<<<dim3(blocks, heads), THREADS, 0, s>>>(static_cast<const __nv_bfloat16*>(x), to_layout(layout), n_tokens, partial,
+                                                                 nullptr, rope);
     channel_stats_finish_kernel<<<dim3(groups, heads), HEAD_DIM, 0, s>>>(partial, blocks, per_group, n_tokens, mean, low, high);
     return unica_check_launch("channel_stats");
+}
+
+extern "C" int unica_b200_channel_stats(const void* x, unica_token_layout layout, int heads, int n_tokens, int per,
+                                        float* partial, float* mean, float* low, float* high, void* stream) {
+    return channel_stats(x, layout, RopeTable{nullptr, 0}, heads, n_tokens, per, partial, mean, low, high, stream);
+}
+
+extern "C" int unica_b200_channel_stats_rope(const void* x, unica_token_layout layout, const void* rope, long long rope_batch_stride,
+                                             int heads, int n_tokens, int per, float* partial, float* mean, float* low, float* high,
+                                             void* stream) {
+    if (!rope) return unica_fail(UNICA_B200_ERR_ARGUMENT, "channel_stats_rope: null table");
+    return channel_stats(x, layout, RopeTable{static_cast<const __half*>(rope), rope_batch_stride}, heads, n_tokens, per, partial, mean,
+                         low, high, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -323,8 +346,8 @@ extern "C" int unica_b200_channel_stats_masked(const void* x, unica_token_layout
     return unica_check_launch("channel_stats_masked");
 }
 
-extern "C" int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const float* mean, int heads, int n_tokens,
-                                        int block_tokens, int tiles, int8_t* codes, float* scales, void* stream) {
+static int quantize_int8(const void* x, unica_token_layout layout, const float* mean, RopeTable rope, int heads, int n_tokens,
+                         int block_tokens, int tiles, int8_t* codes, float* scales, void* stream) {
     if (!x || !codes || !scales) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: null pointer");
     if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: heads and n_tokens must be positive");
     if (block_tokens != 128 && block_tokens != 64) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8: block_tokens must be 128 (Q) or 64 (K)");
@@ -332,10 +355,23 @@ extern "C" int unica_b200_quantize_int8(const void* x, unica_token_layout layout
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
     if (block_tokens == 128)
-        quantize_rows_int8_kernel<128><<<dim3(tiles, heads), THREADS, 0, s>>>(xb, to_layout(layout), mean, n_tokens, codes, scales);
+        quantize_rows_int8_kernel<128><<<dim3(tiles, heads), THREADS, 0, s>>>(xb, to_layout(layout), mean, n_tokens, codes, scales, rope);
     else
-        quantize_rows_int8_kernel<64><<<dim3(tiles, heads), THREADS, 0, s>>>(xb, to_layout(layout), mean, n_tokens, codes, scales);
+        quantize_rows_int8_kernel<64><<<dim3(tiles, heads), THREADS, 0, s>>>(xb, to_layout(layout), mean, n_tokens, codes, scales, rope);
     return unica_check_launch("quantize_int8");
+}
+
+extern "C" int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const float* mean, int heads, int n_tokens,
+                                        int block_tokens, int tiles, int8_t* codes, float* scales, void* stream) {
+    return quantize_int8(x, layout, mean, RopeTable{nullptr, 0}, heads, n_tokens, block_tokens, tiles, codes, scales, stream);
+}
+
+extern "C" int unica_b200_quantize_int8_rope(const void* x, unica_token_layout layout, const float* mean, const void* rope,
+                                             long long rope_batch_stride, int heads, int n_tokens, int block_tokens, int tiles,
+                                             int8_t* codes, float* scales, void* stream) {
+    if (!rope) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_int8_rope: null table");
+    return quantize_int8(x, layout, mean, RopeTable{static_cast<const __half*>(rope), rope_batch_stride}, heads, n_tokens, block_tokens,
+                         tiles, codes, scales, stream);
 }
 
 extern "C" int unica_b200_quantize_v_int8(const void* v, unica_token_layout layout, const float* low, const float* high,

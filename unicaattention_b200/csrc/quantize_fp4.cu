@@ -83,7 +83,8 @@ template <int ROWS, bool SLOTS>
 __global__ void __launch_bounds__(FP4_THREADS) quantize_rows_fp4_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
                                                                          const float* __restrict__ mean, int mean_tokens, int groups,
                                                                          const float* __restrict__ outer, int n_tokens,
-                                                                         uint8_t* __restrict__ codes, uint8_t* __restrict__ sf) {
+                                                                         uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
+                                                                         RopeTable rope) {
     const int head = blockIdx.y, tile = blockIdx.x;
     const float head_outer = outer[head];
     uint8_t* tile_codes = codes + (size_t(head) * gridDim.x + tile) * (ROWS * HEAD_DIM / 2);
@@ -101,9 +102,15 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_rows_fp4_kernel(const __
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const float2 f = __bfloat1622float2(pairs[i]);
-                v[2 * i] = f.x - (mu ? mu[2 * i] : 0.0f);
-                v[2 * i + 1] = f.y - (mu ? mu[2 * i + 1] : 0.0f);
+                v[2 * i] = f.x, v[2 * i + 1] = f.y;
             }
+            if (rope.table) {  // rotate first: the mean is the rotated x's
+                const __half* f = rope.row(in, head, token);
+                rope8(*reinterpret_cast<float(*)[8]>(v), f, block * 16);
+                rope8(*reinterpret_cast<float(*)[8]>(v + 8), f, block * 16 + 8);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] -= mu ? mu[i] : 0.0f;
         } else {
 #pragma unroll
             for (int i = 0; i < 16; ++i) v[i] = 0.0f;
@@ -174,13 +181,23 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_
 // the last key.  bias: [heads][q_blocks][k_tiles * 64].  Grid (k_tiles, heads).
 __global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfloat16* __restrict__ k, TokenLayout in,
                                                                    const float* __restrict__ k_mean, const float* __restrict__ q_mean,
-                                                                   int q_blocks, int n_keys, float scale_log2, float* __restrict__ bias) {
+                                                                   int q_blocks, int n_keys, float scale_log2, float* __restrict__ bias,
+                                                                   RopeTable rope) {
     __shared__ float centred[KEY_TILE][HEAD_DIM + 1];
     __shared__ float qm[4][HEAD_DIM];
     const int head = blockIdx.y, t = blockIdx.x, k_tiles = gridDim.x;
-    for (int item = threadIdx.x; item < KEY_TILE * HEAD_DIM; item += FP4_THREADS) {
-        const int slot = item / HEAD_DIM, c = item % HEAD_DIM, key = t * KEY_TILE + slot_key(slot);
-        centred[slot][c] = key < n_keys ? __bfloat162float(k[in.offset(head, key) + c]) - k_mean[head * HEAD_DIM + c] : 0.0f;
+    for (int item = threadIdx.x; item < KEY_TILE * HEAD_DIM / 2; item += FP4_THREADS) {  // a pair of channels each
+        const int slot = item / (HEAD_DIM / 2), c = item % (HEAD_DIM / 2) * 2, key = t * KEY_TILE + slot_key(slot);
+        float2 x = make_float2(0.0f, 0.0f);
+        if (key < n_keys) {
+            x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k + in.offset(head, key) + c));
+            if (rope.table) {
+                const float2 r = __half22float2(*reinterpret_cast<const __half2*>(rope.row(in, head, key) + c));  // (cos, sin)
+                x = make_float2(__fsub_rn(__fmul_rn(r.x, x.x), __fmul_rn(r.y, x.y)), __fadd_rn(__fmul_rn(r.y, x.x), __fmul_rn(r.x, x.y)));
+            }
+            x.x -= k_mean[head * HEAD_DIM + c], x.y -= k_mean[head * HEAD_DIM + c + 1];
+        }
+        centred[slot][c] = x.x, centred[slot][c + 1] = x.y;
     }
     const int slot = threadIdx.x % KEY_TILE, lane_block = threadIdx.x / KEY_TILE;  // 4 query blocks at a time
     for (int b0 = 0; b0 < q_blocks; b0 += 4) {
@@ -212,9 +229,9 @@ extern "C" int unica_b200_nvfp4_outer(const float* mean, const float* low, const
     return unica_check_launch("nvfp4_outer");
 }
 
-extern "C" int unica_b200_quantize_fp4_rows(const void* x, unica_token_layout layout, const float* mean, int mean_tokens,
-                                            const float* outer, int heads, int n_tokens, int rows_per_tile, int tiles,
-                                            uint8_t* codes, uint8_t* sf, void* stream) {
+static int quantize_fp4_rows(const void* x, unica_token_layout layout, const float* mean, int mean_tokens, RopeTable rope,
+                             const float* outer, int heads, int n_tokens, int rows_per_tile, int tiles, uint8_t* codes, uint8_t* sf,
+                             void* stream) {
     if (!x || !outer || !codes || !sf) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows: null pointer");
     if (heads <= 0 || n_tokens <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows: heads and n_tokens must be positive");
     if (rows_per_tile != 128 && rows_per_tile != 64)
@@ -226,10 +243,24 @@ extern "C" int unica_b200_quantize_fp4_rows(const void* x, unica_token_layout la
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
     if (rows_per_tile == 128)
-        quantize_rows_fp4_kernel<128, false><<<dim3(tiles, heads), FP4_THREADS, 0, s>>>(xb, to_layout(layout), mean, mean_tokens, groups, outer, n_tokens, codes, sf);
+        quantize_rows_fp4_kernel<128, false><<<dim3(tiles, heads), FP4_THREADS, 0, s>>>(xb, to_layout(layout), mean, mean_tokens, groups, outer, n_tokens, codes, sf, rope);
     else
-        quantize_rows_fp4_kernel<64, true><<<dim3(tiles, heads), FP4_THREADS, 0, s>>>(xb, to_layout(layout), mean, mean_tokens, groups, outer, n_tokens, codes, sf);
+        quantize_rows_fp4_kernel<64, true><<<dim3(tiles, heads), FP4_THREADS, 0, s>>>(xb, to_layout(layout), mean, mean_tokens, groups, outer, n_tokens, codes, sf, rope);
     return unica_check_launch("quantize_fp4_rows");
+}
+
+extern "C" int unica_b200_quantize_fp4_rows(const void* x, unica_token_layout layout, const float* mean, int mean_tokens,
+                                            const float* outer, int heads, int n_tokens, int rows_per_tile, int tiles,
+                                            uint8_t* codes, uint8_t* sf, void* stream) {
+    return quantize_fp4_rows(x, layout, mean, mean_tokens, RopeTable{nullptr, 0}, outer, heads, n_tokens, rows_per_tile, tiles, codes, sf, stream);
+}
+
+extern "C" int unica_b200_quantize_fp4_rows_rope(const void* x, unica_token_layout layout, const float* mean, int mean_tokens,
+                                                 const void* rope, long long rope_batch_stride, const float* outer, int heads,
+                                                 int n_tokens, int rows_per_tile, int tiles, uint8_t* codes, uint8_t* sf, void* stream) {
+    if (!rope) return unica_fail(UNICA_B200_ERR_ARGUMENT, "quantize_fp4_rows_rope: null table");
+    return quantize_fp4_rows(x, layout, mean, mean_tokens, RopeTable{static_cast<const __half*>(rope), rope_batch_stride}, outer, heads,
+                             n_tokens, rows_per_tile, tiles, codes, sf, stream);
 }
 
 extern "C" int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layout, const float* low, const float* high,
@@ -242,12 +273,25 @@ extern "C" int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layou
     return unica_check_launch("quantize_v_fp4");
 }
 
-extern "C" int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
-                                      int heads, int q_blocks, int n_keys, float scale_log2, float* bias, void* stream) {
+static int smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean, RopeTable rope, int heads,
+                       int q_blocks, int n_keys, float scale_log2, float* bias, void* stream) {
     if (!k || !k_mean || !q_mean || !bias) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: null pointer");
     if (heads <= 0 || q_blocks <= 0 || n_keys <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: heads, q_blocks and n_keys must be positive");
     const int tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
     smooth_bias_kernel<<<dim3(tiles, heads), FP4_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias);
+        static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias, rope);
     return unica_check_launch("smooth_bias");
+}
+
+extern "C" int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
+                                      int heads, int q_blocks, int n_keys, float scale_log2, float* bias, void* stream) {
+    return smooth_bias(k, layout, k_mean, q_mean, RopeTable{nullptr, 0}, heads, q_blocks, n_keys, scale_log2, bias, stream);
+}
+
+extern "C" int unica_b200_smooth_bias_rope(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
+                                           const void* rope, long long rope_batch_stride, int heads, int q_blocks, int n_keys,
+                                           float scale_log2, float* bias, void* stream) {
+    if (!rope) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias_rope: null table");
+    return smooth_bias(k, layout, k_mean, q_mean, RopeTable{static_cast<const __half*>(rope), rope_batch_stride}, heads, q_blocks, n_keys,
+                       scale_log2, bias, stream);
 }

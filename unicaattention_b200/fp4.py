@@ -46,11 +46,11 @@ def quantize_fp4_rows(x: torch.Tensor, mean: torch.Tensor | None, pad_to: int = 
     """x - mean in NVFP4 along d under one float scale per head; bit for bit the reference emulator's
     block_scaled(x - mean, "nvfp4", -1).  pad_to 64: K (64-key tiles, keys in slot order); 1: Q (128-query tiles).
     mean: float32 [batch, heads, 128], or [batch, heads, blocks, 128] with mean_tokens (Q smoothing).  low_high: the
-    per-channel (per block) min and max of x, as rope_stats returns them; taken here when not given.
+    per-channel (per block) min and max of x, as rope_stats returns them; taken here when not given.  rope: x is
+    rotated first; mean and low_high are then the rotated x's.
     Returns (FP4Rows, outer float32 [batch, heads])."""
     import unicaattention_b200 as unica
 
-    unica._no_rope(rope)
     unica._check_input(x, "x")
     if pad_to not in (1, 64):
         raise ValueError(f"pad_to must be 1 (Q) or 64 (K), got {pad_to}")
@@ -60,7 +60,7 @@ def quantize_fp4_rows(x: torch.Tensor, mean: torch.Tensor | None, pad_to: int = 
     per = mean_tokens or 0
     groups = 1 if not per else math.ceil(n / per)
     if low_high is None:
-        _, low, high = unica._stats(x, per)
+        _, low, high = unica._stats(x, per, rope)
     else:
         low, high = (t.float().reshape(batch, heads, groups, HEAD_DIM).contiguous() for t in low_high)
     mean_arg = None if mean is None else mean.float().reshape(batch, heads, groups, HEAD_DIM).contiguous()
@@ -71,8 +71,8 @@ def quantize_fp4_rows(x: torch.Tensor, mean: torch.Tensor | None, pad_to: int = 
     tiles = need if tiles is None else tiles
     codes = torch.empty(batch, heads, tiles, 4, rows, 16, dtype=torch.uint8, device=x.device)
     sf = torch.empty(batch, heads, tiles, 2, rows, 4, dtype=torch.uint8, device=x.device)
-    lib.call("unica_b200_quantize_fp4_rows", lib.ptr(x), _layout(x), lib.ptr(mean_arg), per, lib.ptr(outer), batch * heads, n,
-             rows, tiles, lib.ptr(codes), lib.ptr(sf), lib.stream())
+    lib.call("unica_b200_quantize_fp4_rows" + ("_rope" if rope is not None else ""), lib.ptr(x), _layout(x), lib.ptr(mean_arg), per,
+             *unica.rope_args(rope, x), lib.ptr(outer), batch * heads, n, rows, tiles, lib.ptr(codes), lib.ptr(sf), lib.stream())
     return FP4Rows(codes, sf), outer
 
 
@@ -102,7 +102,6 @@ def smooth_bias(k: torch.Tensor, k_mean: torch.Tensor, q_mean: torch.Tensor, qk_
     order, 0 past the last key.  Returns float32 [batch, heads, blocks, ceil64(n_keys)]."""
     import unicaattention_b200 as unica
 
-    unica._no_rope(rope)
     unica._check_input(k, "k")
     k = unica.readable(k)
     batch, heads, n, _ = k.shape
@@ -111,8 +110,9 @@ def smooth_bias(k: torch.Tensor, k_mean: torch.Tensor, q_mean: torch.Tensor, qk_
     if padded_keys is not None and padded_keys != padded:
         raise ValueError(f"padded_keys must be {padded} for {n} keys, got {padded_keys}")
     bias = torch.empty(batch, heads, blocks, padded, device=k.device)
-    lib.call("unica_b200_smooth_bias", lib.ptr(k), _layout(k), lib.ptr(k_mean.float().contiguous()),
-             lib.ptr(q_mean.float().contiguous()), batch * heads, blocks, n, HEAD_DIM**-0.5 * LOG2E, lib.ptr(bias), lib.stream())
+    lib.call("unica_b200_smooth_bias" + ("_rope" if rope is not None else ""), lib.ptr(k), _layout(k),
+             lib.ptr(k_mean.float().contiguous()), lib.ptr(q_mean.float().contiguous()), *unica.rope_args(rope, k), batch * heads,
+             blocks, n, HEAD_DIM**-0.5 * LOG2E, lib.ptr(bias), lib.stream())
     return bias
 
 

@@ -31,7 +31,7 @@ class TokenLayout(ctypes.Structure):
                 ("heads", ctypes.c_int)]
 
 
-_P, _I, _F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_P, _I, _F, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 SIGNATURES = {
     # name: argument types (every entry point returns int)
     "unica_b200_version": [],
@@ -49,6 +49,10 @@ SIGNATURES = {
     "unica_b200_quantize_fp4_rows": [_P, TokenLayout, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_v_fp4": [_P, TokenLayout, _P, _P, _I, _I, _P, _P, _P, _P],
     "unica_b200_smooth_bias": [_P, TokenLayout, _P, _P, _I, _I, _I, _F, _P, _P],
+    "unica_b200_channel_stats_rope": [_P, TokenLayout, _P, _LL, _I, _I, _I, _P, _P, _P, _P, _P],
+    "unica_b200_quantize_int8_rope": [_P, TokenLayout, _P, _P, _LL, _I, _I, _I, _I, _P, _P, _P],
+    "unica_b200_quantize_fp4_rows_rope": [_P, TokenLayout, _P, _I, _P, _LL, _P, _I, _I, _I, _I, _P, _P, _P],
+    "unica_b200_smooth_bias_rope": [_P, TokenLayout, _P, _P, _P, _LL, _I, _I, _I, _F, _P, _P],
 }
 
 
