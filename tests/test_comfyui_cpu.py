@@ -139,3 +139,71 @@ def test_mode_names_round_trip():
     assert nodes.mode_settings(nodes.mode_name("per_token", "fast")) == unica.PRESETS["fast"]
     assert nodes.mode_settings("sdpa") is None and nodes.mode_settings("unica") == unica.PRESETS["per_token"]
     assert set(nodes.NODE_CLASS_MAPPINGS) == set(nodes.NODE_DISPLAY_NAME_MAPPINGS)
+
+
+class WanSelfAttention(torch.nn.Module):
+    """What fused_rope_forward uses of ComfyUI's module of that name: the projections, the norms and the sizes."""
+
+    def __init__(self, heads=2, dim=128):
+        super().__init__()
+        self.num_heads, self.head_dim = heads, dim
+        self.q, self.k, self.v, self.o = (torch.nn.Linear(heads * dim, heads * dim) for _ in range(4))
+        self.norm_q = self.norm_k = torch.nn.Identity()
+
+    def forward(self, x, freqs, transformer_options={}):  # noqa: B006
+        return "model's own forward"
+
+
+class WanCrossAttention(WanSelfAttention):
+    pass
+
+
+class BlockPatcher(Patcher):
+    """A ModelPatcher with diffusion_model.blocks and object patches."""
+
+    def __init__(self, blocks, options=None):
+        super().__init__(options)
+        self.blocks, self.object_patches = blocks, {}
+
+    def clone(self):
+        return BlockPatcher(self.blocks, {"transformer_options": dict(self.model_options["transformer_options"])})
+
+    def get_model_object(self, name):
+        if name == "diffusion_model.blocks":
+            return self.blocks
+        return getattr(self.blocks[int(name.split(".")[2])], name.split(".")[3])
+
+    def add_object_patch(self, name, value):
+        self.object_patches[name] = value
+
+
+def test_fused_rope_forward(fake_unica):
+    """fuse_rope: the self-attention blocks' forward hands q, k (not rotated) and the model's table to unica; calls it
+    cannot take go to the original forward (the reference's tests/test_comfyui.py covers its patch the same way)."""
+    blocks = [types.SimpleNamespace(self_attn=WanSelfAttention(), cross_attn=WanCrossAttention()) for _ in range(2)]
+    blocks.append(types.SimpleNamespace(self_attn=WanCrossAttention()))  # derived class in a self_attn slot: left alone
+    (patched,) = nodes.UnicaAttentionNative().patch(BlockPatcher(blocks), True, v_scale="per_channel", fuse_rope=True)
+    assert sorted(patched.object_patches) == [f"diffusion_model.blocks.{i}.self_attn.forward" for i in range(2)]
+    forward = patched.object_patches["diffusion_model.blocks.0.self_attn.forward"]
+    module = blocks[0].self_attn
+    x, freqs = torch.randn(2, 50, 256), torch.zeros(1, 50, 1, 64, 2, 2)
+    out = forward(x, freqs)
+    assert fake_unica[-1] == unica.PRESETS["per_channel"] | {"rope": freqs}
+    heads = lambda t: t.view(2, 50, 2, 128).transpose(1, 2)  # noqa: E731
+    exact = torch.nn.functional.scaled_dot_product_attention(heads(module.q(x)), heads(module.k(x)), heads(module.v(x)))
+    assert torch.allclose(out, module.o(exact.transpose(1, 2).reshape(2, 50, 256)), atol=3e-2)
+    # what it cannot take: no table, a table of another length, an attn1 patch
+    assert forward(x, None) == "model's own forward"
+    assert forward(x, freqs[:, :40]) == "model's own forward"
+    assert forward(x, freqs, transformer_options={"patches": {"attn1_patch": [print]}}) == "model's own forward"
+    # patched again: the new forward wraps the module's own, not the first patch
+    again = BlockPatcher(blocks)
+    again.object_patches = dict(patched.object_patches)
+    assert nodes.patch_self_attention_forward(again, unica.PRESETS["fast"]) == 2
+    assert again.object_patches["diffusion_model.blocks.0.self_attn.forward"].original == module.forward
+    # a failure sends this call and the later ones to the model's forward
+    def broken(*args, **kwargs):
+        raise RuntimeError("driver error")
+    unica.attention = broken  # the fixture's monkeypatch restores it
+    assert forward(x, freqs) == "model's own forward" and nodes.FAILED
+    assert forward(x, freqs) == "model's own forward"

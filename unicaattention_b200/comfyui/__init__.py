@@ -1,6 +1,6 @@
 """ComfyUI nodes that run a model's self-attention on unicaattention_b200: the drop-in boundary of the reference's
-comfyui/__init__.py (same node classes, inputs, override call convention, routing rules and fallback), without its
-measurement CSV, RIFE node and fused-RoPE patch, which lie outside the attention path.
+comfyui/__init__.py (same node classes, inputs, override call convention, routing rules, fallback and fused-RoPE
+forward), without its measurement CSV and RIFE node, which lie outside the attention path.
 
     model -> Unica Attention (native)   -> sampler     ComfyUI's own models: an `optimized_attention_override`
     WanVideoModelLoader -> Unica Attention (WanVideo) -> WanVideoSampler   ComfyUI-WanVideoWrapper: `attention` wrapped
@@ -153,12 +153,61 @@ def native_override(previous, settings: dict):
     return override
 
 
+def fused_rope_forward(module, original, settings: dict):
+    """A forward for ComfyUI's WanSelfAttention that hands q and k to unica BEFORE RoPE, with the model's own table: the
+    quantizers rotate them on the way in, so the model's pass over q and k to rotate them goes, and with it a bf16
+    rounding (comfyui/__init__.py:415-441 in the reference).  The rest as the module does it: q = norm_q(q(x)),
+    k = norm_k(k(x)), v = v(x), out = o(attention).  Calls with an attn1_patch (it wants the rotated q and k), another
+    head size, no table or a table that does not fit, tensors off the GPU, and every call after a failure go to the
+    original forward."""
+
+    def forward(x, freqs, transformer_options={}):  # noqa: B006 (the signature of the forward it replaces)
+        batch, tokens, heads, dim = *x.shape[:2], module.num_heads, module.head_dim
+        if (FAILED or transformer_options.get("patches", {}).get("attn1_patch") or freqs is None or dim != HEAD_DIM
+                or not x.is_cuda or freqs.dim() != 6 or freqs.shape[1] != tokens):
+            return original(x, freqs, transformer_options=transformer_options)
+        q = module.norm_q(module.q(x)).view(batch, tokens, heads, dim)
+        k = module.norm_k(module.k(x)).view(batch, tokens, heads, dim)
+        v = module.v(x).view(batch, tokens, heads, dim)
+        try:
+            out = unica.attention(*(t.transpose(1, 2).to(torch.bfloat16) for t in (q, k, v)), rope=freqs, **settings)
+        except UNICA_ERRORS as error:
+            log.error("unica failed, the model's own attention takes over: %s", error)
+            FAILED.append(error)
+            return original(x, freqs, transformer_options=transformer_options)
+        return module.o(out.transpose(1, 2).reshape(batch, tokens, heads * dim).to(x.dtype))
+
+    forward.unica, forward.original = True, original
+    return forward
+
+
+def patch_self_attention_forward(patched, settings: dict) -> int:
+    """fused_rope_forward on every WanSelfAttention of the model, as object patches of this clone only; returns how
+    many.  Cross-attention classes derive from WanSelfAttention and are left alone."""
+    blocks = patched.get_model_object("diffusion_model.blocks")
+    count = 0
+    for i in range(len(blocks)):
+        name = f"diffusion_model.blocks.{i}.self_attn"
+        module = patched.get_model_object(name)
+        if type(module).__name__ != "WanSelfAttention":
+            continue
+        original = patched.object_patches.get(f"{name}.forward", module.forward)
+        if getattr(original, "unica", False):  # patched before: wrap what was there before it
+            original = original.original
+        patched.add_object_patch(f"{name}.forward", fused_rope_forward(module, original, settings))
+        count += 1
+    return count
+
+
 class UnicaAttentionNative:
     @classmethod
     def INPUT_TYPES(cls):
         return {"required": {"model": ("MODEL",),
                              "enabled": ("BOOLEAN", {"default": True, "tooltip": "Off: the model as it came, for A/B runs"})},
-                "optional": dict(KERNEL_INPUTS)}
+                "optional": dict(KERNEL_INPUTS) | {
+                    "fuse_rope": ("BOOLEAN", {"default": False,
+                                              "tooltip": "WAN models: rotate q and k inside the quantization instead of "
+                                                         "in a pass of their own before attention"})}}
 
     RETURN_TYPES = ("MODEL",)
     RETURN_NAMES = ("model",)
@@ -167,7 +216,7 @@ class UnicaAttentionNative:
     DESCRIPTION = ("Self-attention on unica-b200 through optimized_attention_override.  Put it after other attention "
                    "patches: calls it does not take (cross-attention, masks) go to the override before it.")
 
-    def patch(self, model, enabled, v_scale="per_token", mode="accurate", vram_reserve_mb=0, **ignored):
+    def patch(self, model, enabled, v_scale="per_token", mode="accurate", vram_reserve_mb=0, fuse_rope=False, **ignored):
         if not enabled or checked().status == unica.UNSUPPORTED:
             return (model,)
         settings = choose_kernel(v_scale, mode, vram_reserve_mb)
@@ -177,6 +226,8 @@ class UnicaAttentionNative:
         if getattr(previous, "unica", False):  # patched before: wrap what was there before it, with the new settings
             previous = previous.previous
         options["optimized_attention_override"] = native_override(previous, settings)
+        if fuse_rope and not patch_self_attention_forward(patched, settings):
+            log.warning("fuse_rope: the model has no WanSelfAttention blocks; nothing fused")
         return (patched,)
 
 
