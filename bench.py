@@ -304,7 +304,12 @@ def main():
         written = {"per_channel": 3 * 128, "per_token": 3 * 128 + 8, "outliers": 3 * 128, "fast": 72 + 72 + 82}[args.mode]
         reads = {"per_channel": 5 * 256, "per_token": 4 * 256, "outliers": 6 * 256, "fast": 7 * 256}[args.mode]  # statistics passes read again
         # DRAM traffic of the attention kernel per launch: ncu on 40 heads x 8192 tokens (profiles/), scaled by heads x tokens
-        traffic = 544.3 * batch * heads * tokens / world if args.mode == "per_channel" else None
+        # (per channel: 126.52 MB read + 52.43 MB written; fast: 95.10 + 45.62 MB, the rest of the output still in L2)
+        traffic_per_token = {"per_channel": 546.1, "fast": 429.4}.get(args.mode)
+        traffic = traffic_per_token * batch * heads * tokens / world if traffic_per_token else None
+        # what the tensor pipe alone sustains on one tile's tcgen05.mma mix, measured now by the micro-benchmark
+        from unicaattention_b200 import peak as peak_bench
+        mix_tops = peak_bench.attention_mix_tops("fast" if args.mode == "fast" else "accurate", clocks.get("sm_max_mhz") or 1965.0) * world
         line = {
             "metric": metric_name(args, batch, heads, tokens), "value": value, "unit": "TOPS", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
@@ -312,7 +317,8 @@ def main():
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "roofline": {"bound": "tensor", "kernel": kernel_name, "achieved": achieved, "peak": peak, "unit": "TOP/s (x1e12)",
                          "frac": achieved / peak, "traffic": traffic, "traffic_unit": "bytes per launch per GPU", "ms_per_launch": ms_kernel,
-                         "peak_source": peak_source, "frac_of_nominal": achieved / (NOMINAL_PEAK_TOPS[args.mode] * world)},
+                         "peak_source": peak_source, "frac_of_nominal": achieved / (NOMINAL_PEAK_TOPS[args.mode] * world),
+                         "tensor_mix_microbench": mix_tops, "frac_of_tensor_mix_microbench": achieved / mix_tops},
             "quantization": {"ms": ms_quant, "algorithmic_gbs": (3 * 256 + written) * batch * heads * tokens / world / (ms_quant * 1e-3) / 1e9,
                              "moved_gbs": (reads + written) * batch * heads * tokens / world / (ms_quant * 1e-3) / 1e9,
                              "hbm_peak_gbs": peaks.get("hbm_gbs")},

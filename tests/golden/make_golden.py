@@ -2,7 +2,7 @@
 
 Run once where the reference checkout exists (it does not travel with the tests):
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 Everything is computed on CPU tensors, so scalar divisions are IEEE divisions (the oracle's recip=False form).  For each
 case the file holds the inputs (bf16 bits; the seed-0 headline case is regenerated from its seed and only its checksum
@@ -19,7 +19,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit(__doc__)
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "bench"))
 from emulate import FP4_SLOT_KEY, TODAY, block_scaled, emulate, errors, quant, reference, to_e2m1, to_fmt  # noqa: E402
 

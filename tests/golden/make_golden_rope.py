@@ -2,7 +2,7 @@
 the case of the reference's tests/test_rope.py (a WAN latent of 3 x 7 x 9 = 189 tokens, past a tile edge and a
 statistics block), on CPU tensors.
 
-    python tests/golden/make_golden_rope.py [/path/to/reference]
+    python tests/golden/make_golden_rope.py /path/to/reference
 
 Holds the inputs (bf16 bits), the emulator's own table (to pin the restated table builder), the rotated statistics,
 the quantizer pieces of the rotated tensors and the emulator's outputs for the accurate and fast contracts.
@@ -17,7 +17,9 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit(__doc__)
+REF = Path(sys.argv[1])
 sys.path.insert(0, str(REF / "bench"))
 from emulate import TODAY, block_scaled, emulate, errors, quant, reference, rope, wan_rope_table  # noqa: E402
 

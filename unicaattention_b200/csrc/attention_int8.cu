@@ -15,7 +15,7 @@
 // out = out * alpha + beta * float(acc) with alpha = 2^(m_old - m_new), beta = 2^(m_tile - m_new).
 // The 255 stays in numerator and denominator alike (as csrc/flash.cu:409-414 does).
 //
-// What bounds it (measured on B200, see the micro-benchmarks quoted in DESIGN.md): ex2 issues once per 8 cycles per
+// What bounds it (measured on B200 with the micro-benchmarks of peak.cu): ex2 issues once per 8 cycles per
 // scheduler, float->int conversions too, so the loop has no conversion instruction at all (MAGIC in common.cuh) and
 // the exponentials are the busiest unit; a tensor-memory load costs ~180 cycles of latency, so the flush prefetches.
 //
