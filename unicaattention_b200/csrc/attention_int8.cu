@@ -226,8 +226,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         TRACE_DECL;
 
         // Every accumulator starts at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
-#pragma unroll
-        for (int c = 0; c < 256; c += 32) tmem_fill32(t_scores + c, MAGIC_BITS);
+        uint32_t magic[FILL_BLOCK];
+        fill_block_init(magic, MAGIC_BITS);
+        tmem_fill<256>(t_scores, magic);
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.s_free[g][0]);
@@ -251,8 +252,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             if constexpr (V_TOKEN) {
                 float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
                 tmem_ld64_sync(t_scores + buf * 64, x);
-                tmem_fill32(t_scores + buf * 64, MAGIC_BITS);  // completes while the maximum is taken
-                tmem_fill32(t_scores + buf * 64 + 32, MAGIC_BITS);
+                tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // completes while the maximum is taken
                 TRACE(TR_LOAD_S);
 
                 const float2 c2 = make_float2(c, c);
@@ -362,8 +362,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     if (chunk + 1 < KEY_TILE / 16) {
                         tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
                     } else {  // every score has been read: refill the buffer (the wait comes after this chunk's arithmetic)
-                        tmem_fill32(t_scores + buf * 64, MAGIC_BITS);
-                        tmem_fill32(t_scores + buf * 64 + 32, MAGIC_BITS);
+                        tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);
                     }
                     uint32_t w[4];
     #pragma unroll
@@ -431,7 +430,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 if (part + 4 < HEAD_DIM / 16) tmem_ld16_async(t_acc + (part + 4) * 16, a[part % 4]);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) o[part * 8 + i] = fma2(beta2, f[i], o[part * 8 + i]);
-                if (part % 2 == 1) tmem_fill32(t_acc + (part - 1) * 16, MAGIC_BITS);
+                if (part % 2 == 1) tmem_fill<32>(t_acc + (part - 1) * 16, magic);
             }
             tmem_wait_st();
             tc_fence_before();

@@ -11,6 +11,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifndef UNICA_FILL_BLOCK
+#define UNICA_FILL_BLOCK 8
+#endif
+
 namespace unica {
 
 constexpr int HEAD_DIM = 128;
@@ -261,6 +265,33 @@ __device__ __forceinline__ void tmem_fill32(uint32_t taddr, uint32_t v) {
         "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr),
         "r"(v)
         : "memory");
+}
+
+// The same from a block of registers the caller keeps alive: tcgen05.st takes consecutive registers, so a single value
+// would be copied into as many registers before every store.  fill_block_init() makes the block; the `volatile` moves
+// keep the compiler from folding it back into one register.
+constexpr int FILL_BLOCK = UNICA_FILL_BLOCK;
+__device__ __forceinline__ void fill_block_init(uint32_t (&r)[FILL_BLOCK], uint32_t v) {
+#pragma unroll
+    for (int i = 0; i < FILL_BLOCK; ++i) asm volatile("mov.b32 %0, %1;" : "=r"(r[i]) : "r"(v));
+}
+__device__ __forceinline__ void tmem_fill_block(uint32_t taddr, const uint32_t (&r)[FILL_BLOCK]) {
+#if UNICA_FILL_BLOCK == 16
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+                 "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+                 "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+#else
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+                 "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+#endif
+}
+// `columns` (a multiple of FILL_BLOCK) consecutive columns of this thread's lane set to the block's value.
+template <int COLUMNS>
+__device__ __forceinline__ void tmem_fill(uint32_t taddr, const uint32_t (&r)[FILL_BLOCK]) {
+#pragma unroll
+    for (int c = 0; c < COLUMNS; c += FILL_BLOCK) tmem_fill_block(taddr + c, r);
 }
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
