@@ -43,6 +43,31 @@ constexpr int F4_TMEM_COLUMNS = 512;
 constexpr int F4_S = 0, F4_O = 64, F4_SFQ = 208, F4_SFK = 216, F4_SFP = 220, F4_SFV = 224;
 constexpr float P_LOG2_GAIN = 10.0f;  // P is taken times 2^10: its block scales (up to 1024 / 6) stay below e4m3's 448
 
+// -DUNICA_TRACE: the first thread of each warpgroup of block (0, 0) adds up the cycles of each phase of its tile loop
+// in registers and leaves the totals in g_trace_fp4 (see attention_int8.cu for the accurate kernel's).
+#ifdef UNICA_TRACE
+__device__ long long g_trace_fp4[4][8];
+#define F4_TRACE_DECL long long trace_t0 = clock64(), trace_sum[8] = {}; const bool tracing = blockIdx.x == 0 && blockIdx.y == 0 && row == 0
+#define F4_TRACE(phase)                              \
+    do {                                             \
+        if (tracing) {                               \
+            const long long now = clock64();         \
+            trace_sum[phase] += now - trace_t0;      \
+            trace_t0 = now;                          \
+        }                                            \
+    } while (0)
+#define F4_TRACE_END(slot)                                                    \
+    do {                                                                      \
+        if (tracing)                                                          \
+            for (int i = 0; i < 8; ++i) g_trace_fp4[slot][i] = trace_sum[i];  \
+    } while (0)
+#else
+#define F4_TRACE_DECL
+#define F4_TRACE(phase)
+#define F4_TRACE_END(slot)
+#endif
+enum { F4_TR_WAIT_S = 0, F4_TR_LOAD_S = 1, F4_TR_MAX = 2, F4_TR_QUANTIZE = 3, F4_TR_WAIT_O = 4, F4_TR_RESCALE = 5, F4_TR_EXCHANGE = 6, F4_TR_OTHER = 7 };
+
 struct __align__(128) Fp4Smem {
     uint8_t q[2][Q4_BYTES];
     uint32_t sfq[2][2][QUERY_TILE];
@@ -210,12 +235,15 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             mbar_arrive(&sm.s_free[g]);
         }
 
+        F4_TRACE_DECL;
         for (int t = 0; ok && t < k_tiles; ++t) {
             const int stage = t % F4_STAGES;
+            F4_TRACE(F4_TR_OTHER);
             ok = mbar_wait_warp(&sm.s_full[g], t & 1, abort_flag, status, STATUS_WAIT_SCORES) &&
                  mbar_wait_warp(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
             if (!ok) break;
             tc_fence_after();
+            F4_TRACE(F4_TR_WAIT_S);
             float2 x[KEY_TILE / 2];
             tmem_ld64_sync(my + F4_S, x);
             if (t + 1 < k_tiles) {  // the next K tile's scale bytes, then the scores buffer goes back
@@ -227,6 +255,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             }
             tc_fence_before();
             mbar_arrive(&sm.s_free[g]);
+            F4_TRACE(F4_TR_LOAD_S);
 
             // scores in the log2 domain, the smoothing term added back, slots past the last key out of the maximum
             if (smoothed) {
@@ -255,6 +284,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             const float m_new = fmaxf(m, fmaxf(fmaxf(block_max[0], block_max[1]), fmaxf(block_max[2], block_max[3])));
             const float alpha = ex2(m - m_new);
             m = m_new;
+            F4_TRACE(F4_TR_MAX);
 
             // P in NVFP4: per 16 slots a scale byte e4m3(max P / 6), then the codes straight out of the exponent
             uint32_t codes[8], sf_word = 0;
@@ -282,10 +312,12 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 }
             }
 
+            F4_TRACE(F4_TR_QUANTIZE);
             if (t > 0) {  // P.V of the previous tile must have read P, its scales and V's, and written O
                 ok = mbar_wait_warp(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
                 if (!ok) break;
                 tc_fence_after();
+                F4_TRACE(F4_TR_WAIT_O);
                 if (!__all_sync(0xffffffffu, alpha == 1.0f)) {  // the maximum moved: O and the denominator shrink
                     const float2 alpha2 = make_float2(alpha, alpha);
 #pragma unroll
@@ -298,6 +330,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                     }
                 }
             }
+            F4_TRACE(F4_TR_RESCALE);
             uint8_t* p_row = sm.p[g] + row * 16;
             *reinterpret_cast<uint4*>(p_row) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
             *reinterpret_cast<uint4*>(p_row + QUERY_TILE * 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
@@ -313,7 +346,9 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             tc_fence_before();
             fence_proxy_async();
             mbar_arrive(&sm.p_ready[g]);
+            F4_TRACE(F4_TR_EXCHANGE);
         }
+        F4_TRACE_END(g);
 
         if (ok) ok = mbar_wait_warp(&sm.o_full[g], (k_tiles - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
         if (ok) {
@@ -354,6 +389,16 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 }  // namespace unica
 
 using namespace unica;
+
+#ifdef UNICA_TRACE
+// Trace builds only: copies the per-phase cycle totals of block (0, 0) to `host_out` (4 x 8 long long) and clears them.
+extern "C" int unica_b200_trace_read_fp4(long long* host_out) {
+    if (cudaMemcpyFromSymbol(host_out, g_trace_fp4, sizeof(long long) * 32) != cudaSuccess) return unica_check_launch("trace_read_fp4");
+    static const long long zeros[32] = {};
+    if (cudaMemcpyToSymbol(g_trace_fp4, zeros, sizeof zeros) != cudaSuccess) return unica_check_launch("trace_read_fp4");
+    return UNICA_B200_OK;
+}
+#endif
 
 extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
                                         const void* sfv, const float* qk_outer, const float* v_outer, const float* bias,
