@@ -28,8 +28,10 @@
 
 namespace unica {
 
-constexpr int F4_THREADS = 384;
-constexpr int F4_PRODUCER_WARP = 8, F4_MMA_WARP = 9;
+constexpr int F4_COMPUTE_WARPS = 16;  // 2 query tiles x 2 threads per row x 4 warps
+constexpr int F4_THREADS = (F4_COMPUTE_WARPS + 4) * 32;
+constexpr int F4_PRODUCER_WARP = F4_COMPUTE_WARPS, F4_MMA_WARP = F4_COMPUTE_WARPS + 1;
+constexpr int F4_HALF_SLOTS = KEY_TILE / 2;  // what one of a row's two threads takes
 constexpr int F4_STAGES = 3;
 constexpr int Q4_BYTES = QUERY_TILE * HEAD_DIM / 2;  // 8192
 constexpr int SFQ_BYTES = 2 * QUERY_TILE * 4;        // 1024
@@ -78,6 +80,7 @@ struct __align__(128) Fp4Smem {
     float bias[F4_STAGES][KEY_TILE];
     uint8_t p[2][P4_BYTES];
     uint32_t sfp[2][QUERY_TILE];
+    uint2 exchange[2][2][2][QUERY_TILE];  // [query tile][tag parity][thread of the row][row] = {tag, value}
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
     uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], sfp_ready[2], drain[2];
     uint32_t tmem_base;
@@ -124,15 +127,16 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         }
         for (int g = 0; g < 2; ++g) {
             mbar_init(&sm.s_full[g], 1);
-            mbar_init(&sm.s_free[g], 128);
-            mbar_init(&sm.p_ready[g], 128);
+            mbar_init(&sm.s_free[g], 2 * QUERY_TILE);  // both threads of every row
+            mbar_init(&sm.p_ready[g], 2 * QUERY_TILE);
             mbar_init(&sm.o_full[g], 1);
-            mbar_init(&sm.sfp_ready[g], 128);
+            mbar_init(&sm.sfp_ready[g], 2 * QUERY_TILE);
         }
         mbar_init(&sm.drain[0], 1);
         mbar_init(&sm.drain[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    for (int i = threadIdx.x; i < 2 * 2 * 2 * QUERY_TILE; i += F4_THREADS) (&sm.exchange[0][0][0][0])[i] = make_uint2(0xffffffffu, 0u);  // no tag
     if (warp == F4_MMA_WARP) tmem_alloc(&sm.tmem_base, F4_TMEM_COLUMNS);
     tc_fence_before();
     __syncthreads();
@@ -214,9 +218,13 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 mbar_wait(&sm.drain[g], 0, &never, nullptr, 0);
             }
         }
-    } else if (warp < 8) {
+    } else if (warp < F4_COMPUTE_WARPS) {
         // ------------------------------------------------------------------------------------------------ softmax
-        const int g = warp / 4, row = threadIdx.x % 128;
+        // Two threads per query row: warp = 8 g + 4 half + quarter, both on tensor-memory lane 32 quarter + lane.  Thread
+        // `half` takes slots 32 half .. 32 half + 31 of every tile (two scale blocks of P) and output channels 64 half ..
+        // 64 half + 63; the two meet in one number per tile, the maximum of their scores (a tagged word in shared memory).
+        // Half 0 also stores K's and P's scale bytes into tensor memory, half 1 V's.
+        const int g = warp / 8, half = (warp / 4) % 2, row = (warp % 4) * 32 + lane;
         const int q_row = (2 * blockIdx.x + g) * QUERY_TILE + row;
         const uint32_t my = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256;
         const float c = qk_outer[head] * scale_log2;
@@ -226,14 +234,43 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         bool ok = mbar_wait_warp(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
                   mbar_wait_warp(&sm.k_full[0], 0, abort_flag, status, STATUS_WAIT_TILE);
         if (ok) {  // scale bytes of Q (for the whole loop) and of the first K tile
+            if (half == 0) {
 #pragma unroll
-            for (int s = 0; s < 2; ++s)
-                tmem_st4(my + F4_SFQ + 4 * s, sm.sfq[g][s][lane], sm.sfq[g][s][32 + lane], sm.sfq[g][s][64 + lane], sm.sfq[g][s][96 + lane]);
-            tmem_st4(my + F4_SFK, sm.sfk[0][0][lane], sm.sfk[0][0][32 + lane], sm.sfk[0][1][lane], sm.sfk[0][1][32 + lane]);
-            tmem_wait_st();
+                for (int s = 0; s < 2; ++s)
+                    tmem_st4(my + F4_SFQ + 4 * s, sm.sfq[g][s][lane], sm.sfq[g][s][32 + lane], sm.sfq[g][s][64 + lane], sm.sfq[g][s][96 + lane]);
+                tmem_st4(my + F4_SFK, sm.sfk[0][0][lane], sm.sfk[0][0][32 + lane], sm.sfk[0][1][lane], sm.sfk[0][1][32 + lane]);
+                tmem_wait_st();
+            }
             tc_fence_before();
             mbar_arrive(&sm.s_free[g]);
         }
+
+        // This thread's `value` for `tag` goes to its partner, the partner's comes back (false: gave up waiting).
+        // One 8-byte word {tag, value} per thread and tag parity: a word is written again two tags later, after the
+        // partner has read it (the partner reads tag n before it writes tag n + 1, which this thread waits for).
+        auto exchange = [&](int tag, float value, float& partner) -> bool {
+            const uint32_t mine = smem_u32(&sm.exchange[g][tag & 1][half][row]);
+            const uint32_t theirs = smem_u32(&sm.exchange[g][tag & 1][half ^ 1][row]);
+            asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(mine), "r"(uint32_t(tag)), "r"(__float_as_uint(value)) : "memory");
+            bool got = false;
+            const long long start = clock64();
+            while (true) {
+                uint2 w;
+                asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "r"(theirs) : "memory");
+                if (w.x == uint32_t(tag)) {
+                    partner = __uint_as_float(w.y);
+                    got = true;
+                    break;
+                }
+                if (*abort_flag) break;
+                if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                    *abort_flag = 1;
+                    if (status) atomicCAS(status, 0, int(STATUS_WAIT_PARTNER));
+                    break;
+                }
+            }
+            return __all_sync(0xffffffffu, got);
+        };
 
         F4_TRACE_DECL;
         for (int t = 0; ok && t < k_tiles; ++t) {
@@ -244,9 +281,11 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             if (!ok) break;
             tc_fence_after();
             F4_TRACE(F4_TR_WAIT_S);
-            float2 x[KEY_TILE / 2];
-            tmem_ld64_sync(my + F4_S, x);
-            if (t + 1 < k_tiles) {  // the next K tile's scale bytes, then the scores buffer goes back
+            float2 x[F4_HALF_SLOTS / 2];
+            tmem_ld32_async(my + F4_S + half * F4_HALF_SLOTS, x);
+            tmem_wait_ld();
+            reg_fence16(x);
+            if (half == 0 && t + 1 < k_tiles) {  // the next K tile's scale bytes, then the scores buffer goes back
                 const int next = (t + 1) % F4_STAGES;
                 ok = mbar_wait_warp(&sm.k_full[next], ((t + 1) / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
                 if (!ok) break;
@@ -259,38 +298,42 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 
             // scores in the log2 domain, the smoothing term added back, slots past the last key out of the maximum
             if (smoothed) {
-                const float2* b2 = reinterpret_cast<const float2*>(sm.bias[stage]);
+                const float2* b2 = reinterpret_cast<const float2*>(sm.bias[stage]) + half * (F4_HALF_SLOTS / 2);
 #pragma unroll
-                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(x[j], c2, b2[j]);
+                for (int j = 0; j < F4_HALF_SLOTS / 2; ++j) x[j] = fma2(x[j], c2, b2[j]);
             } else {
 #pragma unroll
-                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = mul2(x[j], c2);
+                for (int j = 0; j < F4_HALF_SLOTS / 2; ++j) x[j] = mul2(x[j], c2);
             }
             if ((t + 1) * KEY_TILE > n_keys) {
 #pragma unroll
-                for (int j = 0; j < KEY_TILE; ++j) {
-                    const int key = t * KEY_TILE + 32 * (j / 32) + 8 * (j % 8 / 2) + 2 * (j % 32 / 8) + j % 2;  // slot -> key
+                for (int j = 0; j < F4_HALF_SLOTS; ++j) {
+                    const int key = t * KEY_TILE + 32 * half + 8 * (j % 8 / 2) + 2 * (j / 8) + j % 2;  // slot 32 half + j -> key
                     if (key >= n_keys) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
                 }
             }
-            float block_max[4];
+            float block_max[2];
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
+            for (int b = 0; b < 2; ++b) {
                 float top = fmaxf(x[8 * b].x, x[8 * b].y);
 #pragma unroll
                 for (int i = 1; i < 8; ++i) top = max3(top, x[8 * b + i].x, x[8 * b + i].y);
                 block_max[b] = top;
             }
-            const float m_new = fmaxf(m, fmaxf(fmaxf(block_max[0], block_max[1]), fmaxf(block_max[2], block_max[3])));
+            const float mine = fmaxf(block_max[0], block_max[1]);
+            float theirs = mine;
+            ok = exchange(t, mine, theirs);
+            if (!ok) break;
+            const float m_new = fmaxf(m, fmaxf(mine, theirs));
             const float alpha = ex2(m - m_new);
             m = m_new;
             F4_TRACE(F4_TR_MAX);
 
             // P in NVFP4: per 16 slots a scale byte e4m3(max P / 6), then the codes straight out of the exponent
-            uint32_t codes[8], sf_word = 0;
+            uint32_t codes[4], sf_pair = 0;
             const float2 gain2 = make_float2(P_LOG2_GAIN - m_new, P_LOG2_GAIN - m_new);
 #pragma unroll
-            for (int b = 0; b < 4; ++b) {
+            for (int b = 0; b < 2; ++b) {
                 const float top = ex2(block_max[b] - m_new + P_LOG2_GAIN) * (1.0f / 6.0f);
                 const uint32_t byte = __nv_cvt_float_to_fp8(top, __NV_SATFINITE, __NV_E4M3);
                 const float sp = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3)));
@@ -298,7 +341,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 // factors lands on the other side of an e2m1 tie far less often than 2^(x - m + 10 - log2 sp) does
                 const float inv = sp > 0.0f ? __fdiv_rn(1.0f, sp) : 0.0f;
                 const float2 inv2 = make_float2(inv, inv);
-                sf_word |= byte << (8 * b);
+                sf_pair |= byte << (8 * b);
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     uint32_t word = 0;
@@ -311,8 +354,8 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                     codes[2 * b + w] = word;
                 }
             }
-
             F4_TRACE(F4_TR_QUANTIZE);
+
             if (t > 0) {  // P.V of the previous tile must have read P, its scales and V's, and written O
                 ok = mbar_wait_warp(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
                 if (!ok) break;
@@ -320,28 +363,42 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 F4_TRACE(F4_TR_WAIT_O);
                 if (!__all_sync(0xffffffffu, alpha == 1.0f)) {  // the maximum moved: O and the denominator shrink
                     const float2 alpha2 = make_float2(alpha, alpha);
+                    const uint32_t mine_o = my + F4_O + half * (V4_TILE_ROWS / 2);  // 72 columns each: 32 + 40
+                    float2 o[2][8], tail[4];
 #pragma unroll
-                    for (int part = 0; part < V4_TILE_ROWS / 16; ++part) {
-                        float2 o[8];
-                        tmem_ld16_sync(my + F4_O + part * 16, o);
+                    for (int round = 0; round < 2; ++round) {
+                        tmem_ld16_async(mine_o + round * 32, o[0]);
+                        tmem_ld16_async(mine_o + round * 32 + 16, o[1]);
+                        if (round) tmem_ld8_async(mine_o + 64, tail);
+                        tmem_wait_ld();
+                        reg_fence8(o[0]);
+                        reg_fence8(o[1]);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) o[i] = mul2(o[i], alpha2);
-                        tmem_st16(my + F4_O + part * 16, o);
+                        for (int i = 0; i < 16; ++i) o[i / 8][i % 8] = mul2(o[i / 8][i % 8], alpha2);
+                        tmem_st16(mine_o + round * 32, o[0]);
+                        tmem_st16(mine_o + round * 32 + 16, o[1]);
+                        if (round) {
+                            reg_fence4(tail);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) tail[i] = mul2(tail[i], alpha2);
+                            tmem_st8(mine_o + 64, tail);
+                        }
                     }
                 }
             }
-            F4_TRACE(F4_TR_RESCALE);
-            uint8_t* p_row = sm.p[g] + row * 16;
-            *reinterpret_cast<uint4*>(p_row) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-            *reinterpret_cast<uint4*>(p_row + QUERY_TILE * 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-            // every 32-lane quarter of tensor memory needs the scale bytes of all 128 rows: exchange them through shared memory
-            sm.sfp[g][row] = sf_word;
+            // P.V of the previous tile has read P^: this tile's codes and scale bytes may take its place
+            *reinterpret_cast<uint4*>(sm.p[g] + half * (QUERY_TILE * 16) + row * 16) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+            reinterpret_cast<uint16_t*>(&sm.sfp[g][row])[half] = uint16_t(sf_pair);  // bytes 2 half, 2 half + 1 of the row's word
             mbar_arrive(&sm.sfp_ready[g]);  // an mbarrier, not bar.sync: its wait is bounded like every other
-            ok = mbar_wait_warp(&sm.sfp_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
-            if (!ok) break;
-            tmem_st4(my + F4_SFP, sm.sfp[g][lane], sm.sfp[g][32 + lane], sm.sfp[g][64 + lane], sm.sfp[g][96 + lane]);
-            tmem_st4(my + F4_SFV, sm.sfv[stage][lane], sm.sfv[stage][32 + lane], sm.sfv[stage][64 + lane], sm.sfv[stage][96 + lane]);
-            tmem_st1(my + F4_SFV + 4, sm.sfv[stage][128 + lane]);
+            F4_TRACE(F4_TR_RESCALE);
+            if (half == 0) {  // every 32-lane quarter of tensor memory needs the scale bytes of all 128 rows of P
+                ok = mbar_wait_warp(&sm.sfp_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
+                if (!ok) break;
+                tmem_st4(my + F4_SFP, sm.sfp[g][lane], sm.sfp[g][32 + lane], sm.sfp[g][64 + lane], sm.sfp[g][96 + lane]);
+            } else {  // and of V's 144 rows
+                tmem_st4(my + F4_SFV, sm.sfv[stage][lane], sm.sfv[stage][32 + lane], sm.sfv[stage][64 + lane], sm.sfv[stage][96 + lane]);
+                tmem_st1(my + F4_SFV + 4, sm.sfv[stage][128 + lane]);
+            }
             tmem_wait_st();
             tc_fence_before();
             fence_proxy_async();
@@ -354,20 +411,20 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         if (ok) {
             tc_fence_after();
             const bool valid_row = q_row < n_queries;
-            __nv_bfloat16* dst = out + out_layout.offset(head, valid_row ? q_row : 0);
+            __nv_bfloat16* dst = out + out_layout.offset(head, valid_row ? q_row : 0) + half * (HEAD_DIM / 2);
+            const float* scale = v_outer + head * HEAD_DIM + half * (HEAD_DIM / 2);
             float2 last[8];
             tmem_ld16_sync(my + F4_O + HEAD_DIM, last);  // column 128: the sum of P^
             const float inv = 1.0f / last[0].x;
 #pragma unroll
-            for (int part = 0; part < HEAD_DIM / 16; ++part) {
+            for (int part = 0; part < HEAD_DIM / 32; ++part) {
                 float2 o[8];
-                tmem_ld16_sync(my + F4_O + part * 16, o);
+                tmem_ld16_sync(my + F4_O + half * (HEAD_DIM / 2) + part * 16, o);
                 uint32_t w[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int c0 = part * 16 + 2 * i;
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i].x * v_outer[head * HEAD_DIM + c0] * inv,
-                                                                      o[i].y * v_outer[head * HEAD_DIM + c0 + 1] * inv);
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i].x * scale[c0] * inv, o[i].y * scale[c0 + 1] * inv);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pair);
                 }
                 if (valid_row) {

@@ -20,6 +20,8 @@
 // the exponentials are the busiest unit; a tensor-memory load costs ~180 cycles of latency, so the flush prefetches.
 //
 // Tensor memory: 512 columns = per warpgroup S x 2 (64 each) + acc (128).  All waits are bounded (common.cuh).
+#include <type_traits>
+
 #include "capi.h"
 
 namespace unica {
@@ -353,37 +355,46 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 unsigned isum[2] = {0, 0};
                 float2 fsum = make_float2(0.0f, 0.0f);
                 // Pass 2: P^ = rint(255 * 2^(x - tile max)), 16 keys per step, the next 16 scores loading meanwhile.
-                float2 x[2][8];
-                tmem_ld16_async(t_scores + buf * 64, x[0]);
-    #pragma unroll
-                for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
-                    tmem_wait_ld();
-                    reg_fence8(x[chunk % 2]);
-                    if (chunk + 1 < KEY_TILE / 16) {
-                        tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
-                    } else {  // every score has been read: refill the buffer (the wait comes after this chunk's arithmetic)
-                        tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);
-                    }
-                    uint32_t w[4];
-    #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t half[2];
-    #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const float2 e = fma2(add2(x[chunk % 2][i * 2 + h], minus_magic), c2, offset2);
-                            const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                            const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
-                            half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
+                // The masking of a ragged last tile is compiled apart: a test inside the loop would cut it into short
+                // basic blocks and leave the exponentials' latency exposed on every tile.
+                auto pass2 = [&](auto masked) {
+                    constexpr bool MASKED = decltype(masked)::value;
+                    float2 x[2][8];
+                    tmem_ld16_async(t_scores + buf * 64, x[0]);
+#pragma unroll
+                    for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
+                        tmem_wait_ld();
+                        reg_fence8(x[chunk % 2]);
+                        if (chunk + 1 < KEY_TILE / 16) {
+                            tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
+                        } else {  // every score has been read: refill the buffer (the wait comes after this chunk's arithmetic)
+                            tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);
                         }
-                        w[i] = __byte_perm(half[0], half[1], 0x5410);
-                        if (valid < KEY_TILE) {  // keys past the end weigh nothing
-                            const int left = valid - (chunk * 16 + i * 4);
-                            w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
+                        uint32_t w[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t half[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const float2 e = fma2(add2(x[chunk % 2][i * 2 + h], minus_magic), c2, offset2);
+                                const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                                const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
+                                half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
+                            }
+                            w[i] = __byte_perm(half[0], half[1], 0x5410);
+                            if (MASKED) {  // keys past the end weigh nothing
+                                const int left = valid - (chunk * 16 + i * 4);
+                                w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
+                            }
+                            isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
                         }
-                        isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
+                        *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
+                };
+                if (valid < KEY_TILE)
+                    pass2(std::true_type{});
+                else
+                    pass2(std::false_type{});
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sm.s_free[g][buf]);

@@ -67,6 +67,7 @@ enum Status : int {
     STATUS_WAIT_PV = 4,       // P.V never completed
     STATUS_WAIT_FREE = 5,     // a buffer was never released
     STATUS_WAIT_STAGE = 6,    // the producer never got a stage back
+    STATUS_WAIT_PARTNER = 7,  // the other thread of a query row never published its value
 };
 
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second
@@ -256,6 +257,23 @@ __device__ __forceinline__ void reg_fence8(float2 (&v)[8]) {
                    "+f"(v[4].x), "+f"(v[4].y), "+f"(v[5].x), "+f"(v[5].y), "+f"(v[6].x), "+f"(v[6].y), "+f"(v[7].x), "+f"(v[7].y)
                  :
                  : "memory");
+}
+
+// 8 consecutive columns as 4 float2: load issued without waiting (tmem_wait_ld() then reg_fence4() before the first
+// use) / store.
+__device__ __forceinline__ void tmem_ld8_async(uint32_t taddr, float2 (&v)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=f"(v[0].x), "=f"(v[0].y), "=f"(v[1].x), "=f"(v[1].y), "=f"(v[2].x), "=f"(v[2].y), "=f"(v[3].x), "=f"(v[3].y)
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const float2 (&v)[4]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "f"(v[0].x), "f"(v[0].y),
+                 "f"(v[1].x), "f"(v[1].y), "f"(v[2].x), "f"(v[2].y), "f"(v[3].x), "f"(v[3].y)
+                 : "memory");
+}
+__device__ __forceinline__ void reg_fence4(float2 (&v)[4]) {
+    asm volatile("" : "+f"(v[0].x), "+f"(v[0].y), "+f"(v[1].x), "+f"(v[1].y), "+f"(v[2].x), "+f"(v[2].y), "+f"(v[3].x), "+f"(v[3].y) : : "memory");
 }
 
 // 32 consecutive columns of this thread's lane set to one value.

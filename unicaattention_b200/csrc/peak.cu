@@ -128,7 +128,7 @@ extern "C" int unica_b200_peak(int kind, int n, int count, int blocks, double* c
         if (kind % 100 <= PEAK_NVF4)
             peak_mma_kernel<<<blocks, 128, (128 + n) * 128 + 1024 + 128, s>>>(kind % 100, n, count, kind / 100 % 100, kind / 10000, cycles, status);
         else
-            peak_scalar_kernel<<<blocks, 512, 0, s>>>(kind, count, cycles, sink, 0.3f);
+            peak_scalar_kernel<<<blocks, 128 * (n >= 1 && n <= 4 ? n : 4), 0, s>>>(kind, count, cycles, sink, 0.3f);  // n: warps per scheduler
     }
     long long host[1024];
     cudaError_t e = cudaMemcpyAsync(host, cycles, sizeof(long long) * blocks, cudaMemcpyDeviceToHost, s);
@@ -143,6 +143,6 @@ extern "C" int unica_b200_peak(int kind, int n, int count, int blocks, double* c
     const long long median = host[blocks / 2];
     if (median < 0) return unica_fail(UNICA_B200_ERR_KERNEL, "peak: the tensor-core chain never completed");
     // scalar kinds: 8 chains x 4 warps per scheduler -> per warp instruction per scheduler
-    *cycles_per_instruction = kind % 100 <= PEAK_NVF4 ? double(median) / count : double(median) / (double(count) * 8 * 4);
+    *cycles_per_instruction = kind % 100 <= PEAK_NVF4 ? double(median) / count : double(median) / (double(count) * 8 * (n >= 1 && n <= 4 ? n : 4));
     return UNICA_B200_OK;
 }
