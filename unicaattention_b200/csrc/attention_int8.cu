@@ -247,6 +247,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             const float c = (sq * sk_reg) * scale_log2;
             if (t + 1 < k_tiles) sk_reg = load_scale(sk + t + 1);
             TRACE(TR_OTHER);
+#ifdef UNICA_ALTERNATE
+            // The two query tiles take turns: tile 1 starts its softmax of key tile t when tile 0 has delivered its P^(t),
+            // tile 0 its softmax of t + 1 when tile 1 has delivered P^(t).
+            if (g == 1) {
+                if (!mbar_wait_warp(&sm.p_ready[0][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P)) return false;
+            } else if (t > 0) {
+                if (!mbar_wait_warp(&sm.p_ready[1][(t - 1) & 1], ((t - 1) >> 1) & 1, abort_flag, status, STATUS_WAIT_P)) return false;
+            }
+#endif
             if (!mbar_wait_warp(&sm.s_full[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
             if (V_TOKEN && !mbar_wait_warp(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
             tc_fence_after();
@@ -327,23 +336,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 den = den * alpha + (fsum.x + fsum.y) * beta;
             } else {
                 const float2 c2 = make_float2(c, c);
+                float2 x[KEY_TILE / 2];  // MAGIC + score, exactly; kept from the maximum to the exponentials
+                tmem_ld64_sync(t_scores + buf * 64, x);
+                tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // completes while the maximum is taken
+                if (valid < KEY_TILE) {  // keys past the end: below every real score (|score| < 2^21)
+#pragma unroll
+                    for (int j = 0; j < KEY_TILE; ++j)
+                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = MAGIC - 4194303.0f;
+                }
                 float tile_max;
-                {   // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels already fill most
-                    // of the register file, so pass 2 reads the scores again, 16 at a time.
-                    float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
-                    tmem_ld64_sync(t_scores + buf * 64, x);
-                    if (valid < KEY_TILE) {  // keys past the end: below every real score (|score| < 2^21)
-    #pragma unroll
-                        for (int j = 0; j < KEY_TILE; ++j)
-                            if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = MAGIC - 4194303.0f;
-                    }
+                {
                     float top[4];
-    #pragma unroll
+#pragma unroll
                     for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
-    #pragma unroll
+#pragma unroll
                     for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
                     tile_max = (fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) - MAGIC) * c;
                 }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.s_free[g][buf]);  // the scores of tile t + 2 may be written from here on
                 TRACE(TR_LOAD_S);
                 const float m_new = fmaxf(m, tile_max);
                 alpha = ex2(m - m_new);
@@ -353,30 +365,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 const float2 offset2 = make_float2(offset, offset);
                 uint8_t* p_row = sm.p[g][buf] + row * 16;
                 unsigned isum[2] = {0, 0};
-                float2 fsum = make_float2(0.0f, 0.0f);
-                // Pass 2: P^ = rint(255 * 2^(x - tile max)), 16 keys per step, the next 16 scores loading meanwhile.
-                // The masking of a ragged last tile is compiled apart: a test inside the loop would cut it into short
-                // basic blocks and leave the exponentials' latency exposed on every tile.
+                // P^ = rint(255 * 2^(x - tile max)): one straight run over the 64 keys.  The masking of a ragged last
+                // tile is compiled apart: a test inside the loop would cut it into short basic blocks and leave the
+                // exponentials' latency exposed on every tile.
                 auto pass2 = [&](auto masked) {
                     constexpr bool MASKED = decltype(masked)::value;
-                    float2 x[2][8];
-                    tmem_ld16_async(t_scores + buf * 64, x[0]);
 #pragma unroll
                     for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
-                        tmem_wait_ld();
-                        reg_fence8(x[chunk % 2]);
-                        if (chunk + 1 < KEY_TILE / 16) {
-                            tmem_ld16_async(t_scores + buf * 64 + (chunk + 1) * 16, x[(chunk + 1) % 2]);
-                        } else {  // every score has been read: refill the buffer (the wait comes after this chunk's arithmetic)
-                            tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);
-                        }
                         uint32_t w[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint32_t half[2];
 #pragma unroll
                             for (int h = 0; h < 2; ++h) {
-                                const float2 e = fma2(add2(x[chunk % 2][i * 2 + h], minus_magic), c2, offset2);
+                                const float2 e = fma2(add2(x[chunk * 8 + i * 2 + h], minus_magic), c2, offset2);
                                 const float2 p = make_float2(ex2(e.x), ex2(e.y));
                                 const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
                                 half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
@@ -395,9 +397,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     pass2(std::true_type{});
                 else
                     pass2(std::false_type{});
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&sm.s_free[g][buf]);
                 TRACE(TR_SOFTMAX);
                 fence_proxy_async();
                 mbar_arrive(&sm.p_ready[g][buf]);
