@@ -240,171 +240,290 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         // alternate between the exponentials and the flush instead of competing for the same unit at the same time.
         if (g == 1) ok = mbar_wait_warp(&sm.p_ready[0][0], 0, abort_flag, status, STATUS_WAIT_P);
 
-        // One step of the loop: the scores of key tile `ts` become P^ in shared memory (SOFT) while the accumulator of
-        // tile `tf` is flushed into `out` (FLUSH).  In the steady state both happen, interleaved 16 keys and 32 channels
-        // at a time in one straight run of instructions, so that the exponentials (XU), the flush's multiply-adds (FMA
-        // pipe) and the packing (ALU) overlap inside one warp, and one wait covers the tensor-memory loads of both.
-        // Every choice is a template argument: a test inside the run would cut it into short basic blocks and leave
-        // the latencies exposed.  alpha_s, beta_s: of tile ts, for its flush one step later.
-        auto tile_step = [&](auto soft_c, auto flush_c, auto masked_c, auto rescale_c, int ts, int tf, float& alpha_s, float& beta_s,
-                             float alpha_f, float beta_f) -> bool {
-            constexpr bool SOFT = decltype(soft_c)::value, FLUSH = decltype(flush_c)::value;
-            constexpr bool MASKED = decltype(masked_c)::value, RESCALE = decltype(rescale_c)::value;
-            const int buf = ts & 1, stage = SOFT ? ts % STAGES : 0;
-            const int valid = min(KEY_TILE, n_keys - ts * KEY_TILE);
-            float c = 0.0f, offset = 0.0f;
-            TRACE(TR_OTHER);
-            if (SOFT) {
-                c = (sq * sk_reg) * scale_log2;
-                if (ts + 1 < k_tiles) sk_reg = load_scale(sk + ts + 1);
-                if (!mbar_wait_warp(&sm.s_full[g][buf], (ts >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
-                if (V_TOKEN && !mbar_wait_warp(&sm.v_full[stage], (ts / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
-                tc_fence_after();
+        if constexpr (!V_TOKEN) {
+            // One step of the loop: the scores of key tile `ts` become P^ in shared memory (SOFT) while the accumulator of
+            // tile `tf` is flushed into `out` (FLUSH).  In the steady state both happen, interleaved 16 keys and 32 channels
+            // at a time in one straight run of instructions, so that the exponentials (XU), the flush's multiply-adds (FMA
+            // pipe) and the packing (ALU) overlap inside one warp, and one wait covers the tensor-memory loads of both.
+            // Every choice is a template argument: a test inside the run would cut it into short basic blocks and leave
+            // the latencies exposed.  alpha_s, beta_s: of tile ts, for its flush one step later.
+            auto tile_step = [&](auto soft_c, auto flush_c, auto masked_c, auto rescale_c, int ts, int tf, float& alpha_s, float& beta_s,
+                                 float alpha_f, float beta_f) -> bool {
+                constexpr bool SOFT = decltype(soft_c)::value, FLUSH = decltype(flush_c)::value;
+                constexpr bool MASKED = decltype(masked_c)::value, RESCALE = decltype(rescale_c)::value;
+                const int buf = ts & 1, stage = SOFT ? ts % STAGES : 0;
+                const int valid = min(KEY_TILE, n_keys - ts * KEY_TILE);
+                float c = 0.0f, offset = 0.0f;
+                TRACE(TR_OTHER);
+                if (SOFT) {
+                    c = (sq * sk_reg) * scale_log2;
+                    if (ts + 1 < k_tiles) sk_reg = load_scale(sk + ts + 1);
+                    if (!mbar_wait_warp(&sm.s_full[g][buf], (ts >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+                    if (V_TOKEN && !mbar_wait_warp(&sm.v_full[stage], (ts / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+                    tc_fence_after();
+                }
+                TRACE(TR_WAIT_S);
+                const float2 c2 = make_float2(c, c);
+                const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
+                const float2* inv_s = reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE);
+                if (SOFT) {
+                    // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels and the flush's
+                    // accumulator values fill the register file, so pass 2 reads the scores again, 16 at a time.
+                    float tile_max;
+                    {
+                        float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
+                        tmem_ld64_sync(t_scores + buf * 64, x);
+                        if (V_TOKEN) {
+#pragma unroll
+                            for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
+                        }
+                        if (MASKED) {  // keys past the end: below every real score (|score| < 2^21)
+                            const float low = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
+#pragma unroll
+                            for (int j = 0; j < KEY_TILE; ++j)
+                                if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = low;
+                        }
+                        float top[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
+#pragma unroll
+                        for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
+                        tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
+                        if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
+                    }
+                    const float m_new = fmaxf(m, tile_max);
+                    alpha_s = ex2(m - m_new);
+                    beta_s = ex2(tile_max - m_new);
+                    m = m_new;
+                    offset = LOG2_255 - tile_max;
+                }
+                TRACE(TR_LOAD_S);
+                if (FLUSH) {
+                    if (!mbar_wait_warp(&sm.acc_full[g], tf & 1, abort_flag, status, STATUS_WAIT_PV)) return false;
+                    tc_fence_after();
+                }
+                TRACE(TR_WAIT_PV);
+                const float2 offset2 = make_float2(offset, offset), alpha2 = make_float2(alpha_f, alpha_f), beta2 = make_float2(beta_f, beta_f);
+                uint8_t* p_row = sm.p[g][buf] + row * 16;
+                unsigned isum[2] = {0, 0};
+                float2 fsum = make_float2(0.0f, 0.0f);
+                float2 x[2][8], a[2][8];  // 16 scores ahead; the 32 accumulator channels of the step
+                if (SOFT) tmem_ld16_async(t_scores + buf * 64, x[0]);
+                if (FLUSH) {
+                    tmem_ld16_async(t_acc, a[0]);
+                    tmem_ld16_async(t_acc + 16, a[1]);
+                }
+#pragma unroll
+                for (int step = 0; step < KEY_TILE / 16; ++step) {
+                    tmem_wait_ld();  // every load issued so far
+                    if (SOFT) {
+                        reg_fence8(x[step % 2]);
+                        if (step + 1 < KEY_TILE / 16) tmem_ld16_async(t_scores + buf * 64 + (step + 1) * 16, x[(step + 1) % 2]);
+                    }
+                    float2 f[16];  // MAGIC taken off the accumulator values: their registers go back to the next loads at once
+                    if (FLUSH) {
+                        reg_fence8(a[0]);
+                        reg_fence8(a[1]);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) f[i] = add2(a[i / 8][i % 8], minus_magic);
+                        if (step + 1 < KEY_TILE / 16) {
+                            reg_fence8(a[0]);
+                            reg_fence8(a[1]);
+                            tmem_ld16_async(t_acc + (step + 1) * 32, a[0]);
+                            tmem_ld16_async(t_acc + (step + 1) * 32 + 16, a[1]);
+                        }
+                    }
+                    uint32_t w[4];
+                    if (SOFT) {  // P^ = rint(255 * 2^(x - tile max)), keys 16 step .. 16 step + 15
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            uint32_t pair[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const int j = step * 8 + i * 2 + h;  // a pair of keys
+                                float2 e = fma2(add2(x[step % 2][i * 2 + h], minus_magic), c2, V_TOKEN ? log_s[j] : offset2);
+                                if (V_TOKEN) e = add2(e, offset2);
+                                const float2 p = make_float2(ex2(e.x), ex2(e.y));
+                                if (V_TOKEN) fsum = fma2(p, inv_s[j], fsum);
+                                const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
+                                pair[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
+                            }
+                            w[i] = __byte_perm(pair[0], pair[1], 0x5410);
+                            if (!V_TOKEN && MASKED) {  // keys past the end weigh nothing
+                                const int left = valid - (step * 16 + i * 4);
+                                w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
+                            }
+                            if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
+                        }
+                    }
+                    if (FLUSH) {  // out = out * alpha + beta * float(acc), channels 32 step .. 32 step + 31
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            float2 v = o[step * 16 + i];
+                            if (RESCALE) v = mul2(v, alpha2);
+                            o[step * 16 + i] = fma2(beta2, f[i], v);
+                        }
+                    }
+                    if (SOFT) *reinterpret_cast<uint4*>(p_row + step * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                    if (FLUSH) tmem_fill<32>(t_acc + step * 32, magic);
+                }
+                if (SOFT) tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // every score has been read: refill the buffer
+                tmem_wait_st();
+                tc_fence_before();
+                TRACE(TR_SOFTMAX);
+                if (SOFT) {
+                    mbar_arrive(&sm.s_free[g][buf]);
+                    fence_proxy_async();
+                    mbar_arrive(&sm.p_ready[g][buf]);
+                    den = den * alpha_s + (V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1])) * beta_s;
+                }
+                if (FLUSH) mbar_arrive(&sm.acc_free[g]);
+                TRACE(TR_STORE_P);
+                return true;
+            };
+            using yes = std::true_type;
+            using no = std::false_type;
+            float unused_a = 1.0f, unused_b = 1.0f;
+            auto flush_only = [&](int tf, float alpha_f, float beta_f) -> bool {
+                return __all_sync(0xffffffffu, alpha_f == 1.0f) ? tile_step(no{}, yes{}, no{}, no{}, -1, tf, unused_a, unused_b, alpha_f, beta_f)
+                                                                : tile_step(no{}, yes{}, no{}, yes{}, -1, tf, unused_a, unused_b, alpha_f, beta_f);
+            };
+            const bool ragged = n_keys % KEY_TILE != 0;  // the last key tile needs masking: it is taken apart from the flush
+
+            float alpha = 1.0f, beta = 1.0f;
+            if (ok) ok = k_tiles == 1 && ragged ? tile_step(yes{}, no{}, yes{}, no{}, 0, -1, alpha, beta, 1.0f, 1.0f)
+                                                : tile_step(yes{}, no{}, no{}, no{}, 0, -1, alpha, beta, 1.0f, 1.0f);
+            for (int t = 0; ok && t < k_tiles; ++t) {
+                float alpha_next = 1.0f, beta_next = 1.0f;
+                if (t + 1 == k_tiles) {
+                    ok = flush_only(t, alpha, beta);
+                } else if (t + 2 == k_tiles && ragged) {
+                    ok = tile_step(yes{}, no{}, yes{}, no{}, t + 1, -1, alpha_next, beta_next, 1.0f, 1.0f) && flush_only(t, alpha, beta);
+                } else if (__all_sync(0xffffffffu, alpha == 1.0f)) {
+                    ok = tile_step(yes{}, yes{}, no{}, no{}, t + 1, t, alpha_next, beta_next, alpha, beta);
+                } else {
+                    ok = tile_step(yes{}, yes{}, no{}, yes{}, t + 1, t, alpha_next, beta_next, alpha, beta);
+                }
+                alpha = alpha_next;
+                beta = beta_next;
             }
-            TRACE(TR_WAIT_S);
-            const float2 c2 = make_float2(c, c);
-            const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
-            const float2* inv_s = reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE);
-            if (SOFT) {
-                // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels and the flush's
-                // accumulator values fill the register file, so pass 2 reads the scores again, 16 at a time.
+        } else {
+            // Per token the registers do not reach for the fused step (log2 s_j and 1 / s_j of every key come on top):
+            // the softmax of a tile, its 64 scores kept in registers, then the flush of the previous tile.
+            auto softmax_token = [&](int t, float& alpha, float& beta) -> bool {
+                const int buf = t & 1, stage = t % STAGES;
+                const int valid = min(KEY_TILE, n_keys - t * KEY_TILE);
+                const float c = (sq * sk_reg) * scale_log2;
+                if (t + 1 < k_tiles) sk_reg = load_scale(sk + t + 1);
+                TRACE(TR_OTHER);
+                if (!mbar_wait_warp(&sm.s_full[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+                if (!mbar_wait_warp(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+                tc_fence_after();
+                TRACE(TR_WAIT_S);
+                float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
+                tmem_ld64_sync(t_scores + buf * 64, x);
+                tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // completes while the maximum is taken
+                TRACE(TR_LOAD_S);
+
+                const float2 c2 = make_float2(c, c);
+                const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
+#pragma unroll
+                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
+                if (valid < KEY_TILE) {  // keys past the end take no part
+#pragma unroll
+                    for (int j = 0; j < KEY_TILE; ++j)
+                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
+                }
                 float tile_max;
-                {
-                    float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
-                    tmem_ld64_sync(t_scores + buf * 64, x);
-                    if (V_TOKEN) {
-#pragma unroll
-                        for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
-                    }
-                    if (MASKED) {  // keys past the end: below every real score (|score| < 2^21)
-                        const float low = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
-#pragma unroll
-                        for (int j = 0; j < KEY_TILE; ++j)
-                            if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = low;
-                    }
+                {  // four independent chains, then a tree
                     float top[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
 #pragma unroll
                     for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
                     tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-                    if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
                 }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.s_free[g][buf]);
                 const float m_new = fmaxf(m, tile_max);
-                alpha_s = ex2(m - m_new);
-                beta_s = ex2(tile_max - m_new);
+                alpha = ex2(m - m_new);
+                beta = ex2(tile_max - m_new);
                 m = m_new;
-                offset = LOG2_255 - tile_max;
-            }
-            TRACE(TR_LOAD_S);
-            if (FLUSH) {
-                if (!mbar_wait_warp(&sm.acc_full[g], tf & 1, abort_flag, status, STATUS_WAIT_PV)) return false;
-                tc_fence_after();
-            }
-            TRACE(TR_WAIT_PV);
-            const float2 offset2 = make_float2(offset, offset), alpha2 = make_float2(alpha_f, alpha_f), beta2 = make_float2(beta_f, beta_f);
-            uint8_t* p_row = sm.p[g][buf] + row * 16;
-            unsigned isum[2] = {0, 0};
-            float2 fsum = make_float2(0.0f, 0.0f);
-            float2 x[2][8], a[2][8];  // 16 scores ahead; the 32 accumulator channels of the step
-            if (SOFT) tmem_ld16_async(t_scores + buf * 64, x[0]);
-            if (FLUSH) {
-                tmem_ld16_async(t_acc, a[0]);
-                tmem_ld16_async(t_acc + 16, a[1]);
-            }
+                const float offset = LOG2_255 - tile_max;
+                const float2 offset2 = make_float2(offset, offset);
+                uint8_t* p_row = sm.p[g][buf] + row * 16;
+                float2 fsum = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int step = 0; step < KEY_TILE / 16; ++step) {
-                tmem_wait_ld();  // every load issued so far
-                if (SOFT) {
-                    reg_fence8(x[step % 2]);
-                    if (step + 1 < KEY_TILE / 16) tmem_ld16_async(t_scores + buf * 64 + (step + 1) * 16, x[(step + 1) % 2]);
-                }
-                float2 f[16];  // MAGIC taken off the accumulator values: their registers go back to the next loads at once
-                if (FLUSH) {
-                    reg_fence8(a[0]);
-                    reg_fence8(a[1]);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) f[i] = add2(a[i / 8][i % 8], minus_magic);
-                    if (step + 1 < KEY_TILE / 16) {
-                        reg_fence8(a[0]);
-                        reg_fence8(a[1]);
-                        tmem_ld16_async(t_acc + (step + 1) * 32, a[0]);
-                        tmem_ld16_async(t_acc + (step + 1) * 32 + 16, a[1]);
-                    }
-                }
-                uint32_t w[4];
-                if (SOFT) {  // P^ = rint(255 * 2^(x - tile max)), keys 16 step .. 16 step + 15
+                for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
+                    uint32_t w[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        uint32_t pair[2];
+                        uint32_t half[2];
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            const int j = step * 8 + i * 2 + h;  // a pair of keys
-                            float2 e = fma2(add2(x[step % 2][i * 2 + h], minus_magic), c2, V_TOKEN ? log_s[j] : offset2);
-                            if (V_TOKEN) e = add2(e, offset2);
+                            const int j = chunk * 8 + i * 2 + h;  // a pair of keys
+                            const float2 e = add2(x[j], offset2);
                             const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                            if (V_TOKEN) fsum = fma2(p, inv_s[j], fsum);
+                            fsum = fma2(p, reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE)[j], fsum);  // sum of p / s_j
                             const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
-                            pair[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
+                            half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
                         }
-                        w[i] = __byte_perm(pair[0], pair[1], 0x5410);
-                        if (!V_TOKEN && MASKED) {  // keys past the end weigh nothing
-                            const int left = valid - (step * 16 + i * 4);
-                            w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
-                        }
-                        if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
+                        w[i] = __byte_perm(half[0], half[1], 0x5410);  // keys past the end: V8 and 1 / s_j are zeros there
                     }
+                    *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                if (FLUSH) {  // out = out * alpha + beta * float(acc), channels 32 step .. 32 step + 31
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        float2 v = o[step * 16 + i];
-                        if (RESCALE) v = mul2(v, alpha2);
-                        o[step * 16 + i] = fma2(beta2, f[i], v);
-                    }
-                }
-                if (SOFT) *reinterpret_cast<uint4*>(p_row + step * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-                if (FLUSH) tmem_fill<32>(t_acc + step * 32, magic);
-            }
-            if (SOFT) tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // every score has been read: refill the buffer
-            tmem_wait_st();
-            tc_fence_before();
-            TRACE(TR_SOFTMAX);
-            if (SOFT) {
-                mbar_arrive(&sm.s_free[g][buf]);
+                TRACE(TR_SOFTMAX);
                 fence_proxy_async();
                 mbar_arrive(&sm.p_ready[g][buf]);
-                den = den * alpha_s + (V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1])) * beta_s;
-            }
-            if (FLUSH) mbar_arrive(&sm.acc_free[g]);
-            TRACE(TR_STORE_P);
-            return true;
-        };
-        using yes = std::true_type;
-        using no = std::false_type;
-        float unused_a = 1.0f, unused_b = 1.0f;
-        auto flush_only = [&](int tf, float alpha_f, float beta_f) -> bool {
-            return __all_sync(0xffffffffu, alpha_f == 1.0f) ? tile_step(no{}, yes{}, no{}, no{}, -1, tf, unused_a, unused_b, alpha_f, beta_f)
-                                                            : tile_step(no{}, yes{}, no{}, yes{}, -1, tf, unused_a, unused_b, alpha_f, beta_f);
-        };
-        const bool ragged = n_keys % KEY_TILE != 0;  // the last key tile needs masking: it is taken apart from the flush
+                TRACE(TR_STORE_P);
+                den = den * alpha + (fsum.x + fsum.y) * beta;
+                return true;
+            };
 
-        float alpha = 1.0f, beta = 1.0f;
-        if (ok) ok = k_tiles == 1 && ragged ? tile_step(yes{}, no{}, yes{}, no{}, 0, -1, alpha, beta, 1.0f, 1.0f)
-                                            : tile_step(yes{}, no{}, no{}, no{}, 0, -1, alpha, beta, 1.0f, 1.0f);
-        for (int t = 0; ok && t < k_tiles; ++t) {
-            float alpha_next = 1.0f, beta_next = 1.0f;
-            if (t + 1 == k_tiles) {
-                ok = flush_only(t, alpha, beta);
-            } else if (t + 2 == k_tiles && ragged) {
-                ok = tile_step(yes{}, no{}, yes{}, no{}, t + 1, -1, alpha_next, beta_next, 1.0f, 1.0f) && flush_only(t, alpha, beta);
-            } else if (__all_sync(0xffffffffu, alpha == 1.0f)) {
-                ok = tile_step(yes{}, yes{}, no{}, no{}, t + 1, t, alpha_next, beta_next, alpha, beta);
-            } else {
-                ok = tile_step(yes{}, yes{}, no{}, yes{}, t + 1, t, alpha_next, beta_next, alpha, beta);
+            float alpha = 1.0f, beta = 1.0f;
+            if (ok) ok = softmax_token(0, alpha, beta);
+            for (int t = 0; ok && t < k_tiles; ++t) {
+                float alpha_next = 1.0f, beta_next = 1.0f;
+                if (t + 1 < k_tiles) ok = softmax_token(t + 1, alpha_next, beta_next);
+                if (!ok) break;
+                // flush of tile t: out = out * alpha + beta * float(acc)
+                TRACE(TR_OTHER);
+                ok = mbar_wait_warp(&sm.acc_full[g], t & 1, abort_flag, status, STATUS_WAIT_PV);
+                if (!ok) break;
+                tc_fence_after();
+                TRACE(TR_WAIT_PV);
+                float2 a[4][8];  // a ring of four 16-channel loads: tensor-memory latency (~180 cycles) hides behind the arithmetic
+#pragma unroll
+                for (int i = 0; i < 4; ++i) tmem_ld16_async(t_acc + i * 16, a[i]);
+                if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
+                    const float2 alpha2 = make_float2(alpha, alpha);
+#pragma unroll
+                    for (int i = 0; i < HEAD_DIM / 2; ++i) o[i] = mul2(o[i], alpha2);
+                }
+                const float2 beta2 = make_float2(beta, beta);
+#pragma unroll
+                for (int part = 0; part < HEAD_DIM / 16; ++part) {
+                    if (part % 4 == 0) {  // tcgen05.wait::ld waits for every load issued so far
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) reg_fence8(a[i]);
+                    }
+                    float2 f[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) f[i] = add2(a[part % 4][i], minus_magic);
+                    if (part + 4 < HEAD_DIM / 16) tmem_ld16_async(t_acc + (part + 4) * 16, a[part % 4]);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) o[part * 8 + i] = fma2(beta2, f[i], o[part * 8 + i]);
+                    if (part % 2 == 1) tmem_fill<32>(t_acc + (part - 1) * 16, magic);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.acc_free[g]);
+                TRACE(TR_FLUSH);
+                alpha = alpha_next;
+                beta = beta_next;
             }
-            alpha = alpha_next;
-            beta = beta_next;
         }
         TRACE_END(g);
 
