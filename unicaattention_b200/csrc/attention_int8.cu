@@ -36,6 +36,7 @@ constexpr int V_BYTES = KEY_TILE * HEAD_DIM;    // 8192
 constexpr int TOK_BYTES = 2 * KEY_TILE * 4;     // 512
 constexpr int P_BYTES = QUERY_TILE * KEY_TILE;  // 8192
 constexpr int TMEM_COLUMNS = 512;
+constexpr float REFERENCE_SLACK = 60.0f;  // log2: how far a tile maximum may rise above a row's reference exponent
 constexpr int COL_S = 0, COL_ACC = 128;  // inside a query tile's 256 columns: S buffers at 0 and 64, acc at 128
 
 struct __align__(128) AttSmem {
@@ -291,8 +292,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                         tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
                         if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
                     }
-                    const float m_new = fmaxf(m, tile_max);
-                    alpha_s = ex2(m - m_new);
+                    // `m` is the exponent the row's sums are kept at, not the running maximum: out = sum over tiles of
+                    // 2^(tile max - m) * acc, the same for the denominator, and the common factor cancels at the end.  The
+                    // textbook form moves m to every new maximum and multiplies out and den by alpha = 2^(m_old - m_new)
+                    // each time; here m moves only when a tile maximum is more than 2^REFERENCE_SLACK above it, so that
+                    // multiplication (128 per row) all but disappears.  The difference is rounding only.
+                    const bool first = m == -INFINITY;
+                    const float m_new = tile_max > m + REFERENCE_SLACK ? tile_max : m;
+                    alpha_s = first ? 1.0f : ex2(m - m_new);
                     beta_s = ex2(tile_max - m_new);
                     m = m_new;
                     offset = LOG2_255 - tile_max;
