@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < KEY_TILE / 32; ++ks)
                     mma_i8_ss(base + COL_ACC, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, true);
+                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, V_TOKEN || ks > 0);
                 mma_commit(&sm.acc_full[g]);
                 mma_commit(&sm.v_empty[stage]);
                 if (t + 2 < k_tiles) ok = scores(t + 2);
@@ -231,7 +231,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         // Every accumulator starts at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
         uint32_t magic[FILL_BLOCK];
         fill_block_init(magic, MAGIC_BITS);
-        tmem_fill<256>(t_scores, magic);
+        tmem_fill<V_TOKEN ? 256 : 128>(t_scores, magic);  // both score buffers; per token the P.V accumulator too
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.s_free[g][0]);
@@ -332,7 +332,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                         reg_fence8(a[0]);
                         reg_fence8(a[1]);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) f[i] = add2(a[i / 8][i % 8], minus_magic);
+                        for (int i = 0; i < 16; ++i)  // the accumulator is overwritten by every tile's P.V: plain integers
+                            f[i] = make_float2(__int2float_rn(__float_as_int(a[i / 8][i % 8].x)), __int2float_rn(__float_as_int(a[i / 8][i % 8].y)));
                         if (step + 1 < KEY_TILE / 16) {
                             reg_fence8(a[0]);
                             reg_fence8(a[1]);
@@ -372,7 +373,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                         }
                     }
                     if (SOFT) *reinterpret_cast<uint4*>(p_row + step * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-                    if (FLUSH) tmem_fill<32>(t_acc + step * 32, magic);
                 }
                 if (SOFT) tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // every score has been read: refill the buffer
                 tmem_wait_st();
