@@ -259,7 +259,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 if (SOFT) {
                     c = (sq * sk_reg) * scale_log2;
                     if (ts + 1 < k_tiles) sk_reg = load_scale(sk + ts + 1);
-                    if (!mbar_wait_warp(&sm.s_full[g][buf], (ts >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+                    // One wait serves both halves of a full step: the tile's issuing thread queued S(ts) before P.V(tf)
+                    // (tf = ts - 1), tcgen05.mma of one thread complete in order, and a commit covers everything issued
+                    // before it, so when the accumulator's barrier has flipped the scores are there too.
+                    if (FLUSH ? !mbar_wait_warp(&sm.acc_full[g], tf & 1, abort_flag, status, STATUS_WAIT_PV)
+                              : !mbar_wait_warp(&sm.s_full[g][buf], (ts >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES))
+                        return false;
                     if (V_TOKEN && !mbar_wait_warp(&sm.v_full[stage], (ts / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
                     tc_fence_after();
                 }
@@ -305,7 +310,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     offset = LOG2_255 - tile_max;
                 }
                 TRACE(TR_LOAD_S);
-                if (FLUSH) {
+                if (FLUSH && !SOFT) {
                     if (!mbar_wait_warp(&sm.acc_full[g], tf & 1, abort_flag, status, STATUS_WAIT_PV)) return false;
                     tc_fence_after();
                 }
