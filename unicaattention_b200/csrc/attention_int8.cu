@@ -46,7 +46,7 @@ struct __align__(128) AttSmem {
     float tok[STAGES][2 * KEY_TILE];
     uint8_t p[2][2][P_BYTES];
     uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], drain[2];
+    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], step_done[2], drain[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -112,6 +112,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
             mbar_init(&sm.acc_full[g], 1);
             mbar_init(&sm.acc_free[g], 128);
+            mbar_init(&sm.step_done[g], 128);
         }
         mbar_init(&sm.drain[0], 1);
         mbar_init(&sm.drain[1], 1);
@@ -164,10 +165,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
             const int g = warp - MMA_WARP;
             const uint32_t q_addr = smem_u32(sm.q[g]), base = tmem + g * 256;
+            // Per channel / outliers: a query tile's threads end every step with ONE arrival (step_done): step t holds
+            // the softmax of key tile t and the flush of tile t - 1, so its end frees the accumulator, delivers P^(t) and
+            // empties a scores buffer at once, and P.V(t) and the scores of tile t + 2 go out back to back after a single
+            // wake-up.  Per token the softmax and the flush end at different times and keep a barrier each.
             auto scores = [&](int n) -> bool {
                 const int stage = n % STAGES, buf = n & 1;
                 if (!mbar_wait(&sm.k_full[stage], (n / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
-                if (!mbar_wait(&sm.s_free[g][buf], (n >> 1) & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
+                if ((V_TOKEN || n < 2) && !mbar_wait(&sm.s_free[g][buf], (n >> 1) & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sm.k[stage]);
 #pragma unroll
@@ -182,9 +187,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             for (int n = 0; ok && n < min(2, k_tiles); ++n) ok = scores(n);
             for (int t = 0; ok && t < k_tiles; ++t) {
                 const int stage = t % STAGES, buf = t & 1;
-                ok = mbar_wait(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE) &&
-                     mbar_wait(&sm.p_ready[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P) &&
-                     mbar_wait(&sm.acc_free[g], t & 1, abort_flag, status, STATUS_WAIT_FREE);
+                ok = mbar_wait(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+                if (V_TOKEN) {
+                    ok = ok && mbar_wait(&sm.p_ready[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P) &&
+                         mbar_wait(&sm.acc_free[g], t & 1, abort_flag, status, STATUS_WAIT_FREE);
+                } else {  // K(t + 2) has long landed: probing it before the step's end keeps that probe off the critical path
+                    if (t + 2 < k_tiles) ok = ok && mbar_wait(&sm.k_full[(t + 2) % STAGES], ((t + 2) / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+                    ok = ok && mbar_wait(&sm.step_done[g], t & 1, abort_flag, status, STATUS_WAIT_P);
+                }
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t p_addr = smem_u32(sm.p[g][buf]), v_addr = smem_u32(sm.v[stage]);
@@ -237,9 +247,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         mbar_arrive(&sm.s_free[g][0]);
         mbar_arrive(&sm.s_free[g][1]);
         mbar_arrive(&sm.acc_free[g]);
-        // The second warpgroup starts half a period late (when the first has delivered its first P^): the two then
-        // alternate between the exponentials and the flush instead of competing for the same unit at the same time.
-        if (g == 1) ok = mbar_wait_warp(&sm.p_ready[0][0], 0, abort_flag, status, STATUS_WAIT_P);
+        // Per token the second query tile starts when the first has delivered its first P^, so that the two begin out of
+        // step (exponentials against flush); the fused steps of the other modes mix both kinds of work anyway.
+        if (V_TOKEN && g == 1) ok = mbar_wait_warp(&sm.p_ready[0][0], 0, abort_flag, status, STATUS_WAIT_P);
 
         if constexpr (!V_TOKEN) {
             // One step of the loop: the scores of key tile `ts` become P^ in shared memory (SOFT) while the accumulator of
@@ -249,7 +259,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             // Every choice is a template argument: a test inside the run would cut it into short basic blocks and leave
             // the latencies exposed.  alpha_s, beta_s: of tile ts, for its flush one step later.
             auto tile_step = [&](auto soft_c, auto flush_c, auto masked_c, auto rescale_c, int ts, int tf, float& alpha_s, float& beta_s,
-                                 float alpha_f, float beta_f) -> bool {
+                                 float alpha_f, float beta_f, bool last_of_step = true) -> bool {
                 constexpr bool SOFT = decltype(soft_c)::value, FLUSH = decltype(flush_c)::value;
                 constexpr bool MASKED = decltype(masked_c)::value, RESCALE = decltype(rescale_c)::value;
                 const int buf = ts & 1, stage = SOFT ? ts % STAGES : 0;
@@ -384,12 +394,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 tc_fence_before();
                 TRACE(TR_SOFTMAX);
                 if (SOFT) {
-                    mbar_arrive(&sm.s_free[g][buf]);
                     fence_proxy_async();
-                    mbar_arrive(&sm.p_ready[g][buf]);
                     den = den * alpha_s + (V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1])) * beta_s;
                 }
-                if (FLUSH) mbar_arrive(&sm.acc_free[g]);
+                if (last_of_step) mbar_arrive(&sm.step_done[g]);  // P^(ts) delivered, its scores buffer and the accumulator free
                 TRACE(TR_STORE_P);
                 return true;
             };
@@ -410,7 +418,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 if (t + 1 == k_tiles) {
                     ok = flush_only(t, alpha, beta);
                 } else if (t + 2 == k_tiles && ragged) {
-                    ok = tile_step(yes{}, no{}, yes{}, no{}, t + 1, -1, alpha_next, beta_next, 1.0f, 1.0f) && flush_only(t, alpha, beta);
+                    ok = tile_step(yes{}, no{}, yes{}, no{}, t + 1, -1, alpha_next, beta_next, 1.0f, 1.0f, false) && flush_only(t, alpha, beta);
                 } else if (__all_sync(0xffffffffu, alpha == 1.0f)) {
                     ok = tile_step(yes{}, yes{}, no{}, no{}, t + 1, t, alpha_next, beta_next, alpha, beta);
                 } else {
