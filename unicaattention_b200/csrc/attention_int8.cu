@@ -279,6 +279,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     tc_fence_after();
                 }
                 TRACE(TR_WAIT_S);
+#ifdef UNICA_TRACE
+                if (tracing && ts >= 100 && ts < 108) g_trace[2 + g][ts - 100] = clock64();  // when the steps of tiles 100..107 began
+#endif
                 const float2 c2 = make_float2(c, c);
                 const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
                 const float2* inv_s = reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE);
