@@ -81,6 +81,7 @@ struct __align__(128) Fp4Smem {
     uint8_t p[2][P4_BYTES];
     uint32_t sfp[2][QUERY_TILE];
     uint2 exchange[2][2][2][QUERY_TILE];  // [query tile][tag parity][thread of the row][row] = {tag, value}
+    float inv_e4m3[128];                  // 1 / value of every non-negative e4m3 byte, correctly rounded; 0 for the byte 0
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
     uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], sfp_ready[2], drain[2];
     uint32_t tmem_base;
@@ -95,11 +96,20 @@ __device__ __forceinline__ float lg2(float x) {
     asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
-// two floats -> one byte of two e2m1 codes, `lo` in the low nibble
-__device__ __forceinline__ uint32_t e2m1x2(float lo, float hi) {
-    uint32_t byte;
-    asm("{ .reg .b8 b; cvt.rn.satfinite.e2m1x2.f32 b, %2, %1; cvt.u32.u8 %0, b; }" : "=r"(byte) : "f"(lo), "f"(hi));
-    return byte;
+// eight floats -> eight e2m1 codes in one word, element i in nibble i
+__device__ __forceinline__ uint32_t e2m1x8(const float2 (&v)[4]) {
+    uint32_t word;
+    asm("{\n\t"
+        ".reg .b8 b0, b1, b2, b3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n\t"
+        "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n\t"
+        "mov.b32 %0, {b0, b1, b2, b3};\n\t"
+        "}"
+        : "=r"(word)
+        : "f"(v[0].x), "f"(v[0].y), "f"(v[1].x), "f"(v[1].y), "f"(v[2].x), "f"(v[2].y), "f"(v[3].x), "f"(v[3].y));
+    return word;
 }
 
 __global__ void __launch_bounds__(F4_THREADS, 1)
@@ -137,6 +147,10 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int i = threadIdx.x; i < 2 * 2 * 2 * QUERY_TILE; i += F4_THREADS) (&sm.exchange[0][0][0][0])[i] = make_uint2(0xffffffffu, 0u);  // no tag
+    if (threadIdx.x < 128) {
+        const float value = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(threadIdx.x), __NV_E4M3)));
+        sm.inv_e4m3[threadIdx.x] = value > 0.0f ? __fdiv_rn(1.0f, value) : 0.0f;  // byte 127 is NaN: never produced (satfinite)
+    }
     if (warp == F4_MMA_WARP) tmem_alloc(&sm.tmem_base, F4_TMEM_COLUMNS);
     tc_fence_before();
     __syncthreads();
@@ -336,22 +350,22 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             for (int b = 0; b < 2; ++b) {
                 const float top = ex2(block_max[b] - m_new + P_LOG2_GAIN) * (1.0f / 6.0f);
                 const uint32_t byte = __nv_cvt_float_to_fp8(top, __NV_SATFINITE, __NV_E4M3);
-                const float sp = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3)));
                 // P / sp as the emulation takes it, 1024 * 2^(x - m) times 1 / sp: a product of two correctly rounded
-                // factors lands on the other side of an e2m1 tie far less often than 2^(x - m + 10 - log2 sp) does
-                const float inv = sp > 0.0f ? __fdiv_rn(1.0f, sp) : 0.0f;
+                // factors lands on the other side of an e2m1 tie far less often than 2^(x - m + 10 - log2 sp) does.
+                // 1 / sp comes from a table of the 127 e4m3 values: a division here would put a branch (its slow path)
+                // into the middle of the exponentials.
+                const float inv = sm.inv_e4m3[byte];
                 const float2 inv2 = make_float2(inv, inv);
                 sf_pair |= byte << (8 * b);
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
-                    uint32_t word = 0;
+                    float2 r[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float2 e = add2(x[8 * b + 4 * w + i], gain2);
-                        const float2 r = mul2(make_float2(ex2(e.x), ex2(e.y)), inv2);
-                        word |= e2m1x2(r.x, r.y) << (8 * i);
+                        r[i] = mul2(make_float2(ex2(e.x), ex2(e.y)), inv2);
                     }
-                    codes[2 * b + w] = word;
+                    codes[2 * b + w] = e2m1x8(r);
                 }
             }
             F4_TRACE(F4_TR_QUANTIZE);
