@@ -41,7 +41,7 @@ def fp4_image(codes: np.ndarray) -> np.ndarray:
     return np.ascontiguousarray(packed.reshape(rows, k // 32, 16).transpose(1, 0, 2))
 
 
-@pytest.mark.parametrize("n,k,variant", [(64, 128, 0), (144, 64, 0), (128, 64, 0), (16, 64, 0)])
+@pytest.mark.parametrize("n,k,variant", [(64, 128, 0), (144, 64, 0), (128, 64, 0), (16, 64, 0), (64, 128, 2), (144, 64, 2)])
 def test_mma_nvf4_exact(n, k, variant):
     from unicaattention_b200 import lib
 

@@ -36,4 +36,11 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b,
     asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// Scale bytes from shared memory into tensor memory by the tensor-core pipe itself: 32 rows of 16 bytes at `src`
+// (row i = the four 32-bit words that lane i of columns taddr .. taddr + 3 gets), copied into all four 32-lane quarters.
+// Issued by one thread; ordered with the tcgen05.mma that the same thread issues after it.
+__device__ __forceinline__ void tmem_cp_32x128b(uint32_t taddr, uint32_t src) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc(src, 16, 128)) : "memory");
+}
+
 }  // namespace unica

@@ -108,14 +108,21 @@ __device__ __forceinline__ float block_max(float x, float* scratch) {
     return x;
 }
 
-__device__ __forceinline__ uint32_t pack4(const float* v, float scale) {
-    uint32_t word = 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int code = __float2int_rn(fminf(fmaxf(rintf(__fdiv_rn(v[i], scale)), -127.0f), 127.0f));
-        word |= uint32_t(code & 0xff) << (8 * i);
-    }
-    return word;
+// clamp(rint(x / scale), -127, 127) as the low byte of the result, bit for bit the IEEE division's answer, without the
+// division: q = x * (1 / scale) is within 2^-23 |q| of the true quotient, so its rounding can differ only when q sits
+// that close to a half; then (a few elements in 10^5) the division is done.  Rounding and the float -> int step are one
+// addition: q + 1.5 * 2^23 has rint(q), in two's complement, in its low mantissa bits.
+__device__ __forceinline__ uint32_t code_bits(float x, float scale, float inv) {
+    const float q = x * inv;
+    float t = q + MAGIC;                                 // MAGIC + rint(q)
+    if (fabsf(fabsf(q - (t - MAGIC)) - 0.5f) < 1e-4f) t = rintf(__fdiv_rn(x, scale)) + MAGIC;  // |q| <= 128: 2^-23 |q| < 1.6e-5
+    return __float_as_uint(fminf(fmaxf(t, MAGIC - 127.0f), MAGIC + 127.0f));
+}
+
+__device__ __forceinline__ uint32_t pack4(const float* v, float scale, float inv) {
+    const uint32_t lo = __byte_perm(code_bits(v[0], scale, inv), code_bits(v[1], scale, inv), 0x0040);
+    const uint32_t hi = __byte_perm(code_bits(v[2], scale, inv), code_bits(v[3], scale, inv), 0x0040);
+    return __byte_perm(lo, hi, 0x5410);
 }
 
 // Q or K (minus `mean`, [heads][128] or null) in INT8 with one scale per tile of ROWS tokens (128: Q, 64: K).
@@ -160,16 +167,17 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_int8_kernel(const __nv_
         for (int i = 0; i < 16; ++i) local = fmaxf(local, fabsf(v[it][i]));
     }
     const float scale = fmaxf(block_max(local, scratch) * (1.0f / 127.0f), 1e-12f);
+    const float inv = __frcp_rn(scale);
     if (threadIdx.x == 0) scales[size_t(head) * gridDim.x + tile] = scale;
     int8_t* out = codes + (size_t(head) * gridDim.x + tile) * (ROWS * HEAD_DIM);
 #pragma unroll
     for (int it = 0; it < ITEMS; ++it) {
         const int item = it * THREADS + threadIdx.x, row = item % ROWS, chunk = item / ROWS;
         uint4 w;
-        w.x = pack4(&v[it][0], scale);
-        w.y = pack4(&v[it][4], scale);
-        w.z = pack4(&v[it][8], scale);
-        w.w = pack4(&v[it][12], scale);
+        w.x = pack4(&v[it][0], scale, inv);
+        w.y = pack4(&v[it][4], scale, inv);
+        w.z = pack4(&v[it][8], scale, inv);
+        w.w = pack4(&v[it][12], scale, inv);
         *reinterpret_cast<uint4*>(out + (chunk * ROWS + row) * 16) = w;
     }
 }
@@ -185,61 +193,66 @@ __global__ void __launch_bounds__(THREADS) quantize_v_int8_kernel(const __nv_bfl
                                                                    const uint8_t* __restrict__ skip, int n_tokens,
                                                                    int8_t* __restrict__ v8, float* __restrict__ v_scale,
                                                                    float* __restrict__ v_token) {
-    __shared__ __align__(16) int8_t tile_out[KEY_TILE * HEAD_DIM];
-    const int head = blockIdx.y, tile = blockIdx.x, token0 = tile * KEY_TILE;
+    // The tile goes through shared memory as bf16, keys x channels, and comes out transposed: a thread then owns one
+    // channel and 16 keys, i.e. one 16-byte row of the operand image, and a warp writes 512 contiguous bytes.
+    __shared__ __align__(16) __nv_bfloat16 tile[KEY_TILE][HEAD_DIM];
+    __shared__ float key_scale[KEY_TILE], key_inv[KEY_TILE];
+    const int head = blockIdx.y, t = blockIdx.x, token0 = t * KEY_TILE;
     const int chunk = threadIdx.x % 16;  // 8 channels
-    float scale[8];
-    if (!PER_TOKEN) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int c = head * HEAD_DIM + chunk * 8 + i;
-            scale[i] = fmaxf(fmaxf(high[c], -low[c]) * (1.0f / 127.0f), 1e-12f);
-        }
-        if (tile == 0 && threadIdx.x < 16) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v_scale[head * HEAD_DIM + chunk * 8 + i] = scale[i];
-        }
-    } else if (tile == 0 && threadIdx.x < 16) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v_scale[head * HEAD_DIM + chunk * 8 + i] = 1.0f;
-    }
 #pragma unroll
     for (int it = 0; it < KEY_TILE * 16 / THREADS; ++it) {
         const int key = it * (THREADS / 16) + threadIdx.x / 16;
         const bool valid = token0 + key < n_tokens;
-        float x[8];
-        if (valid && !(skip && skip[size_t(head) * n_tokens + token0 + key])) {
-            load8(x, v + in.offset(head, token0 + key) + chunk * 8);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) x[i] = 0.0f;
-        }
-        if (PER_TOKEN) {
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (valid && !(skip && skip[size_t(head) * n_tokens + token0 + key]))
+            raw = *reinterpret_cast<const uint4*>(v + in.offset(head, token0 + key) + chunk * 8);
+        *reinterpret_cast<uint4*>(&tile[key][chunk * 8]) = raw;
+        if (PER_TOKEN) {  // one scale per key over its channels: the 16 threads of a key share their maxima
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
             float amax = 0.0f;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[i]));
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(pairs[i]);
+                amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+            }
 #pragma unroll
             for (int d = 8; d > 0; d /= 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, d));
-            const float s = fmaxf(amax * (1.0f / 127.0f), 1e-12f);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) scale[i] = s;
             if (chunk == 0) {
-                float* tok = v_token + (size_t(head) * gridDim.x + tile) * 2 * KEY_TILE;
+                const float s = fmaxf(amax * (1.0f / 127.0f), 1e-12f);
+                key_scale[key] = s;
+                key_inv[key] = __frcp_rn(s);
+                float* tok = v_token + (size_t(head) * gridDim.x + t) * 2 * KEY_TILE;
                 tok[key] = valid ? log2f(s) : 0.0f;
                 tok[KEY_TILE + key] = valid ? __fdiv_rn(1.0f, s) : 0.0f;
             }
         }
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int code = __float2int_rn(fminf(fmaxf(rintf(__fdiv_rn(x[i], scale[i])), -127.0f), 127.0f));
-            tile_out[((key / 16) * HEAD_DIM + chunk * 8 + i) * 16 + key % 16] = int8_t(code);
-        }
     }
     __syncthreads();
-    uint4* dst = reinterpret_cast<uint4*>(v8 + (size_t(head) * gridDim.x + tile) * (KEY_TILE * HEAD_DIM));
-    const uint4* src = reinterpret_cast<const uint4*>(tile_out);
+    const int c = threadIdx.x % HEAD_DIM;
+    float scale = 1.0f, inv = 1.0f;
+    if (!PER_TOKEN) {  // max(|low|, |high|) * (1/127) from the channel's minimum and maximum over the head
+        scale = fmaxf(fmaxf(high[head * HEAD_DIM + c], -low[head * HEAD_DIM + c]) * (1.0f / 127.0f), 1e-12f);
+        inv = __frcp_rn(scale);
+    }
+    if (t == 0 && threadIdx.x < HEAD_DIM) v_scale[head * HEAD_DIM + c] = scale;
+    uint4* dst = reinterpret_cast<uint4*>(v8 + (size_t(head) * gridDim.x + t) * (KEY_TILE * HEAD_DIM));
 #pragma unroll
-    for (int i = threadIdx.x; i < KEY_TILE * HEAD_DIM / 16; i += THREADS) dst[i] = src[i];
+    for (int it = 0; it < KEY_TILE / 16 * HEAD_DIM / THREADS; ++it) {
+        const int keys = (it * (THREADS / HEAD_DIM) + threadIdx.x / HEAD_DIM) * 16;  // this thread's 16 keys
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint32_t b[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int key = keys + 4 * i + j;
+                const float x = __bfloat162float(tile[key][c]);
+                b[j] = PER_TOKEN ? code_bits(x, key_scale[key], key_inv[key]) : code_bits(x, scale, inv);
+            }
+            w[i] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+        }
+        dst[(keys / 16) * HEAD_DIM + c] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
 }
 
 }  // namespace unica

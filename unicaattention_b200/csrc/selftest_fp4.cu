@@ -8,6 +8,8 @@ namespace unica {
 
 // a_image [k / 32][128][16], b_image [k / 32][n][16] (two codes per byte); sfa [k / 64][128] words, sfb [k / 64][n]
 // words (byte i of a word scales elements 16 i .. 16 i + 15 of that K step); d float [128][n].
+// variant 0: scale words stored into tensor memory by the threads (tcgen05.st); 2: A's copied from shared memory by
+// the issuing thread (tcgen05.cp); 1: a deliberately wrong layout (diagnostic).
 __global__ void __launch_bounds__(128) selftest_mma_nvf4_kernel(const uint8_t* __restrict__ a_image, const uint8_t* __restrict__ b_image,
                                                                 const uint32_t* __restrict__ sfa, const uint32_t* __restrict__ sfb,
                                                                 int n, int k, int variant, float* __restrict__ d, int* status) {
@@ -17,6 +19,9 @@ __global__ void __launch_bounds__(128) selftest_mma_nvf4_kernel(const uint8_t* _
     __shared__ uint64_t done;
     __shared__ uint32_t tmem_base;
     __shared__ int abort_flag;
+    __shared__ __align__(128) uint32_t sfa_s[2][32][4];  // variant 2: A's scale words as tcgen05.cp takes them, [K step][lane][row / 32]
+    if (variant == 2)
+        for (int i = threadIdx.x; i < (k / 64) * 128; i += 128) sfa_s[i / 128][i % 32][i % 128 / 32] = sfa[i];
     for (int i = threadIdx.x; i < 64 * k / 16; i += 128) reinterpret_cast<uint4*>(a_s)[i] = reinterpret_cast<const uint4*>(a_image)[i];
     for (int i = threadIdx.x; i < n * k / 32; i += 128) reinterpret_cast<uint4*>(b_s)[i] = reinterpret_cast<const uint4*>(b_image)[i];
     if (threadIdx.x == 0) {
@@ -38,11 +43,12 @@ __global__ void __launch_bounds__(128) selftest_mma_nvf4_kernel(const uint8_t* _
     for (int s = 0; s < k_steps; ++s) {
         if (variant == 0) {
             tmem_st4(my + col_sfa + 4 * s, sfa[s * 128 + lane], sfa[s * 128 + 32 + lane], sfa[s * 128 + 64 + lane], sfa[s * 128 + 96 + lane]);
+        } else if (variant == 2) {  // A's scale words are copied from shared memory by the issuing thread below
         } else {  // diagnostic: row r in lane r, one column per K step
             tmem_st1(my + col_sfa + 4 * s, sfa[s * 128 + threadIdx.x]);
         }
         for (int c = 0; c < b_cols; ++c) {
-            const int row = variant == 0 ? 32 * c + lane : threadIdx.x + 128 * c;
+            const int row = variant != 1 ? 32 * c + lane : threadIdx.x + 128 * c;
             tmem_st1(my + col_sfb + b_cols * s + c, row < n ? sfb[s * n + row] : 0u);
         }
     }
@@ -52,6 +58,8 @@ __global__ void __launch_bounds__(128) selftest_mma_nvf4_kernel(const uint8_t* _
     tc_fence_after();
     if (threadIdx.x == 0) {
         const uint32_t idesc = idesc_nvf4(128, n);
+        if (variant == 2)
+            for (int s = 0; s < k_steps; ++s) tmem_cp_32x128b(tmem + col_sfa + 4 * s, smem_u32(&sfa_s[s][0][0]));
         for (int s = 0; s < k_steps; ++s)
             mma_nvf4_ss(tmem, smem_desc(smem_u32(a_s) + s * 2 * 128 * 16, 128 * 16, 128), smem_desc(smem_u32(b_s) + s * 2 * n * 16, n * 16, 128),
                         idesc, tmem + col_sfa + 4 * s, tmem + col_sfb + b_cols * s, s > 0);
