@@ -117,9 +117,12 @@ int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8
  * Operand layouts, per head (two e2m1 codes per byte, the lower contraction index in the low nibble; one e4m3 scale
  * byte per 16 elements along the contraction; keys of a 64-key tile in the reference's slot order, bench/emulate.py:116-119):
  *   Q4  [q_tiles (even)][4 chunks of 32 channels][128 rows][16]  8 KB/tile   SFQ [q_tiles][2 halves of 64 channels][128][4]
- *   K4  [k_tiles][4][64 slots][16]                               4 KB/tile   SFK [k_tiles][2][64][4]
- *   V4  [k_tiles][2 chunks of 32 slots][144 rows][16]            4.5 KB      SFV [k_tiles][160][4]
+ *   K4  [k_tiles][4][64 slots][16]                               4 KB/tile   SFK [k_tiles][32 lanes][4 words][4]
+ *   V4  [k_tiles][2 chunks of 32 slots][144 rows][16]            4.5 KB      SFV [k_tiles][2 blocks][32 lanes][4 words][4]
  *       rows 0..127 channels, rows 128..143 ones (their column of P.V is the softmax denominator)
+ *   K's and V's scale bytes lie as tcgen05.cp (32x128b) takes them, 16 bytes per tensor-memory lane: the word (four
+ *   bytes, one per 16-element block of a K = 64 step) of operand row r is word r / 32 of lane r % 32; K's two steps
+ *   follow each other (word 2 step + r / 32); V's second block holds rows 128..143 (word 0 of lanes 0..15: ones).
  *   bias [q_blocks][k_tiles * 64] float: the Q-smoothing term, already times log2(e)/sqrt(128), slot order */
 
 /* outer = max(max|x - mean| * (1/2688), 1e-30) per head from per-channel statistics (mean may be NULL; all

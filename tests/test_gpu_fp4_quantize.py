@@ -74,7 +74,9 @@ def test_v_bit_for_bit(n):
     assert np.array_equal(np_heads(codes)[live], o_codes[live])
     # the rows of ones and their scales
     ones = v4.codes[:, :, :, :, 128:]
-    assert torch.all(ones == 0x22) and torch.all(v4.sf[:, :, :, 128:144] == 0x38) and not v4.sf[:, :, :, 144:].any()
+    second = v4.sf[:, :, :, 128:].unflatten(3, (32, 4))  # [.., lane, word, byte]: rows 128..143 are word 0 of lanes 0..15
+    assert torch.all(ones == 0x22) and torch.all(second[:, :, :, :16, 0] == 0x38)
+    assert not second[:, :, :, 16:].any() and not second[:, :, :, :, 1:].any()
 
 
 def test_smooth_bias_is_exact_to_float():

@@ -15,11 +15,12 @@
 // O = O * 2^(m_old - m) + P^ . V^; out = O / (sum of P^) * v_outer.  The exponentials are ex2.approx, so a code of P
 // can land on the other side of a rounding tie than the emulation's: results agree to rounding, not bit for bit.
 //
-// Scale bytes live in tensor memory, row r of an operand in lane r % 32 of column r / 32 of every 32-lane quarter.  The
-// computing warps put them there with tcgen05.st: Q's once, K's and V's from the tile's shared-memory stage, P's after
-// exchanging the four bytes of each row through shared memory.
+// Scale bytes live in tensor memory, row r of an operand in lane r % 32 of column r / 32 of every 32-lane quarter.  Q's
+// are stored once by the computing warps (tcgen05.st); K's, V's and P's are copied from shared memory by the issuing
+// thread right before the MMA that reads them (tcgen05.cp 32x128b.warpx4: 16 bytes per lane, all four quarters), K's
+// and V's as the quantizers laid them out, P's as the computing threads wrote them a moment earlier.
 //
-// Tensor memory per query tile (256 columns): S 0..63 | O 64..207 | SF of Q 208..215, K 216..219, P 220..223, V 224..228.
+// Tensor memory per query tile (256 columns): S 0..63 | O 64..207 | SF of Q 208..215, K 216..219, P 220..223, V 224..231.
 // All waits are bounded (common.cuh).
 #include <cuda_fp8.h>
 
@@ -38,7 +39,7 @@ constexpr int SFQ_BYTES = 2 * QUERY_TILE * 4;        // 1024
 constexpr int K4_BYTES = KEY_TILE * HEAD_DIM / 2;    // 4096
 constexpr int SFK_BYTES = 2 * KEY_TILE * 4;          // 512
 constexpr int V4_TILE_ROWS = 144, V4_BYTES = 2 * V4_TILE_ROWS * 16;  // 4608
-constexpr int SFV_BYTES = 160 * 4;                   // 640
+constexpr int SFV_BYTES = 256 * 4;                   // 1024: two blocks of 32 lanes x 4 words
 constexpr int BIAS_BYTES = KEY_TILE * 4;             // 256
 constexpr int P4_BYTES = QUERY_TILE * KEY_TILE / 2;  // 4096
 constexpr int F4_TMEM_COLUMNS = 512;
@@ -74,16 +75,16 @@ struct __align__(128) Fp4Smem {
     uint8_t q[2][Q4_BYTES];
     uint32_t sfq[2][2][QUERY_TILE];
     uint8_t k[F4_STAGES][K4_BYTES];
-    uint32_t sfk[F4_STAGES][2][KEY_TILE];
+    uint32_t sfk[F4_STAGES][32][4];  // as tcgen05.cp takes them: lane, word 2 step + row / 32
     uint8_t v[F4_STAGES][V4_BYTES];
-    uint32_t sfv[F4_STAGES][160];
+    uint32_t sfv[F4_STAGES][2][32][4];  // block 0: channel c = word c / 32 of lane c % 32; block 1: the ones rows
     float bias[F4_STAGES][KEY_TILE];
     uint8_t p[2][P4_BYTES];
-    uint32_t sfp[2][QUERY_TILE];
+    uint32_t sfp[2][32][4];  // P's scale words of a query tile: row r = word r / 32 of lane r % 32
     uint2 exchange[2][2][2][QUERY_TILE];  // [query tile][tag parity][thread of the row][row] = {tag, value}
     float inv_e4m3[128];                  // 1 / value of every non-negative e4m3 byte, correctly rounded; 0 for the byte 0
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
-    uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], sfp_ready[2], drain[2];
+    uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], drain[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -140,7 +141,6 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             mbar_init(&sm.s_free[g], 2 * QUERY_TILE);  // both threads of every row
             mbar_init(&sm.p_ready[g], 2 * QUERY_TILE);
             mbar_init(&sm.o_full[g], 1);
-            mbar_init(&sm.sfp_ready[g], 2 * QUERY_TILE);
         }
         mbar_init(&sm.drain[0], 1);
         mbar_init(&sm.drain[1], 1);
@@ -204,6 +204,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 if (!mbar_wait(&sm.s_free[g], n & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sm.k[stage]);
+                tmem_cp_32x128b(base + F4_SFK, smem_u32(sm.sfk[stage]));  // K's scale bytes; ordered before the MMAs below
 #pragma unroll
                 for (int ks = 0; ks < 2; ++ks)
                     mma_nvf4_ss(base + F4_S, smem_desc(q_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
@@ -221,6 +222,9 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                      mbar_wait(&sm.p_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
                 if (!ok) break;
                 tc_fence_after();
+                tmem_cp_32x128b(base + F4_SFP, smem_u32(sm.sfp[g]));  // the scale bytes of P^ and of V
+                tmem_cp_32x128b(base + F4_SFV, smem_u32(sm.sfv[stage][0]));
+                tmem_cp_32x128b(base + F4_SFV + 4, smem_u32(sm.sfv[stage][1]));
                 mma_nvf4_ss(base + F4_O, smem_desc(smem_u32(sm.p[g]), QUERY_TILE * 16, 128),
                             smem_desc(smem_u32(sm.v[stage]), V4_TILE_ROWS * 16, 128), IDESC_F4_PV, base + F4_SFP, base + F4_SFV, t > 0);
                 mma_commit(&sm.o_full[g]);
@@ -237,7 +241,6 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         // Two threads per query row: warp = 8 g + 4 half + quarter, both on tensor-memory lane 32 quarter + lane.  Thread
         // `half` takes slots 32 half .. 32 half + 31 of every tile (two scale blocks of P) and output channels 64 half ..
         // 64 half + 63; the two meet in one number per tile, the maximum of their scores (a tagged word in shared memory).
-        // Half 0 also stores K's and P's scale bytes into tensor memory, half 1 V's.
         const int g = warp / 8, half = (warp / 4) % 2, row = (warp % 4) * 32 + lane;
         const int q_row = (2 * blockIdx.x + g) * QUERY_TILE + row;
         const uint32_t my = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256;
@@ -252,7 +255,6 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 #pragma unroll
                 for (int s = 0; s < 2; ++s)
                     tmem_st4(my + F4_SFQ + 4 * s, sm.sfq[g][s][lane], sm.sfq[g][s][32 + lane], sm.sfq[g][s][64 + lane], sm.sfq[g][s][96 + lane]);
-                tmem_st4(my + F4_SFK, sm.sfk[0][0][lane], sm.sfk[0][0][32 + lane], sm.sfk[0][1][lane], sm.sfk[0][1][32 + lane]);
                 tmem_wait_st();
             }
             tc_fence_before();
@@ -299,15 +301,8 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             tmem_ld32_async(my + F4_S + half * F4_HALF_SLOTS, x);
             tmem_wait_ld();
             reg_fence16(x);
-            if (half == 0 && t + 1 < k_tiles) {  // the next K tile's scale bytes, then the scores buffer goes back
-                const int next = (t + 1) % F4_STAGES;
-                ok = mbar_wait_warp(&sm.k_full[next], ((t + 1) / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
-                if (!ok) break;
-                tmem_st4(my + F4_SFK, sm.sfk[next][0][lane], sm.sfk[next][0][32 + lane], sm.sfk[next][1][lane], sm.sfk[next][1][32 + lane]);
-                tmem_wait_st();
-            }
             tc_fence_before();
-            mbar_arrive(&sm.s_free[g]);
+            mbar_arrive(&sm.s_free[g]);  // the scores are in registers: the buffer goes back
             F4_TRACE(F4_TR_LOAD_S);
 
             // scores in the log2 domain, the smoothing term added back, slots past the last key out of the maximum
@@ -402,20 +397,11 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             }
             // P.V of the previous tile has read P^: this tile's codes and scale bytes may take its place
             *reinterpret_cast<uint4*>(sm.p[g] + half * (QUERY_TILE * 16) + row * 16) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-            reinterpret_cast<uint16_t*>(&sm.sfp[g][row])[half] = uint16_t(sf_pair);  // bytes 2 half, 2 half + 1 of the row's word
-            mbar_arrive(&sm.sfp_ready[g]);  // an mbarrier, not bar.sync: its wait is bounded like every other
+            reinterpret_cast<uint16_t*>(&sm.sfp[g][row % 32][row / 32])[half] = uint16_t(sf_pair);  // bytes 2 half, 2 half + 1 of the row's word
             F4_TRACE(F4_TR_RESCALE);
-            if (half == 0) {  // every 32-lane quarter of tensor memory needs the scale bytes of all 128 rows of P
-                ok = mbar_wait_warp(&sm.sfp_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
-                if (!ok) break;
-                tmem_st4(my + F4_SFP, sm.sfp[g][lane], sm.sfp[g][32 + lane], sm.sfp[g][64 + lane], sm.sfp[g][96 + lane]);
-            } else {  // and of V's 144 rows
-                tmem_st4(my + F4_SFV, sm.sfv[stage][lane], sm.sfv[stage][32 + lane], sm.sfv[stage][64 + lane], sm.sfv[stage][96 + lane]);
-                tmem_st1(my + F4_SFV + 4, sm.sfv[stage][128 + lane]);
-            }
-            tmem_wait_st();
+            tmem_wait_st();  // the rescaled O, if any
             tc_fence_before();
-            fence_proxy_async();
+            fence_proxy_async();  // P^ and its scale bytes are read by the tensor pipe (tcgen05.cp, tcgen05.mma)
             mbar_arrive(&sm.p_ready[g]);
             F4_TRACE(F4_TR_EXCHANGE);
         }

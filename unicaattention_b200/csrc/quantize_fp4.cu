@@ -17,7 +17,7 @@ namespace unica {
 
 constexpr int FP4_THREADS = 256;
 constexpr int V4_ROWS = 144;      // 128 channels + 16 rows of ones: their column of P.V is the running denominator
-constexpr int V4_SF_ROWS = 160;   // scale words: 5 tensor-memory columns of 32 rows
+constexpr int V4_SF_WORDS = 256;  // scale words of a tile: two blocks of [32 lanes][4], the second for rows 128..143
 
 __host__ __device__ __forceinline__ int slot_key(int k) { return 32 * (k / 32) + 8 * (k % 8 / 2) + 2 * (k % 32 / 8) + k % 2; }
 
@@ -78,7 +78,8 @@ __global__ void __launch_bounds__(HEAD_DIM) nvfp4_outer_rows_kernel(const float*
 // Q or K minus its mean in NVFP4 along the channels, one block per tile of ROWS tokens (128: Q, 64: K).
 // SLOTS: row r of a tile holds token tile * 64 + slot_key(r) (K); else token tile * ROWS + r (Q).
 // mean: [heads][groups][128], one group per mean_tokens tokens, or null.
-// codes: [heads][tiles][4 chunks of 32 channels][ROWS][16] bytes; sf: [heads][tiles][2 halves of 64 channels][ROWS][4] bytes.
+// codes: [heads][tiles][4 chunks of 32 channels][ROWS][16] bytes; sf: Q [heads][tiles][2 halves of 64 channels][128][4]
+// bytes, K [heads][tiles][32 lanes][4 words][4] bytes (see the store below).
 template <int ROWS, bool SLOTS>
 __global__ void __launch_bounds__(FP4_THREADS) quantize_rows_fp4_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
                                                                          const float* __restrict__ mean, int mean_tokens, int groups,
@@ -119,14 +120,18 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_rows_fp4_kernel(const __
         uint2 packed;
         quantize_block16(v, head_outer, byte, packed);
         *reinterpret_cast<uint2*>(tile_codes + ((block / 2) * ROWS + row) * 16 + (block % 2) * 8) = packed;
-        tile_sf[((block / 4) * ROWS + row) * 4 + block % 4] = uint8_t(byte);
+        // the word of (K step = block / 4, row): Q [2][128] by row; K [32 lanes][4]: word 2 step + row / 32 of lane row % 32,
+        // the 16 bytes tcgen05.cp hands to one tensor-memory lane
+        const int word = ROWS == 64 ? (row % 32) * 4 + 2 * (block / 4) + row / 32 : (block / 4) * ROWS + row;
+        tile_sf[word * 4 + block % 4] = uint8_t(byte);
     }
 }
 
 // V in NVFP4 along the keys, per channel, one block per tile of 64 keys (slot order).  low/high: the channel's min and
 // max over the head ([heads][128]); v_outer [heads][128] is written by tile 0.
 // codes: [heads][tiles][2 chunks of 32 slots][144 rows][16] bytes, rows 128..143 all ones (code 0x2);
-// sf: [heads][tiles][160 rows][4] bytes, rows 128..143 ones (0x38), rows 144..159 zeros.
+// sf: [heads][tiles][2 blocks][32 lanes][4 words] of 4 bytes: block 0 word c / 32 of lane c % 32 = channel c's four
+// bytes, block 1 word 0 of lanes 0..15 = ones (0x38) for rows 128..143, zeros elsewhere.
 __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_bfloat16* __restrict__ v, TokenLayout in,
                                                                       const float* __restrict__ low, const float* __restrict__ high,
                                                                       int n_tokens, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
@@ -153,7 +158,7 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_
     }
     __syncthreads();
     uint8_t* tile_codes = codes + (size_t(head) * gridDim.x + t) * (V4_ROWS * 32);
-    uint8_t* tile_sf = sf + (size_t(head) * gridDim.x + t) * (V4_SF_ROWS * 4);
+    uint8_t* tile_sf = sf + (size_t(head) * gridDim.x + t) * (V4_SF_WORDS * 4);
     for (int item = threadIdx.x; item < HEAD_DIM * 4; item += FP4_THREADS) {
         const int c = item % HEAD_DIM, block = item / HEAD_DIM;  // block of 16 slots
         const int ci = head * HEAD_DIM + c;
@@ -166,13 +171,14 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_
         uint2 packed;
         quantize_block16(x, outer, byte, packed);
         *reinterpret_cast<uint2*>(tile_codes + ((block / 2) * V4_ROWS + c) * 16 + (block % 2) * 8) = packed;
-        tile_sf[c * 4 + block] = uint8_t(byte);
+        tile_sf[((c % 32) * 4 + c / 32) * 4 + block] = uint8_t(byte);  // word c / 32 of lane c % 32
     }
     for (int item = threadIdx.x; item < 2 * 16 * 4; item += FP4_THREADS) {  // the rows of ones: 2 chunks x 16 rows x 4 words
         const int chunk = item / 64, row = 128 + item / 4 % 16, word = item % 4;
         reinterpret_cast<uint32_t*>(tile_codes + (chunk * V4_ROWS + row) * 16)[word] = 0x22222222u;
     }
-    if (threadIdx.x < 32) reinterpret_cast<uint32_t*>(tile_sf)[128 + threadIdx.x] = threadIdx.x < 16 ? 0x38383838u : 0u;
+    if (threadIdx.x < 128)  // second block: rows 128..143 (ones) are word 0 of lanes 0..15, the rest zeros
+        reinterpret_cast<uint32_t*>(tile_sf)[128 + threadIdx.x] = threadIdx.x % 4 == 0 && threadIdx.x / 4 < 16 ? 0x38383838u : 0u;
 }
 
 // The part of the scores that Q smoothing took out, added back exactly (bench/emulate.py:308-309; the reference's

@@ -16,21 +16,23 @@ from unicaattention_b200 import lib
 
 HEAD_DIM = 128
 FP4_TILE = 64
-V4_ROWS, V4_SF_ROWS = 144, 160
+V4_ROWS, V4_SF_WORDS = 144, 256
 LOG2E = 1.4426950408889634
 E2M1_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)
 SLOT_KEY = tuple(32 * (k // 32) + 8 * (k % 8 // 2) + 2 * (k % 32 // 8) + k % 2 for k in range(64))  # slot -> key in a tile
 
 
 class FP4Rows(NamedTuple):
-    """Q or K in NVFP4: codes uint8 [batch, heads, tiles, 4, rows, 16], scale bytes uint8 [batch, heads, tiles, 2, rows, 4]."""
+    """Q or K in NVFP4: codes uint8 [batch, heads, tiles, 4, rows, 16]; scale bytes uint8, Q [batch, heads, tiles, 2, 128, 4],
+    K [batch, heads, tiles, 32, 4, 4] (lane, word 2 step + row / 32, byte: the order tcgen05.cp takes)."""
 
     codes: torch.Tensor
     sf: torch.Tensor
 
 
 class FP4V(NamedTuple):
-    """V in NVFP4: codes uint8 [batch, heads, tiles, 2, 144, 16], scale bytes uint8 [batch, heads, tiles, 160, 4]."""
+    """V in NVFP4: codes uint8 [batch, heads, tiles, 2, 144, 16], scale bytes uint8 [batch, heads, tiles, 256, 4] (two blocks
+    of 32 lanes x 4 words: channel c is word c / 32 of lane c % 32; the second block is the ones rows')."""
 
     codes: torch.Tensor
     sf: torch.Tensor
@@ -70,7 +72,7 @@ def quantize_fp4_rows(x: torch.Tensor, mean: torch.Tensor | None, pad_to: int = 
     need = math.ceil(n / rows)
     tiles = need if tiles is None else tiles
     codes = torch.empty(batch, heads, tiles, 4, rows, 16, dtype=torch.uint8, device=x.device)
-    sf = torch.empty(batch, heads, tiles, 2, rows, 4, dtype=torch.uint8, device=x.device)
+    sf = torch.empty((batch, heads, tiles, 32, 4, 4) if rows == 64 else (batch, heads, tiles, 2, rows, 4), dtype=torch.uint8, device=x.device)
     lib.call("unica_b200_quantize_fp4_rows" + ("_rope" if rope is not None else ""), lib.ptr(x), _layout(x), lib.ptr(mean_arg), per,
              *unica.rope_args(rope, x), lib.ptr(outer), batch * heads, n, rows, tiles, lib.ptr(codes), lib.ptr(sf), lib.stream())
     return FP4Rows(codes, sf), outer
@@ -87,7 +89,7 @@ def quantize_v4(v: torch.Tensor) -> tuple[FP4V, torch.Tensor]:
     tiles = math.ceil(n / FP4_TILE)
     _, low, high = unica._stats(v, 0)
     codes = torch.empty(batch, heads, tiles, 2, V4_ROWS, 16, dtype=torch.uint8, device=v.device)
-    sf = torch.empty(batch, heads, tiles, V4_SF_ROWS, 4, dtype=torch.uint8, device=v.device)
+    sf = torch.empty(batch, heads, tiles, V4_SF_WORDS, 4, dtype=torch.uint8, device=v.device)
     outer = torch.empty(batch, heads, HEAD_DIM, device=v.device)
     lib.call("unica_b200_quantize_v_fp4", lib.ptr(v), _layout(v), lib.ptr(low), lib.ptr(high), batch * heads, n, lib.ptr(codes),
              lib.ptr(sf), lib.ptr(outer), lib.stream())
@@ -130,7 +132,10 @@ def decode_fp4_rows(x4: FP4Rows, n: int, slots: bool = False) -> tuple[torch.Ten
     codes, sf = x4
     batch, heads, tiles, _, rows, _ = codes.shape
     c = _nibbles(codes.permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles * rows, 64))  # [.., rows, 128]
-    s = sf.permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles * rows, 8)
+    if rows == 64:  # K: [tiles, lane, (step, row / 32), byte] -> [tiles, row = 32 (row / 32) + lane, (step, byte)]
+        s = sf.view(batch, heads, tiles, 32, 2, 2, 4).permute(0, 1, 2, 5, 3, 4, 6).reshape(batch, heads, tiles * rows, 8)
+    else:
+        s = sf.permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles * rows, 8)
     if slots:  # row r of a tile holds key slot_key(r): put the keys back in order
         key_of = torch.tensor(SLOT_KEY, device=codes.device)
         order = (torch.arange(tiles, device=codes.device)[:, None] * rows + key_of).flatten()
@@ -146,5 +151,6 @@ def decode_v4(v4: FP4V) -> tuple[torch.Tensor, torch.Tensor]:
     batch, heads, tiles = codes.shape[:3]
     c = _nibbles(codes[:, :, :, :, :HEAD_DIM].permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles, HEAD_DIM, 32))  # [.., ch, 64 slots]
     c = c.transpose(-1, -2).reshape(batch, heads, tiles * FP4_TILE, HEAD_DIM)
-    s = sf[:, :, :, :HEAD_DIM].transpose(-1, -2)  # [.., tiles, 4, 128]
+    s = sf[:, :, :, :HEAD_DIM].view(batch, heads, tiles, 32, 4, 4).permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles, HEAD_DIM, 4)
+    s = s.transpose(-1, -2)  # channel c = 32 (c / 32) + lane -> [.., tiles, 4, 128]
     return c, s
