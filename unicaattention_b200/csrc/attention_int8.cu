@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < KEY_TILE / 32; ++ks)
                     mma_i8_ss(base + COL_ACC, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, V_TOKEN || ks > 0);
+                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, ks > 0);  // the first instruction of a tile overwrites the accumulator
                 mma_commit(&sm.acc_full[g]);
                 mma_commit(&sm.v_empty[stage]);
                 if (t + 2 < k_tiles) ok = scores(t + 2);
@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         // Every accumulator starts at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
         uint32_t magic[FILL_BLOCK];
         fill_block_init(magic, MAGIC_BITS);
-        tmem_fill<V_TOKEN ? 256 : 128>(t_scores, magic);  // both score buffers; per token the P.V accumulator too
+        tmem_fill<128>(t_scores, magic);  // both score buffers
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(&sm.s_free[g][0]);
@@ -469,8 +469,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sm.s_free[g][buf]);
-                const float m_new = fmaxf(m, tile_max);
-                alpha = ex2(m - m_new);
+                const bool first = m == -INFINITY;  // m: the reference exponent of the row's sums, as in the fused steps
+                const float m_new = tile_max > m + REFERENCE_SLACK ? tile_max : m;
+                alpha = first ? 1.0f : ex2(m - m_new);
                 beta = ex2(tile_max - m_new);
                 m = m_new;
                 const float offset = LOG2_255 - tile_max;
@@ -534,13 +535,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     }
                     float2 f[8];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) f[i] = add2(a[part % 4][i], minus_magic);
+                    for (int i = 0; i < 8; ++i)  // the accumulator holds plain integers
+                        f[i] = make_float2(__int2float_rn(__float_as_int(a[part % 4][i].x)), __int2float_rn(__float_as_int(a[part % 4][i].y)));
                     if (part + 4 < HEAD_DIM / 16) tmem_ld16_async(t_acc + (part + 4) * 16, a[part % 4]);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) o[part * 8 + i] = fma2(beta2, f[i], o[part * 8 + i]);
-                    if (part % 2 == 1) tmem_fill<32>(t_acc + (part - 1) * 16, magic);
                 }
-                tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&sm.acc_free[g]);
                 TRACE(TR_FLUSH);
