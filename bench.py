@@ -65,17 +65,20 @@ def build_inputs(batch, heads_slice, tokens, pin=True):
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while the timed region runs."""
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 50 ms.  Started before the warm-up (the tool's own
+    start-up takes driver locks for a few milliseconds: that must not fall into the timed region); `mark()` at the start of
+    the timed region, and only the samples after it count."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
         self.lines: list[str] = []
+        self.first = 0
         self.proc = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -85,6 +88,9 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
+    def mark(self):
+        self.first = len(self.lines)
+
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -92,7 +98,7 @@ class ClockSampler:
         self.thread.join(timeout=2)
         sm, sm_max, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        for line in self.lines[self.first:] or self.lines[-1:]:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -240,10 +246,12 @@ def main():
             step(q, k, v)
         unica.check_status(device)
         return
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(args.warmup):
         step(q, k, v)
     unica.check_status(device)
-    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.mark()
     ms_step = timed(lambda: step(q, k, v), args.steps)
     clocks = sampler.stop() if sampler else None
     total_ops = ops(batch, heads, tokens, tokens)
