@@ -119,3 +119,24 @@ def test_rejects_what_the_kernel_cannot_take():
         unica.attention(b, b, b, NOPE=1)
     with pytest.raises(ValueError):
         unica.attention(b.cpu(), b.cpu(), b.cpu())
+
+
+@pytest.mark.parametrize("preset", ["per_channel", "fast"])
+def test_host_memory_call_is_the_device_call(preset):
+    """attention_host sends the heads through the GPU in groups with the copies overlapping the kernels: bit for bit the
+    result of one call on the whole tensors, for pinned and for pageable host memory."""
+    import unicaattention_b200 as unica
+
+    q, k, v = qkv(1, 7, 600, 600, seed=5)
+    whole = unica.attention(q.cuda(), k.cuda(), v.cuda(), **unica.PRESETS[preset]).cpu()
+    pinned = [x.pin_memory() for x in (q, k, v)]
+    out = unica.attention_host(*pinned, heads_per_group=3, **unica.PRESETS[preset])
+    torch.cuda.synchronize()
+    assert out.is_pinned() and torch.equal(out, whole)
+    again = torch.empty_like(out)
+    assert unica.attention_host(q, k, v, out=again, **unica.PRESETS[preset]) is again
+    torch.cuda.synchronize()
+    assert torch.equal(again, whole)
+    unica.check_status()
+    with pytest.raises(ValueError):
+        unica.attention_host(q.cuda(), k.cuda(), v.cuda())

@@ -455,3 +455,4 @@ def sm_count(device: torch.device) -> int:
 
 from unicaattention_b200.fp4 import (FP4V, FP4Rows, decode_fp4_rows, decode_v4, quantize_fp4_rows, quantize_v4,  # noqa: E402,F401
                                      smooth_bias)
+from unicaattention_b200.host import attention_host  # noqa: E402,F401

@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             auto scores = [&](int n) -> bool {
                 const int stage = n % STAGES, buf = n & 1;
                 if (!mbar_wait(&sm.k_full[stage], (n / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
-                if ((V_TOKEN || n < 2) && !mbar_wait(&sm.s_free[g][buf], (n >> 1) & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
+                if (n < 2 && !mbar_wait(&sm.s_free[g][buf], (n >> 1) & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sm.k[stage]);
 #pragma unroll
@@ -188,13 +188,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             for (int t = 0; ok && t < k_tiles; ++t) {
                 const int stage = t % STAGES, buf = t & 1;
                 ok = mbar_wait(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
-                if (V_TOKEN) {
-                    ok = ok && mbar_wait(&sm.p_ready[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_P) &&
-                         mbar_wait(&sm.acc_free[g], t & 1, abort_flag, status, STATUS_WAIT_FREE);
-                } else {  // K(t + 2) has long landed: probing it before the step's end keeps that probe off the critical path
-                    if (t + 2 < k_tiles) ok = ok && mbar_wait(&sm.k_full[(t + 2) % STAGES], ((t + 2) / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
-                    ok = ok && mbar_wait(&sm.step_done[g], t & 1, abort_flag, status, STATUS_WAIT_P);
-                }
+                // K(t + 2) has long landed: probing it before the step's end keeps that probe off the critical path
+                if (t + 2 < k_tiles) ok = ok && mbar_wait(&sm.k_full[(t + 2) % STAGES], ((t + 2) / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+                ok = ok && mbar_wait(&sm.step_done[g], t & 1, abort_flag, status, STATUS_WAIT_P);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t p_addr = smem_u32(sm.p[g][buf]), v_addr = smem_u32(sm.v[stage]);
@@ -249,9 +245,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         mbar_arrive(&sm.acc_free[g]);
         // Per token the second query tile starts when the first has delivered its first P^, so that the two begin out of
         // step (exponentials against flush); the fused steps of the other modes mix both kinds of work anyway.
-        if (V_TOKEN && g == 1) ok = mbar_wait_warp(&sm.p_ready[0][0], 0, abort_flag, status, STATUS_WAIT_P);
 
-        if constexpr (!V_TOKEN) {
+        if constexpr (true) {
             // One step of the loop: the scores of key tile `ts` become P^ in shared memory (SOFT) while the accumulator of
             // tile `tf` is flushed into `out` (FLUSH).  In the steady state both happen, interleaved 16 keys and 32 channels
             // at a time in one straight run of instructions, so that the exponentials (XU), the flush's multiply-adds (FMA
@@ -283,32 +278,49 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 if (tracing && ts >= 100 && ts < 108) g_trace[2 + g][ts - 100] = clock64();  // when the steps of tiles 100..107 began
 #endif
                 const float2 c2 = make_float2(c, c);
-                const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
-                const float2* inv_s = reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE);
+                const float4* log_s4 = reinterpret_cast<const float4*>(sm.tok[stage]);
+                const float4* inv_s4 = reinterpret_cast<const float4*>(sm.tok[stage] + KEY_TILE);
                 if (SOFT) {
                     // Pass 1: the tile maximum.  The 64 scores are not kept: the row's 128 output channels and the flush's
                     // accumulator values fill the register file, so pass 2 reads the scores again, 16 at a time.
                     float tile_max;
-                    {
+                    if (!V_TOKEN) {
                         float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
                         tmem_ld64_sync(t_scores + buf * 64, x);
-                        if (V_TOKEN) {
-#pragma unroll
-                            for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
-                        }
                         if (MASKED) {  // keys past the end: below every real score (|score| < 2^21)
-                            const float low = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
 #pragma unroll
                             for (int j = 0; j < KEY_TILE; ++j)
-                                if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = low;
+                                if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = MAGIC - 4194303.0f;
                         }
                         float top[4];
 #pragma unroll
                         for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
 #pragma unroll
                         for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
+                        tile_max = (fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) - MAGIC) * c;
+                    } else {  // log2 s_j joins the scores before the maximum; 32 keys at a time (registers)
+                        float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                        for (int part = 0; part < 2; ++part) {
+                            float2 x[KEY_TILE / 4];
+                            tmem_ld32_async(t_scores + buf * 64 + part * 32, x);
+                            tmem_wait_ld();
+                            reg_fence16(x);
+#pragma unroll
+                            for (int j = 0; j < KEY_TILE / 4; j += 2) {  // 16-byte loads: the loop is short of load slots, not of bytes
+                                const float4 l = log_s4[part * 8 + j / 2];
+                                x[j] = fma2(add2(x[j], minus_magic), c2, make_float2(l.x, l.y));
+                                x[j + 1] = fma2(add2(x[j + 1], minus_magic), c2, make_float2(l.z, l.w));
+                            }
+                            if (MASKED) {
+#pragma unroll
+                                for (int j = 0; j < KEY_TILE / 2; ++j)
+                                    if (part * 32 + j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
+                            }
+#pragma unroll
+                            for (int j = 0; j < KEY_TILE / 4; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
+                        }
                         tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-                        if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
                     }
                     // `m` is the exponent the row's sums are kept at, not the running maximum: out = sum over tiles of
                     // 2^(tile max - m) * acc, the same for the denominator, and the common factor cancels at the end.  The
@@ -345,13 +357,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                         reg_fence8(x[step % 2]);
                         if (step + 1 < KEY_TILE / 16) tmem_ld16_async(t_scores + buf * 64 + (step + 1) * 16, x[(step + 1) % 2]);
                     }
-                    float2 f[16];  // MAGIC taken off the accumulator values: their registers go back to the next loads at once
+                    // Per channel the accumulator values are converted at once and their registers go back to the next loads;
+                    // per token (log2 s_j and 1 / s_j on top) the registers do not reach that far: the values are used where
+                    // they are and the next loads follow the flush arithmetic, with the exponentials still ahead to cover them.
+                    constexpr bool STAGED = !V_TOKEN;
+                    float2 f[STAGED ? 16 : 1];
                     if (FLUSH) {
                         reg_fence8(a[0]);
                         reg_fence8(a[1]);
+                        if (STAGED) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i)  // the accumulator is overwritten by every tile's P.V: plain integers
-                            f[i] = make_float2(__int2float_rn(__float_as_int(a[i / 8][i % 8].x)), __int2float_rn(__float_as_int(a[i / 8][i % 8].y)));
+                            for (int i = 0; i < 16; ++i)  // the accumulator is overwritten by every tile's P.V: plain integers
+                                f[STAGED ? i : 0] = make_float2(__int2float_rn(__float_as_int(a[i / 8][i % 8].x)), __int2float_rn(__float_as_int(a[i / 8][i % 8].y)));
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                float2 v = o[step * 16 + i];
+                                if (RESCALE) v = mul2(v, alpha2);
+                                o[step * 16 + i] = fma2(beta2, make_float2(__int2float_rn(__float_as_int(a[i / 8][i % 8].x)), __int2float_rn(__float_as_int(a[i / 8][i % 8].y))), v);
+                            }
+                        }
                         if (step + 1 < KEY_TILE / 16) {
                             reg_fence8(a[0]);
                             reg_fence8(a[1]);
@@ -364,13 +389,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint32_t pair[2];
+                            float4 l = make_float4(0.0f, 0.0f, 0.0f, 0.0f), r = l;  // log2 s and 1 / s of the four keys
+                            if (V_TOKEN) l = log_s4[step * 4 + i], r = inv_s4[step * 4 + i];
 #pragma unroll
-                            for (int h = 0; h < 2; ++h) {
-                                const int j = step * 8 + i * 2 + h;  // a pair of keys
-                                float2 e = fma2(add2(x[step % 2][i * 2 + h], minus_magic), c2, V_TOKEN ? log_s[j] : offset2);
+                            for (int h = 0; h < 2; ++h) {  // a pair of keys
+                                float2 e = fma2(add2(x[step % 2][i * 2 + h], minus_magic), c2, V_TOKEN ? (h ? make_float2(l.z, l.w) : make_float2(l.x, l.y)) : offset2);
                                 if (V_TOKEN) e = add2(e, offset2);
                                 const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                                if (V_TOKEN) fsum = fma2(p, inv_s[j], fsum);
+                                if (V_TOKEN) fsum = fma2(p, h ? make_float2(r.z, r.w) : make_float2(r.x, r.y), fsum);
                                 const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
                                 pair[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
                             }
@@ -382,12 +408,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                             if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
                         }
                     }
-                    if (FLUSH) {  // out = out * alpha + beta * float(acc), channels 32 step .. 32 step + 31
+                    if (FLUSH && STAGED) {  // out = out * alpha + beta * float(acc), channels 32 step .. 32 step + 31
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
                             float2 v = o[step * 16 + i];
                             if (RESCALE) v = mul2(v, alpha2);
-                            o[step * 16 + i] = fma2(beta2, f[i], v);
+                            o[step * 16 + i] = fma2(beta2, f[STAGED ? i : 0], v);
                         }
                     }
                     if (SOFT) *reinterpret_cast<uint4*>(p_row + step * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);

@@ -1,0 +1,66 @@
+"""attention() for tensors that live in host memory: the heads go through the GPU in groups, so that the copy of the next
+group's q, k, v, the kernels of this one and the copy of the previous group's output run at the same time (three
+streams).  Heads are independent (every head has its own statistics and scales), so the result is bit for bit that of
+one call on the whole tensors.
+
+The reference has no such call: its callers hold their tensors on the GPU.  It is here for hosts that do not (the C-ABI
+side of the boundary works on device pointers only), and it is what bench.py times as `e2e`.
+"""
+
+from __future__ import annotations
+
+import torch
+
+import unicaattention_b200 as unica
+
+_STREAMS: dict = {}
+
+
+def _streams(device: torch.device):
+    if device not in _STREAMS:
+        _STREAMS[device] = (torch.cuda.Stream(device), torch.cuda.Stream(device))
+    return _STREAMS[device]
+
+
+def attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,
+                   device: torch.device | int | None = None, heads_per_group: int | None = None, **settings) -> torch.Tensor:
+    """softmax(q k^T / sqrt(d)) v for q [batch, heads, n_queries, 128], k, v [batch, heads, n_keys, 128] in HOST memory
+    (pinned memory, and batch 1 or a layout whose head slices are contiguous, for the copies to overlap the kernels).
+    `settings`: kernel / tile settings as for attention(), e.g. **PRESETS["per_channel"]; rope= stays a GPU tensor.
+    Returns `out` (made in pinned memory when not given), valid once the current stream of `device` has been
+    synchronised: nothing here waits for the GPU."""
+    if q.is_cuda or k.is_cuda or v.is_cuda:
+        raise ValueError("attention_host takes host tensors; use attention() for tensors on the GPU")
+    if q.dim() != 4 or k.shape != v.shape or k.shape[:2] != q.shape[:2]:
+        raise ValueError(f"q [batch, heads, n_queries, 128] and k, v [batch, heads, n_keys, 128] expected, "
+                         f"got {tuple(q.shape)}, {tuple(k.shape)}, {tuple(v.shape)}")
+    device = torch.device("cuda", torch.cuda.current_device() if device is None else device) if not isinstance(device, torch.device) else device
+    batch, heads = q.shape[:2]
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
+    elif out.shape != q.shape or out.dtype != q.dtype or out.is_cuda:
+        raise ValueError("out must be a host tensor like q")
+    group = heads_per_group or max(1, -(-heads // 5))
+    with torch.cuda.device(device):
+        compute = torch.cuda.current_stream(device)
+        copy_in, copy_out = _streams(device)
+        qd, kd, vd = (torch.empty(x.shape, dtype=x.dtype, device=device) for x in (q, k, v))
+        copy_in.wait_stream(compute)  # the staging memory may still be in use by work queued before this call
+        copy_out.wait_stream(compute)
+        for first in range(0, heads, group):
+            piece = slice(first, min(first + group, heads))
+            with torch.cuda.stream(copy_in):
+                for dst, src in ((qd, q), (kd, k), (vd, v)):
+                    dst[:, piece].copy_(src[:, piece], non_blocking=True)
+                arrived = torch.cuda.Event()
+                arrived.record(copy_in)
+            compute.wait_event(arrived)
+            result = unica.attention(qd[:, piece], kd[:, piece], vd[:, piece], **settings)
+            done = torch.cuda.Event()
+            done.record(compute)
+            copy_out.wait_event(done)
+            with torch.cuda.stream(copy_out):
+                out[:, piece].copy_(result, non_blocking=True)
+            result.record_stream(copy_out)  # keep its memory until the copy has run
+        compute.wait_stream(copy_out)  # a synchronise of the current stream now covers the copies back
+    return out
