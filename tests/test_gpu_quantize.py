@@ -30,6 +30,12 @@ def test_statistics(shape):
             assert np.array_equal(got.cpu().numpy().reshape(want.shape), want)
     with pytest.raises(ValueError):
         unica.rope_stats(x.cuda(), None, 100)
+    # the per-block partials (the reference's block_stats): sums in the fixed lane order, minima and maxima exact
+    partial = unica.block_stats(x.cuda()).cpu().numpy().reshape(-1, -(-shape[2] // 256), 3, 128)
+    for b in range(partial.shape[1]):
+        block = xf[:, 256 * b:256 * (b + 1)]
+        assert np.array_equal(partial[:, b, 1], block.min(1)) and np.array_equal(partial[:, b, 2], block.max(1))
+        assert np.allclose(partial[:, b, 0], block.sum(1, dtype=np.float64), rtol=1e-5, atol=1e-4)
 
 
 @pytest.mark.parametrize("shape", SHAPES)

@@ -145,6 +145,34 @@ def _stats(x: torch.Tensor, per: int, rope: torch.Tensor | None = None) -> tuple
 
 
 @on_their_device
+def block_stats(x: torch.Tensor, rope: torch.Tensor | None = None) -> torch.Tensor:
+    """Sum, min and max per channel over each block of STATS_TOKENS tokens of x (rotated by rope first, if given):
+    float32 [batch, heads, blocks, 3, 128] (unica/__init__.py:580-589).  rope_stats is this plus the reduction over blocks."""
+    _check_input(x, "x")
+    x = readable(x)
+    batch, heads, n, _ = x.shape
+    blocks = math.ceil(n / STATS_TOKENS)
+    partial = torch.empty(batch * heads, blocks, 3, HEAD_DIM, device=x.device)
+    scratch = torch.empty(3, batch, heads, 1, HEAD_DIM, device=x.device)
+    lib.call("unica_b200_channel_stats" + ("_rope" if rope is not None else ""), lib.ptr(x), token_layout(x), *rope_args(rope, x),
+             batch * heads, n, 0, lib.ptr(partial), lib.ptr(scratch[0]), lib.ptr(scratch[1]), lib.ptr(scratch[2]), lib.stream())
+    return partial.view(batch, heads, blocks, 3, HEAD_DIM)
+
+
+def wave_layout(heads: int, n_queries: int, n_keys: int, v_token: int, device) -> dict:
+    """The reference picks between a 4-warp and an 8-warp block per call (unica/__init__.py:281-285).  Here the block is
+    fixed (two query tiles sharing every K and V tile), so there is nothing to pick: always {}."""
+    return {}
+
+
+def source(kernel: str, tile: dict) -> str:
+    """The translation unit a call runs (the reference names the .cu file it builds, unica/__init__.py:256-261): the
+    library is built ahead of time, every setting is a run-time argument."""
+    _settings(kernel, tile)
+    return "attention_fp4" if kernel == "attention_fp4" else "attention_int8"
+
+
+@on_their_device
 def rope_stats(x: torch.Tensor, rope: torch.Tensor | None = None, per: int | None = None):
     """Per channel of each head over all tokens of x: mean, min, max, float32 [batch, heads, 128]; with per (a multiple
     of 256) over each block of that many tokens, [batch, heads, blocks, 128] (unica/__init__.py:592-612).  One pass

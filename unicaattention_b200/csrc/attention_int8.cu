@@ -9,15 +9,21 @@
 //   S[g]   = Q8[g] . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, double-buffered in tensor memory
 //   acc[g] = P^[g](t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, one accumulator per tile
 //
+// The loop runs in steps: step t turns the scores of key tile t into P^ and, in the same straight run of instructions,
+// flushes the accumulator of tile t - 1 into the row's outputs (see tile_step below); one arrival per step tells the
+// issuing thread that P^(t) is delivered, a scores buffer empty and the accumulator read.
+//
 // Numerics (bench/emulate.py:298-369 with the accurate contract): scores in the log2 domain, c = (q_scale * k_scale) *
 // log2(e) / sqrt(d); P^ = rint(255 * 2^(x - tile max)) as u8 against the tile's own maximum; the denominator sums the
 // rounded P^ (per channel) or p / s_j in float before rounding (per token); every tile is flushed as
-// out = out * alpha + beta * float(acc) with alpha = 2^(m_old - m_new), beta = 2^(m_tile - m_new).
+// out = out * alpha + beta * float(acc) with beta = 2^(m_tile - m) and alpha = 2^(m_old - m_new), where m is a reference
+// exponent that follows the running maximum only in large steps (the common factor cancels against the denominator's).
 // The 255 stays in numerator and denominator alike (as csrc/flash.cu:409-414 does).
 //
-// What bounds it (measured on B200 with the micro-benchmarks of peak.cu): ex2 issues once per 8 cycles per
-// scheduler, float->int conversions too, so the loop has no conversion instruction at all (MAGIC in common.cuh) and
-// the exponentials are the busiest unit; a tensor-memory load costs ~180 cycles of latency, so the flush prefetches.
+// What bounds it (measured on B200 with the micro-benchmarks of peak.cu): ex2 issues once per 8 cycles per scheduler,
+// float -> int conversions too, so rounding goes through the float bias MAGIC (common.cuh) instead; int -> float runs on
+// the ALU pipe at 2 cycles; a tensor-memory load costs ~180 cycles of latency and a barrier probe as much, so loads are
+// issued a step ahead and a step has one wait.
 //
 // Tensor memory: 512 columns = per warpgroup S x 2 (64 each) + acc (128).  All waits are bounded (common.cuh).
 #include <type_traits>
@@ -46,7 +52,7 @@ struct __align__(128) AttSmem {
     float tok[STAGES][2 * KEY_TILE];
     uint8_t p[2][2][P_BYTES];
     uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    uint64_t s_full[2][2], s_free[2][2], p_ready[2][2], acc_full[2], acc_free[2], step_done[2], drain[2];
+    uint64_t s_full[2][2], s_free[2][2], acc_full[2], step_done[2], drain[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -108,10 +114,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&sm.s_full[g][b], 1);
                 mbar_init(&sm.s_free[g][b], 128);
-                mbar_init(&sm.p_ready[g][b], 128);
             }
             mbar_init(&sm.acc_full[g], 1);
-            mbar_init(&sm.acc_free[g], 128);
             mbar_init(&sm.step_done[g], 128);
         }
         mbar_init(&sm.drain[0], 1);
@@ -242,11 +246,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         tc_fence_before();
         mbar_arrive(&sm.s_free[g][0]);
         mbar_arrive(&sm.s_free[g][1]);
-        mbar_arrive(&sm.acc_free[g]);
         // Per token the second query tile starts when the first has delivered its first P^, so that the two begin out of
         // step (exponentials against flush); the fused steps of the other modes mix both kinds of work anyway.
 
-        if constexpr (true) {
+        {
             // One step of the loop: the scores of key tile `ts` become P^ in shared memory (SOFT) while the accumulator of
             // tile `tf` is flushed into `out` (FLUSH).  In the steady state both happen, interleaved 16 keys and 32 channels
             // at a time in one straight run of instructions, so that the exponentials (XU), the flush's multiply-adds (FMA
@@ -453,123 +456,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 } else {
                     ok = tile_step(yes{}, yes{}, no{}, yes{}, t + 1, t, alpha_next, beta_next, alpha, beta);
                 }
-                alpha = alpha_next;
-                beta = beta_next;
-            }
-        } else {
-            // Per token the registers do not reach for the fused step (log2 s_j and 1 / s_j of every key come on top):
-            // the softmax of a tile, its 64 scores kept in registers, then the flush of the previous tile.
-            auto softmax_token = [&](int t, float& alpha, float& beta) -> bool {
-                const int buf = t & 1, stage = t % STAGES;
-                const int valid = min(KEY_TILE, n_keys - t * KEY_TILE);
-                const float c = (sq * sk_reg) * scale_log2;
-                if (t + 1 < k_tiles) sk_reg = load_scale(sk + t + 1);
-                TRACE(TR_OTHER);
-                if (!mbar_wait_warp(&sm.s_full[g][buf], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
-                if (!mbar_wait_warp(&sm.v_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
-                tc_fence_after();
-                TRACE(TR_WAIT_S);
-                float2 x[KEY_TILE / 2];  // MAGIC + score, exactly
-                tmem_ld64_sync(t_scores + buf * 64, x);
-                tmem_fill<KEY_TILE>(t_scores + buf * 64, magic);  // completes while the maximum is taken
-                TRACE(TR_LOAD_S);
-
-                const float2 c2 = make_float2(c, c);
-                const float2* log_s = reinterpret_cast<const float2*>(sm.tok[stage]);
-#pragma unroll
-                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(add2(x[j], minus_magic), c2, log_s[j]);
-                if (valid < KEY_TILE) {  // keys past the end take no part
-#pragma unroll
-                    for (int j = 0; j < KEY_TILE; ++j)
-                        if (j >= valid) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
-                }
-                float tile_max;
-                {  // four independent chains, then a tree
-                    float top[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) top[i] = fmaxf(x[i].x, x[i].y);
-#pragma unroll
-                    for (int j = 4; j < KEY_TILE / 2; ++j) top[j % 4] = max3(top[j % 4], x[j].x, x[j].y);
-                    tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-                }
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&sm.s_free[g][buf]);
-                const bool first = m == -INFINITY;  // m: the reference exponent of the row's sums, as in the fused steps
-                const float m_new = tile_max > m + REFERENCE_SLACK ? tile_max : m;
-                alpha = first ? 1.0f : ex2(m - m_new);
-                beta = ex2(tile_max - m_new);
-                m = m_new;
-                const float offset = LOG2_255 - tile_max;
-                const float2 offset2 = make_float2(offset, offset);
-                uint8_t* p_row = sm.p[g][buf] + row * 16;
-                float2 fsum = make_float2(0.0f, 0.0f);
-#pragma unroll
-                for (int chunk = 0; chunk < KEY_TILE / 16; ++chunk) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        uint32_t half[2];
-#pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            const int j = chunk * 8 + i * 2 + h;  // a pair of keys
-                            const float2 e = add2(x[j], offset2);
-                            const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                            fsum = fma2(p, reinterpret_cast<const float2*>(sm.tok[stage] + KEY_TILE)[j], fsum);  // sum of p / s_j
-                            const float2 r = add2(p, plus_magic);  // the low byte of each is rint(p)
-                            half[h] = __byte_perm(__float_as_uint(r.x), __float_as_uint(r.y), 0x0040);
-                        }
-                        w[i] = __byte_perm(half[0], half[1], 0x5410);  // keys past the end: V8 and 1 / s_j are zeros there
-                    }
-                    *reinterpret_cast<uint4*>(p_row + chunk * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-                TRACE(TR_SOFTMAX);
-                fence_proxy_async();
-                mbar_arrive(&sm.p_ready[g][buf]);
-                TRACE(TR_STORE_P);
-                den = den * alpha + (fsum.x + fsum.y) * beta;
-                return true;
-            };
-
-            float alpha = 1.0f, beta = 1.0f;
-            if (ok) ok = softmax_token(0, alpha, beta);
-            for (int t = 0; ok && t < k_tiles; ++t) {
-                float alpha_next = 1.0f, beta_next = 1.0f;
-                if (t + 1 < k_tiles) ok = softmax_token(t + 1, alpha_next, beta_next);
-                if (!ok) break;
-                // flush of tile t: out = out * alpha + beta * float(acc)
-                TRACE(TR_OTHER);
-                ok = mbar_wait_warp(&sm.acc_full[g], t & 1, abort_flag, status, STATUS_WAIT_PV);
-                if (!ok) break;
-                tc_fence_after();
-                TRACE(TR_WAIT_PV);
-                float2 a[4][8];  // a ring of four 16-channel loads: tensor-memory latency (~180 cycles) hides behind the arithmetic
-#pragma unroll
-                for (int i = 0; i < 4; ++i) tmem_ld16_async(t_acc + i * 16, a[i]);
-                if (!__all_sync(0xffffffffu, alpha == 1.0f)) {
-                    const float2 alpha2 = make_float2(alpha, alpha);
-#pragma unroll
-                    for (int i = 0; i < HEAD_DIM / 2; ++i) o[i] = mul2(o[i], alpha2);
-                }
-                const float2 beta2 = make_float2(beta, beta);
-#pragma unroll
-                for (int part = 0; part < HEAD_DIM / 16; ++part) {
-                    if (part % 4 == 0) {  // tcgen05.wait::ld waits for every load issued so far
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) reg_fence8(a[i]);
-                    }
-                    float2 f[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i)  // the accumulator holds plain integers
-                        f[i] = make_float2(__int2float_rn(__float_as_int(a[part % 4][i].x)), __int2float_rn(__float_as_int(a[part % 4][i].y)));
-                    if (part + 4 < HEAD_DIM / 16) tmem_ld16_async(t_acc + (part + 4) * 16, a[part % 4]);
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) o[part * 8 + i] = fma2(beta2, f[i], o[part * 8 + i]);
-                }
-                tc_fence_before();
-                mbar_arrive(&sm.acc_free[g]);
-                TRACE(TR_FLUSH);
                 alpha = alpha_next;
                 beta = beta_next;
             }
