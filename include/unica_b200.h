@@ -199,8 +199,11 @@ int unica_b200_selftest_mma_nvf4(const void* a_image, const void* b_image, const
 /* Peak-rate micro-benchmark (the reference's csrc/peak.cu + bench/peak.py, for the instructions used here): cycles per
  * instruction on one SM, median over `blocks` blocks.  kind 0: tcgen05.mma kind::i8 128 x n x 32; 1: kind::mxf4nvf4
  * 128 x n x 64 (both on shared-memory operands in this library's layout; per MMA); 2..7: ex2.approx, fma.f32x2, fma.f32,
- * prmt, cvt s32->f32, cvt f32->u32 (per warp instruction per scheduler; n unused).  count: instructions in the chain.
- * Allocates scratch and synchronises the stream: a measurement tool. */
+ * prmt, cvt s32->f32, cvt f32->u32 (per warp instruction per scheduler; n = warps per scheduler, 1..4, else 4).
+ * count: instructions in the chain.  Tensor kinds take diagnostic variants in the higher decimal digits of `kind`:
+ * + 100 x L: shared-memory layout type L of the descriptor (0: none, as the library uses; 1, 2, 4, 6: the swizzled
+ * types, timing only); + 1000: M = 64 instead of 128; + 10000 x R: move to the next accumulator every R instructions
+ * (0: one accumulator).  Allocates scratch and synchronises the stream: a measurement tool. */
 int unica_b200_peak(int kind, int n, int count, int blocks, double* cycles_per_instruction, void* stream);
 
 #ifdef __cplusplus
