@@ -1,10 +1,12 @@
 // The accurate mode's flash-attention loop on tcgen05 (replaces the reference's attention_int8pv_tma, csrc/flash.cu:806-959).
 //
-// One block = 256 query rows of one head = two tiles of 128 rows, each owned by one warpgroup of 4 warps in which a
-// thread owns one query row (tensor-memory lane = row, so row maxima and sums need no shuffles) and keeps that row's
-// 128 output channels in registers.  Both warpgroups share every K and V tile.  A third warpgroup holds warp 8, which
-// streams K8 / V8 tiles (contiguous 8 KB images written by the quantizers) into a ring of shared-memory stages with
-// bulk TMA copies, and warps 9 and 10, one elected thread of each issuing one query tile's tcgen05.mma:
+// One block = TILES tiles of 128 query rows of one head, each owned by one warpgroup of 4 warps in which a thread owns
+// one query row (tensor-memory lane = row, so row maxima and sums need no shuffles) and keeps that row's 128 output
+// channels in registers.  TILES = 1 (the default): 256 threads, two blocks per SM, which run out of step and fill each
+// other's waits; TILES = 2: 384 threads, one block per SM whose two tiles share every K and V tile (half the traffic
+// from L2, a few per cent slower).  The last warpgroup of a block holds the producer warp, which streams K8 / V8 tiles
+// (contiguous 8 KB images written by the quantizers) into a ring of shared-memory stages with bulk TMA copies, and one
+// MMA warp per query tile, one elected thread of which issues that tile's tcgen05.mma:
 //
 //   S[g]   = Q8[g] . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, double-buffered in tensor memory
 //   acc[g] = P^[g](t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, one accumulator per tile
@@ -25,34 +27,39 @@
 // the ALU pipe at 2 cycles; a tensor-memory load costs ~180 cycles of latency and a barrier probe as much, so loads are
 // issued a step ahead and a step has one wait.
 //
-// Tensor memory: 512 columns = per warpgroup S x 2 (64 each) + acc (128).  All waits are bounded (common.cuh).
+// Tensor memory: 256 columns per query tile = S x 2 (64 each) + acc (128).  All waits are bounded (common.cuh).
 #include <type_traits>
 
 #include "capi.h"
 
 namespace unica {
 
-constexpr int ATT_THREADS = 384;  // 8 softmax/flush warps + a warpgroup holding the producer warp and the MMA warp
-constexpr int COMPUTE_REGISTERS = 232, SERVICE_REGISTERS = 40;  // registers move from the third warpgroup to the two that hold `out`
-constexpr int PRODUCER_WARP = 8, MMA_WARP = 9;
+#ifndef UNICA_TILES
+#define UNICA_TILES 1
+#endif
+constexpr int TILES = UNICA_TILES;  // query tiles of 128 rows per block: 2 (one block per SM), or 1 (two blocks per SM)
+constexpr int ATT_THREADS = (4 * TILES + 4) * 32;  // a warpgroup per query tile + one holding the producer and MMA warps
+// registers move from the service warpgroup to those that hold `out`: 256 x 232 + 128 x 40 = 384 x 168, 128 x 224 + 128 x 32 = 256 x 128
+constexpr int COMPUTE_REGISTERS = TILES == 2 ? 232 : 224, SERVICE_REGISTERS = TILES == 2 ? 40 : 32;
+constexpr int PRODUCER_WARP = 4 * TILES, MMA_WARP = PRODUCER_WARP + 1;
 constexpr int STAGES = 3;
 constexpr int Q_BYTES = QUERY_TILE * HEAD_DIM;  // 16384
 constexpr int K_BYTES = KEY_TILE * HEAD_DIM;    // 8192
 constexpr int V_BYTES = KEY_TILE * HEAD_DIM;    // 8192
 constexpr int TOK_BYTES = 2 * KEY_TILE * 4;     // 512
 constexpr int P_BYTES = QUERY_TILE * KEY_TILE;  // 8192
-constexpr int TMEM_COLUMNS = 512;
+constexpr int TMEM_COLUMNS = 256 * TILES;
 constexpr float REFERENCE_SLACK = 60.0f;  // log2: how far a tile maximum may rise above a row's reference exponent
 constexpr int COL_S = 0, COL_ACC = 128;  // inside a query tile's 256 columns: S buffers at 0 and 64, acc at 128
 
 struct __align__(128) AttSmem {
-    int8_t q[2][Q_BYTES];
+    int8_t q[TILES][Q_BYTES];
     int8_t k[STAGES][K_BYTES];
     int8_t v[STAGES][V_BYTES];
     float tok[STAGES][2 * KEY_TILE];
-    uint8_t p[2][2][P_BYTES];
+    uint8_t p[TILES][2][P_BYTES];
     uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    uint64_t s_full[2][2], s_free[2][2], acc_full[2], step_done[2], drain[2];
+    uint64_t s_full[TILES][2], s_free[TILES][2], acc_full[TILES], step_done[TILES], drain[TILES];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -87,7 +94,7 @@ constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
 constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM);
 
 template <bool V_TOKEN, bool OUTLIERS>
-__global__ void __launch_bounds__(ATT_THREADS, 1)
+__global__ void __launch_bounds__(ATT_THREADS, 3 - TILES)
     attention_int8_kernel(const int8_t* __restrict__ q8, const float* __restrict__ q_scale, const int8_t* __restrict__ k8,
                           const float* __restrict__ k_scale, const int8_t* __restrict__ v8, const float* __restrict__ v_scale,
                           const float* __restrict__ v_token, const int* __restrict__ outlier_keys,
@@ -97,7 +104,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     AttSmem& sm = *reinterpret_cast<AttSmem*>(smem_raw);
     const int warp = threadIdx.x / 32;
     const int head = blockIdx.y;
-    const int q_tiles = 2 * gridDim.x;  // allocated Q tiles per head (even)
+    const int q_tiles = TILES * gridDim.x;  // allocated Q tiles per head (even)
+    if (TILES == 1 && blockIdx.x * QUERY_TILE >= n_queries) return;  // the padding tile of an odd count: nothing to do
     const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
     volatile int* abort_flag = &sm.abort_flag;
 
@@ -106,11 +114,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         mbar_init(&sm.q_full, 1);
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&sm.k_full[s], 1);
-            mbar_init(&sm.k_empty[s], 2);  // both query tiles' MMA threads commit to it
+            mbar_init(&sm.k_empty[s], TILES);  // every query tile's MMA thread commits to it
             mbar_init(&sm.v_full[s], 1);
-            mbar_init(&sm.v_empty[s], 2);
+            mbar_init(&sm.v_empty[s], TILES);
         }
-        for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < TILES; ++g) {
             for (int b = 0; b < 2; ++b) {
                 mbar_init(&sm.s_full[g][b], 1);
                 mbar_init(&sm.s_free[g][b], 128);
@@ -118,8 +126,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_init(&sm.acc_full[g], 1);
             mbar_init(&sm.step_done[g], 128);
         }
-        mbar_init(&sm.drain[0], 1);
-        mbar_init(&sm.drain[1], 1);
+        for (int g = 0; g < TILES; ++g) mbar_init(&sm.drain[g], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MMA_WARP) tmem_alloc(&sm.tmem_base, TMEM_COLUMNS);
@@ -128,15 +135,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     tc_fence_after();
     const uint32_t tmem = sm.tmem_base;
 
-    if (warp >= 8) {
+    if (warp >= PRODUCER_WARP) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SERVICE_REGISTERS));
       if (warp == PRODUCER_WARP) {
         // ------------------------------------------------------------------------------------------------ producer
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
-            const int8_t* q_src = q8 + (size_t(head) * q_tiles + 2 * blockIdx.x) * Q_BYTES;
-            mbar_expect_tx(&sm.q_full, 2 * Q_BYTES);
-            bulk_load(sm.q[0], q_src, Q_BYTES, &sm.q_full);
-            bulk_load(sm.q[1], q_src + Q_BYTES, Q_BYTES, &sm.q_full);
+            const int8_t* q_src = q8 + (size_t(head) * q_tiles + TILES * blockIdx.x) * Q_BYTES;
+            mbar_expect_tx(&sm.q_full, TILES * Q_BYTES);
+            for (int g = 0; g < TILES; ++g) bulk_load(sm.q[g], q_src + g * Q_BYTES, Q_BYTES, &sm.q_full);
             int issued = 0;
             for (int t = 0; t < k_tiles; ++t) {
                 const int s = t % STAGES, use = t / STAGES;
@@ -159,13 +165,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
-      } else if (warp == MMA_WARP || warp == MMA_WARP + 1) {
+      } else if (warp >= MMA_WARP && warp < MMA_WARP + TILES) {
         // ------------------------------------------------------------------------------------------------ MMA issue
-        // One elected thread per query tile (warp 9: tile 0, warp 10: tile 1) issues that tile's tcgen05.mma in the order
+        // One elected thread per query tile issues that tile's tcgen05.mma in the order
         // its operands become ready: P.V of key tile t once P^(t) is written, V(t) has landed and the flush of tile t - 1
         // has read the accumulator; then the scores of tile t + 2 into the buffer the softmax of tile t has emptied.
         // Each wait blocks in hardware (mbarrier.try_wait) and wakes as the phase completes; a stage of K or V is
-        // released by the second of the two threads' commits.
+        // released by the last of the tiles' commits.
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
             const int g = warp - MMA_WARP;
             const uint32_t q_addr = smem_u32(sm.q[g]), base = tmem + g * 256;
@@ -217,7 +223,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         // ------------------------------------------------------------------------------------- softmax and flush
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(COMPUTE_REGISTERS));
         const int g = warp / 4, row = threadIdx.x % 128;
-        const int q_tile = 2 * blockIdx.x + g, q_row = q_tile * QUERY_TILE + row;
+        const int q_tile = TILES * blockIdx.x + g, q_row = q_tile * QUERY_TILE + row;
         const uint32_t lane_base = uint32_t((warp % 4) * 32) << 16;
         const uint32_t t_scores = tmem + lane_base + g * 256 + COL_S, t_acc = tmem + lane_base + g * 256 + COL_ACC;
         const float sq = q_scale[size_t(head) * q_tiles + q_tile];
@@ -595,11 +601,12 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: the outliers mode needs outlier_keys, outlier_rows and 1..8 outliers");
     if (v_mode == UNICA_B200_V_TOKEN && !v_token) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: per-token mode needs v_token");
     if (int e = unica_check_device()) return e;
-    const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE), heads);
+    const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE) * (2 / TILES), heads);  // Q8 holds an even number of tiles
     const size_t smem = sizeof(AttSmem) + 128;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     auto launch = [&](auto kernel) -> int {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess ||
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
             return unica_check_launch("attention_int8 (shared memory size)");
         kernel<<<grid, ATT_THREADS, smem, s>>>(q8, q_scale, k8, k_scale, v8, v_scale, v_token, outlier_keys, outlier_rows, n_outliers,
                                                static_cast<__nv_bfloat16*>(out), to_layout(out_layout), n_queries, n_keys, scale_log2,
