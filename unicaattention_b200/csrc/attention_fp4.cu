@@ -5,9 +5,10 @@
 //   S[g]  = Q4[g] . K4(t)^T     128 x 64,  2 instructions of K = 64 channels
 //   O[g] += P4[g](t) . V4(t)    128 x 144, 1 instruction of K = 64 keys; columns 0..127 are the output channels, column
 //                               128 multiplies P by a row of ones: the running softmax denominator, rescaled with O
-// One block = 256 query rows of one head = two tiles of 128 rows (warpgroups g = 0, 1; thread = query row = tensor-
-// memory lane) sharing every K and V tile; a third warpgroup holds the producer warp (bulk TMA copies) and two MMA warps, one
-// elected thread of each issuing one query tile's instructions.
+// One block = F4_TILES (2) tiles of 128 query rows of one head sharing every K and V tile, two threads per query row
+// (both on the row's tensor-memory lane, 32 key slots and 64 output channels each); the last warpgroup holds the
+// producer warp (bulk TMA copies) and one MMA warp per query tile, one elected thread of which issues that tile's
+// instructions and copies K's, V's and P's scale bytes into tensor memory.
 //
 // Numerics (bench/emulate.py:298-369 with the fast contract): scores x = S * (q_outer k_outer log2(e)/sqrt(d)) + bias,
 // bias the exact q_mean . (k - k_mean) term of Q smoothing; running maximum m; P = 1024 * 2^(x - m) in NVFP4 along the
@@ -29,7 +30,12 @@
 
 namespace unica {
 
-constexpr int F4_COMPUTE_WARPS = 16;  // 2 query tiles x 2 threads per row x 4 warps
+#ifndef UNICA_F4_TILES
+#define UNICA_F4_TILES 2
+#endif
+constexpr int F4_TILES = UNICA_F4_TILES;  // query tiles of 128 rows per block: 2 (one block per SM; 22.5 ms at 40 x 32760) or 1 (two
+                                          // blocks per SM at 80 registers: 26.5 ms)
+constexpr int F4_COMPUTE_WARPS = 8 * F4_TILES;  // query tiles x 2 threads per row x 4 warps
 constexpr int F4_THREADS = (F4_COMPUTE_WARPS + 4) * 32;
 constexpr int F4_PRODUCER_WARP = F4_COMPUTE_WARPS, F4_MMA_WARP = F4_COMPUTE_WARPS + 1;
 constexpr int F4_HALF_SLOTS = KEY_TILE / 2;  // what one of a row's two threads takes
@@ -42,7 +48,7 @@ constexpr int V4_TILE_ROWS = 144, V4_BYTES = 2 * V4_TILE_ROWS * 16;  // 4608
 constexpr int SFV_BYTES = 256 * 4;                   // 1024: two blocks of 32 lanes x 4 words
 constexpr int BIAS_BYTES = KEY_TILE * 4;             // 256
 constexpr int P4_BYTES = QUERY_TILE * KEY_TILE / 2;  // 4096
-constexpr int F4_TMEM_COLUMNS = 512;
+constexpr int F4_TMEM_COLUMNS = 256 * F4_TILES;
 constexpr int F4_S = 0, F4_O = 64, F4_SFQ = 208, F4_SFK = 216, F4_SFP = 220, F4_SFV = 224;
 constexpr float P_LOG2_GAIN = 10.0f;  // P is taken times 2^10: its block scales (up to 1024 / 6) stay below e4m3's 448
 
@@ -72,19 +78,19 @@ __device__ long long g_trace_fp4[4][8];
 enum { F4_TR_WAIT_S = 0, F4_TR_LOAD_S = 1, F4_TR_MAX = 2, F4_TR_QUANTIZE = 3, F4_TR_WAIT_O = 4, F4_TR_RESCALE = 5, F4_TR_EXCHANGE = 6, F4_TR_OTHER = 7 };
 
 struct __align__(128) Fp4Smem {
-    uint8_t q[2][Q4_BYTES];
-    uint32_t sfq[2][2][QUERY_TILE];
+    uint8_t q[F4_TILES][Q4_BYTES];
+    uint32_t sfq[F4_TILES][2][QUERY_TILE];
     uint8_t k[F4_STAGES][K4_BYTES];
     uint32_t sfk[F4_STAGES][32][4];  // as tcgen05.cp takes them: lane, word 2 step + row / 32
     uint8_t v[F4_STAGES][V4_BYTES];
     uint32_t sfv[F4_STAGES][2][32][4];  // block 0: channel c = word c / 32 of lane c % 32; block 1: the ones rows
     float bias[F4_STAGES][KEY_TILE];
-    uint8_t p[2][P4_BYTES];
-    uint32_t sfp[2][32][4];  // P's scale words of a query tile: row r = word r / 32 of lane r % 32
-    uint2 exchange[2][2][2][QUERY_TILE];  // [query tile][tag parity][thread of the row][row] = {tag, value}
+    uint8_t p[F4_TILES][P4_BYTES];
+    uint32_t sfp[F4_TILES][32][4];  // P's scale words of a query tile: row r = word r / 32 of lane r % 32
+    uint2 exchange[F4_TILES][2][2][QUERY_TILE];  // [query tile][tag parity][thread of the row][row] = {tag, value}
     float inv_e4m3[128];                  // 1 / value of every non-negative e4m3 byte, correctly rounded; 0 for the byte 0
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
-    uint64_t s_full[2], s_free[2], p_ready[2], o_full[2], drain[2];
+    uint64_t s_full[F4_TILES], s_free[F4_TILES], p_ready[F4_TILES], o_full[F4_TILES], drain[F4_TILES];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -113,7 +119,7 @@ __device__ __forceinline__ uint32_t e2m1x8(const float2 (&v)[4]) {
     return word;
 }
 
-__global__ void __launch_bounds__(F4_THREADS, 1)
+__global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
     attention_fp4_kernel(const uint8_t* __restrict__ q4, const uint32_t* __restrict__ sfq, const uint8_t* __restrict__ k4,
                          const uint32_t* __restrict__ sfk, const uint8_t* __restrict__ v4, const uint32_t* __restrict__ sfv,
                          const float* __restrict__ qk_outer, const float* __restrict__ v_outer, const float* __restrict__ bias,
@@ -123,7 +129,8 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
     Fp4Smem& sm = *reinterpret_cast<Fp4Smem*>(smem_raw);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int head = blockIdx.y;
-    const int q_tiles = 2 * gridDim.x;
+    const int q_tiles = F4_TILES * gridDim.x;  // allocated Q tiles per head (even)
+    if (F4_TILES == 1 && blockIdx.x * QUERY_TILE >= n_queries) return;  // the padding tile of an odd count: nothing to do
     const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
     volatile int* abort_flag = &sm.abort_flag;
 
@@ -132,21 +139,20 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         mbar_init(&sm.q_full, 1);
         for (int s = 0; s < F4_STAGES; ++s) {
             mbar_init(&sm.k_full[s], 1);
-            mbar_init(&sm.k_empty[s], 2);  // both query tiles' MMA threads commit to it
+            mbar_init(&sm.k_empty[s], F4_TILES);  // every query tile's MMA thread commits to it
             mbar_init(&sm.v_full[s], 1);
-            mbar_init(&sm.v_empty[s], 2);
+            mbar_init(&sm.v_empty[s], F4_TILES);
         }
-        for (int g = 0; g < 2; ++g) {
+        for (int g = 0; g < F4_TILES; ++g) {
             mbar_init(&sm.s_full[g], 1);
             mbar_init(&sm.s_free[g], 2 * QUERY_TILE);  // both threads of every row
             mbar_init(&sm.p_ready[g], 2 * QUERY_TILE);
             mbar_init(&sm.o_full[g], 1);
         }
-        mbar_init(&sm.drain[0], 1);
-        mbar_init(&sm.drain[1], 1);
+        for (int g = 0; g < F4_TILES; ++g) mbar_init(&sm.drain[g], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < 2 * 2 * 2 * QUERY_TILE; i += F4_THREADS) (&sm.exchange[0][0][0][0])[i] = make_uint2(0xffffffffu, 0u);  // no tag
+    for (int i = threadIdx.x; i < F4_TILES * 2 * 2 * QUERY_TILE; i += F4_THREADS) (&sm.exchange[0][0][0][0])[i] = make_uint2(0xffffffffu, 0u);  // no tag
     if (threadIdx.x < 128) {
         const float value = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(threadIdx.x), __NV_E4M3)));
         sm.inv_e4m3[threadIdx.x] = value > 0.0f ? __fdiv_rn(1.0f, value) : 0.0f;  // byte 127 is NaN: never produced (satfinite)
@@ -160,11 +166,11 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
     if (warp == F4_PRODUCER_WARP) {
         // ------------------------------------------------------------------------------------------------ producer
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
-            const size_t q_first = size_t(head) * q_tiles + 2 * blockIdx.x;
-            mbar_expect_tx(&sm.q_full, 2 * (Q4_BYTES + SFQ_BYTES));
-            bulk_load(sm.q[0], q4 + q_first * Q4_BYTES, 2 * Q4_BYTES, &sm.q_full);
-            bulk_load(sm.sfq[0], sfq + q_first * (SFQ_BYTES / 4), 2 * SFQ_BYTES, &sm.q_full);
-            const float* bias_row = bias ? bias + (size_t(head) * q_blocks + (2 * blockIdx.x * QUERY_TILE) / smooth_q) * (size_t(k_tiles) * KEY_TILE) : nullptr;
+            const size_t q_first = size_t(head) * q_tiles + F4_TILES * blockIdx.x;
+            mbar_expect_tx(&sm.q_full, F4_TILES * (Q4_BYTES + SFQ_BYTES));
+            bulk_load(sm.q[0], q4 + q_first * Q4_BYTES, F4_TILES * Q4_BYTES, &sm.q_full);
+            bulk_load(sm.sfq[0], sfq + q_first * (SFQ_BYTES / 4), F4_TILES * SFQ_BYTES, &sm.q_full);
+            const float* bias_row = bias ? bias + (size_t(head) * q_blocks + (F4_TILES * blockIdx.x * QUERY_TILE) / smooth_q) * (size_t(k_tiles) * KEY_TILE) : nullptr;
             int issued = 0;
             for (int t = 0; t < k_tiles; ++t) {
                 const int s = t % F4_STAGES, use = t / F4_STAGES;
@@ -190,7 +196,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                 mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
-    } else if (warp == F4_MMA_WARP || warp == F4_MMA_WARP + 1) {
+    } else if (warp >= F4_MMA_WARP && warp < F4_MMA_WARP + F4_TILES) {
         // ------------------------------------------------------------------------------------------------ MMA issue
         // One elected thread per query tile (warp 9: tile 0, warp 10: tile 1), blocking on each operand in the order they
         // become ready: the scores of key tile t + 1 once the softmax threads have taken those of tile t and put K(t + 1)'s
@@ -242,7 +248,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
         // `half` takes slots 32 half .. 32 half + 31 of every tile (two scale blocks of P) and output channels 64 half ..
         // 64 half + 63; the two meet in one number per tile, the maximum of their scores (a tagged word in shared memory).
         const int g = warp / 8, half = (warp / 4) % 2, row = (warp % 4) * 32 + lane;
-        const int q_row = (2 * blockIdx.x + g) * QUERY_TILE + row;
+        const int q_row = (F4_TILES * blockIdx.x + g) * QUERY_TILE + row;
         const uint32_t my = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256;
         const float c = qk_outer[head] * scale_log2;
         const float2 c2 = make_float2(c, c);
@@ -467,9 +473,10 @@ extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, cons
     if (bias && (smooth_q <= 0 || smooth_q % 256 || q_blocks != (n_queries + smooth_q - 1) / smooth_q))
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: with a smoothing term, smooth_q must be a multiple of 256 and q_blocks = ceil(n_queries / smooth_q)");
     if (int e = unica_check_device()) return e;
-    const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE), heads);
+    const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE) * (2 / F4_TILES), heads);  // Q4 holds an even number of tiles
     const size_t smem = sizeof(Fp4Smem) + 128;
-    if (cudaFuncSetAttribute(attention_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_fp4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess ||
+        cudaFuncSetAttribute(attention_fp4_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
         return unica_check_launch("attention_fp4 (shared memory size)");
     attention_fp4_kernel<<<grid, F4_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
         q4, static_cast<const uint32_t*>(sfq), k4, static_cast<const uint32_t*>(sfk), v4, static_cast<const uint32_t*>(sfv), qk_outer,
