@@ -20,6 +20,7 @@ from __future__ import annotations
 import functools
 import math
 import os
+import time
 import warnings
 import weakref
 
@@ -429,10 +430,19 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
 # the head-split planner (unica/__init__.py:193-245): on a 180 GB part it rarely splits, but the contract stays
 
 
+_FREE_VRAM: dict = {}  # device -> (bytes free, when asked)
+FREE_VRAM_MAX_AGE = 0.25  # seconds: the driver's answer costs 0.1 to 1 ms of host time, too much to pay on every call
+
+
 def free_vram(device: torch.device) -> int:
-    """Bytes the driver has free on the device; does not wait for the GPU."""
-    free, _ = torch.cuda.mem_get_info(device)
-    return free
+    """Bytes the driver has free on the device (plus what torch's allocator holds unused); does not wait for the GPU.
+    The driver is asked at most every FREE_VRAM_MAX_AGE seconds per device."""
+    now = time.monotonic()
+    cached = _FREE_VRAM.get(device)
+    if cached is None or now - cached[1] > FREE_VRAM_MAX_AGE:
+        free, _ = torch.cuda.mem_get_info(device)
+        cached = _FREE_VRAM[device] = (free, now)
+    return cached[0]
 
 
 def vram_reserve(device: torch.device) -> int:
@@ -443,12 +453,16 @@ def vram_reserve(device: torch.device) -> int:
 
 def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) -> int:
     """How many heads one call takes without its temporary buffers reaching the reserve.  Per head: the quantized q, k,
-    v and the output, at most 2 bytes per element of q, k, v; 2 more for bf16 copies of float16 inputs.  (The fast
-    mode's smoothing term is computed inside the kernel here, so it adds no table.)  A small call runs whole."""
+    v and the output, at most 2 bytes per element of q, k, v; 2 more for bf16 copies of float16 inputs; in the fast
+    mode the smoothing table, one float per key and block of SMOOTH_Q queries (unica/__init__.py:208-232 counts the same
+    things).  A small call runs whole."""
     batch, heads, n_queries, _ = q.shape
     n_keys = k.shape[2]
     elements = batch * HEAD_DIM * (n_queries + 2 * n_keys)
     per_head = max(1, elements * (2 + (2 if q.dtype != torch.bfloat16 else 0)))
+    smooth = (TILE | tile).get("SMOOTH_Q", 0) if kernel == "attention_fp4" else 0
+    if smooth:
+        per_head += batch * 4 * math.ceil(n_queries / smooth) * n_keys
     free, reserve = free_vram(q.device), vram_reserve(q.device)
     if heads * per_head <= min(reserve // SMALL_CALL_FRACTION, free):
         step = heads
