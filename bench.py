@@ -315,8 +315,8 @@ def main():
         written = {"per_channel": 3 * 128, "per_token": 3 * 128 + 8, "outliers": 3 * 128, "fast": 72 + 72 + 82}[args.mode]
         reads = {"per_channel": 5 * 256, "per_token": 4 * 256, "outliers": 6 * 256, "fast": 7 * 256}[args.mode]  # statistics passes read again
         # DRAM traffic of the attention kernel per launch: ncu on 40 heads x 8192 tokens (profiles/), scaled by heads x tokens
-        # (per channel: 125.98 MB read + 51.62 MB written; fast: 97.06 + 44.97 MB, the rest of the output still in L2)
-        traffic_per_token = {"per_channel": 542.0, "fast": 433.4}.get(args.mode)
+        # (per channel: 125.99 MB read + 51.16 MB written; fast: 97.06 + 44.97 MB, the rest of the output still in L2)
+        traffic_per_token = {"per_channel": 540.6, "fast": 433.4}.get(args.mode)
         traffic = traffic_per_token * batch * heads * tokens / world if traffic_per_token else None
         # what the tensor pipe alone sustains on one tile's tcgen05.mma mix, measured now by the micro-benchmark
         from unicaattention_b200 import peak as peak_bench
