@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 3 - TILES)
         const float* sk = k_scale + size_t(head) * k_tiles;
         const float2 minus_magic = make_float2(-MAGIC, -MAGIC), plus_magic = make_float2(MAGIC, MAGIC);
         float m = -INFINITY, den = 0.0f;
-        // The K scale of the tile the next softmax() takes, loaded a whole tile ahead of its use (volatile: the compiler
+        // The K scale of the tile the next step takes, loaded a whole tile ahead of its use (volatile: the compiler
         // would otherwise sink the load to the use and expose its latency on every tile).
         auto load_scale = [](const float* p) {
             float v;
@@ -244,7 +244,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 3 - TILES)
         bool ok = true;
         TRACE_DECL;
 
-        // Every accumulator starts at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
+        // The score buffers start at MAGIC_BITS, so what comes back from tensor memory is already a float (common.cuh).
         uint32_t magic[FILL_BLOCK];
         fill_block_init(magic, MAGIC_BITS);
         tmem_fill<128>(t_scores, magic);  // both score buffers
@@ -252,8 +252,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 3 - TILES)
         tc_fence_before();
         mbar_arrive(&sm.s_free[g][0]);
         mbar_arrive(&sm.s_free[g][1]);
-        // Per token the second query tile starts when the first has delivered its first P^, so that the two begin out of
-        // step (exponentials against flush); the fused steps of the other modes mix both kinds of work anyway.
 
         {
             // One step of the loop: the scores of key tile `ts` become P^ in shared memory (SOFT) while the accumulator of
