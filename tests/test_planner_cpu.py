@@ -1,0 +1,50 @@
+"""The head planner's arithmetic (the reference's heads_per_call, unica/__init__.py:208-232) with the driver's answers
+replaced: no GPU needed."""
+
+import torch
+
+import unicaattention_b200 as unica
+
+GiB = 2**30
+
+
+def plan(monkeypatch, free, reserve, shape=(1, 40, 32760, 128), dtype=torch.bfloat16, kernel=unica.DEFAULT_KERNEL, **tile):
+    monkeypatch.setattr(unica, "free_vram", lambda device: free)
+    monkeypatch.setattr(unica, "vram_reserve", lambda device: reserve)
+    q = torch.empty(shape, dtype=dtype, device="meta")
+    return unica.heads_per_call(q, q, kernel, tile)
+
+
+def test_small_calls_run_whole(monkeypatch):
+    # 40 heads x 32760 tokens: 25 MB of temporaries per head, 1 GB in all: within a quarter of an 18 GiB reserve
+    assert plan(monkeypatch, free=150 * GiB, reserve=18 * GiB) == 40
+    assert plan(monkeypatch, free=2 * GiB, reserve=18 * GiB) == 40  # and it fits the free memory
+
+
+def test_large_calls_are_split_to_stay_above_the_reserve(monkeypatch):
+    per_head = 128 * 3 * 118320 * 2  # hires shape, bf16
+    free, reserve = 6 * GiB, 4 * GiB
+    assert 40 * per_head > reserve // unica.SMALL_CALL_FRACTION
+    assert plan(monkeypatch, free, reserve, shape=(1, 40, 118320, 128)) == (free - reserve) // per_head
+    assert plan(monkeypatch, free=reserve, reserve=reserve, shape=(1, 40, 118320, 128)) == 1  # never less than a head
+
+
+def test_float16_and_the_smoothing_table_cost_more(monkeypatch):
+    free, reserve = 6 * GiB, 4 * GiB
+    shape = (1, 40, 118320, 128)
+    bf16 = plan(monkeypatch, free, reserve, shape)
+    assert plan(monkeypatch, free, reserve, shape, dtype=torch.float16) == bf16 // 2  # a bf16 copy of every input
+    table = 4 * -(-118320 // 512) * 118320  # one float per key and block of 512 queries
+    fast = plan(monkeypatch, free, reserve, shape, kernel="attention_fp4", SMOOTH_Q=512)
+    assert fast == (free - reserve) // (128 * 3 * 118320 * 2 + table) < bf16
+    assert plan(monkeypatch, free, reserve, shape, kernel="attention_fp4", SMOOTH_Q=0) == bf16
+
+
+def test_free_vram_is_asked_seldom(monkeypatch):
+    calls = []
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device: (calls.append(device), (5 * GiB, 8 * GiB))[1])
+    unica._FREE_VRAM.clear()
+    assert unica.free_vram("gpu") == 5 * GiB and unica.free_vram("gpu") == 5 * GiB and len(calls) == 1
+    monkeypatch.setattr(unica, "FREE_VRAM_MAX_AGE", -1.0)
+    assert unica.free_vram("gpu") == 5 * GiB and len(calls) == 2
+    unica._FREE_VRAM.clear()
