@@ -606,6 +606,12 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)) != cudaSuccess ||
             cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) != cudaSuccess)
             return unica_check_launch("attention_int8 (shared memory size)");
+        // setmaxnreg only moves registers the block already holds: the split must not ask for more than the launch gives,
+        // or the computing warps would wait for registers for ever
+        cudaFuncAttributes attributes;
+        if (cudaFuncGetAttributes(&attributes, kernel) != cudaSuccess) return unica_check_launch("attention_int8 (attributes)");
+        if (attributes.numRegs * ATT_THREADS < 128 * TILES * COMPUTE_REGISTERS + 128 * SERVICE_REGISTERS)
+            return unica_fail(UNICA_B200_ERR_KERNEL, "attention_int8: this build holds fewer registers per block than its setmaxnreg split needs");
         kernel<<<grid, ATT_THREADS, smem, s>>>(q8, q_scale, k8, k_scale, v8, v_scale, v_token, outlier_keys, outlier_rows, n_outliers,
                                                static_cast<__nv_bfloat16*>(out), to_layout(out_layout), n_queries, n_keys, scale_log2,
                                                status);
