@@ -119,6 +119,7 @@ def cpu_baseline(mode: str, tokens: int, sample_rows: int = 2048) -> dict:
     import oracle
 
     rows = min(sample_rows, tokens)
+    oracle.threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count() or 1)  # all the host's cores
     q, k, v = (head_tensor(kind, 0, tokens)[None] for kind in range(3))
     start = time.perf_counter()
     if mode == "fast":

@@ -52,9 +52,10 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
-def threads() -> int:
-    """Host threads the OpenMP loops use."""
-    return int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+def threads(n: int = 0) -> int:
+    """Host threads the OpenMP loops use; n > 0 sets them first (a launcher such as torchrun starts its workers with
+    OMP_NUM_THREADS=1)."""
+    return int(lib().uo_set_threads(int(n)))
 
 
 def bf16_bits(x) -> np.ndarray:

@@ -27,6 +27,20 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Host threads of the OpenMP loops: a launcher may have set OMP_NUM_THREADS=1 for its worker processes. */
+int uo_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
 
 #define D 128
 #define STATS_TOKENS 256 /* csrc/flash.cu:285 */
