@@ -185,14 +185,17 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_
 // smooth_bias kernel, csrc/flash.cu:1254-1322, gets there with three bf16 MMAs): for every block of `mean_tokens`
 // queries and every key, q_mean[block] . (k - k_mean) in FP32, times scale_log2, keys of a tile in slot order, 0 past
 // the last key.  bias: [heads][q_blocks][k_tiles * 64].  Grid (k_tiles, heads).
+constexpr int BIAS_ROW = HEAD_DIM + 4;  // row stride in floats: 16-byte aligned rows, no bank conflicts for 16-byte loads
+constexpr int BIAS_BATCH = 64;          // query blocks per pass
+constexpr int BIAS_SMEM = (KEY_TILE * BIAS_ROW + BIAS_BATCH * HEAD_DIM) * 4;  // 66560 bytes
+
 __global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfloat16* __restrict__ k, TokenLayout in,
                                                                    const float* __restrict__ k_mean, const float* __restrict__ q_mean,
                                                                    int q_blocks, int n_keys, float scale_log2, float* __restrict__ bias,
                                                                    RopeTable rope) {
-    constexpr int ROW = HEAD_DIM + 4;    // row stride in floats: 16-byte aligned rows, no bank conflicts for 16-byte loads
-    constexpr int BATCH = 16, MINE = 4;  // query blocks per pass; per thread (4 thread groups of 64 slots)
-    __shared__ __align__(16) float centred[KEY_TILE][ROW];
-    __shared__ __align__(16) float qm[BATCH][HEAD_DIM];
+    extern __shared__ __align__(16) float bias_smem[];
+    float (*centred)[BIAS_ROW] = reinterpret_cast<float (*)[BIAS_ROW]>(bias_smem);                            // [KEY_TILE][BIAS_ROW]
+    float (*qm)[HEAD_DIM] = reinterpret_cast<float (*)[HEAD_DIM]>(bias_smem + KEY_TILE * BIAS_ROW);          // [BIAS_BATCH][HEAD_DIM]
     const int head = blockIdx.y, t = blockIdx.x, k_tiles = gridDim.x;
     for (int item = threadIdx.x; item < KEY_TILE * HEAD_DIM / 2; item += FP4_THREADS) {  // a pair of channels each
         const int slot = item / (HEAD_DIM / 2), c = item % (HEAD_DIM / 2) * 2, key = t * KEY_TILE + slot_key(slot);
@@ -207,30 +210,37 @@ __global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfl
         }
         centred[slot][c] = x.x, centred[slot][c + 1] = x.y;
     }
-    // Thread = (key slot, group of query blocks): the key's centred row is read once per 4 query blocks, the block means
-    // are broadcast reads, so a multiply-add costs about a third of a shared-memory load instead of two.
-    const int slot = threadIdx.x % KEY_TILE, group = threadIdx.x / KEY_TILE;
-    for (int b0 = 0; b0 < q_blocks; b0 += BATCH) {
+    // Thread = (two key slots, eight query blocks): per four channels it reads two 16-byte pieces of the keys' centred rows
+    // and eight of the block means (broadcast) for 64 multiply-adds, i.e. a sixth of a shared-memory load per multiply-add.
+    constexpr int KEYS = 2, MINE = BIAS_BATCH / (FP4_THREADS / (KEY_TILE / KEYS));  // 8 blocks per thread
+    const int slot = threadIdx.x % (KEY_TILE / KEYS), group = threadIdx.x / (KEY_TILE / KEYS);  // slots `slot` and `slot + 32`
+    for (int b0 = 0; b0 < q_blocks; b0 += BIAS_BATCH) {
         __syncthreads();
-        for (int item = threadIdx.x; item < BATCH * HEAD_DIM; item += FP4_THREADS) {
+        for (int item = threadIdx.x; item < BIAS_BATCH * HEAD_DIM; item += FP4_THREADS) {
             const int b = b0 + item / HEAD_DIM;
             qm[item / HEAD_DIM][item % HEAD_DIM] = b < q_blocks ? q_mean[(size_t(head) * q_blocks + b) * HEAD_DIM + item % HEAD_DIM] : 0.0f;
         }
         __syncthreads();
-        float dot[MINE] = {};
-#pragma unroll 4
+        float dot[KEYS][MINE] = {};
+#pragma unroll 2
         for (int c = 0; c < HEAD_DIM; c += 4) {
-            const float4 kc = *reinterpret_cast<const float4*>(&centred[slot][c]);
+            const float4 k0 = *reinterpret_cast<const float4*>(&centred[slot][c]);
+            const float4 k1 = *reinterpret_cast<const float4*>(&centred[slot + KEY_TILE / KEYS][c]);
 #pragma unroll
             for (int j = 0; j < MINE; ++j) {
                 const float4 qc = *reinterpret_cast<const float4*>(&qm[group * MINE + j][c]);
-                dot[j] = fmaf(qc.w, kc.w, fmaf(qc.z, kc.z, fmaf(qc.y, kc.y, fmaf(qc.x, kc.x, dot[j]))));  // channels in order
+                dot[0][j] = fmaf(qc.w, k0.w, fmaf(qc.z, k0.z, fmaf(qc.y, k0.y, fmaf(qc.x, k0.x, dot[0][j]))));  // channels in order
+                dot[1][j] = fmaf(qc.w, k1.w, fmaf(qc.z, k1.z, fmaf(qc.y, k1.y, fmaf(qc.x, k1.x, dot[1][j]))));
             }
         }
 #pragma unroll
         for (int j = 0; j < MINE; ++j) {
             const int b = b0 + group * MINE + j;
-            if (b < q_blocks) bias[(size_t(head) * q_blocks + b) * (size_t(k_tiles) * KEY_TILE) + t * KEY_TILE + slot] = dot[j] * scale_log2;
+            if (b < q_blocks) {
+                float* row = bias + (size_t(head) * q_blocks + b) * (size_t(k_tiles) * KEY_TILE) + t * KEY_TILE;
+                row[slot] = dot[0][j] * scale_log2;
+                row[slot + KEY_TILE / KEYS] = dot[1][j] * scale_log2;
+            }
         }
     }
 }
@@ -296,7 +306,9 @@ static int smooth_bias(const void* k, unica_token_layout layout, const float* k_
     if (!k || !k_mean || !q_mean || !bias) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: null pointer");
     if (heads <= 0 || q_blocks <= 0 || n_keys <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: heads, q_blocks and n_keys must be positive");
     const int tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
-    smooth_bias_kernel<<<dim3(tiles, heads), FP4_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+    if (cudaFuncSetAttribute(smooth_bias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BIAS_SMEM) != cudaSuccess)
+        return unica_check_launch("smooth_bias (shared memory size)");
+    smooth_bias_kernel<<<dim3(tiles, heads), FP4_THREADS, BIAS_SMEM, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias, rope);
     return unica_check_launch("smooth_bias");
 }
