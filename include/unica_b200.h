@@ -170,8 +170,8 @@ int unica_b200_smooth_bias_rope(const void* k, unica_token_layout layout, const 
 /* Hardware self-test of the tensor-core path (the idea of the reference's tests/test_mma.py: small integers make every
  * result exact, so a wrong lane or layout cannot hide).  One tcgen05.mma kind::i8 chain D[128 x n] = A[128 x k] . B[n x k]^T
  * with A (u8 if a_unsigned, else s8) and B (s8) given as the shared-memory images described above
- * ([k / 16][rows][16] bytes); d gets int32 [128][n] row-major.  variant 0 describes the operands as the attention
- * kernels do; 1 exchanges the descriptor's two byte offsets (a diagnostic, expected to give wrong results).
+ * ([k / 16][rows][16] bytes); d gets int32 [128][n] row-major.  The operands are described as the attention
+ * kernels describe theirs; variant must be 0.
  * Allocates a status word and synchronises the stream: not for the hot path. */
 int unica_b200_selftest_mma_i8(const void* a_image, const void* b_image, int n, int k, int a_unsigned, int variant,
                                int32_t* d, void* stream);
@@ -191,7 +191,8 @@ int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* 
  * kind::mxf4nvf4.block_scale.scale_vec::4X per 64 elements of k (k = 64 or 128).  a_image [k / 32][128][16],
  * b_image [k / 32][n][16] bytes (two e2m1 codes per byte, low nibble first); sfa uint32 [k / 64][128], sfb uint32
  * [k / 64][n]: byte i of a word is the e4m3 scale of elements 16 i .. 16 i + 15 of that 64-element step.  d: float
- * [128][n].  variant 0 places the scale bytes in tensor memory as the attention kernel does; 1 is a diagnostic.
+ * [128][n].  variant 0: the computing threads store the scale words into tensor memory (as the attention kernel does for Q's);
+ * 2: A's are copied from shared memory by the issuing thread (tcgen05.cp, as it does for K's, V's and P's).
  * Allocates a status word and synchronises the stream: not for the hot path. */
 int unica_b200_selftest_mma_nvf4(const void* a_image, const void* b_image, const void* sfa, const void* sfb, int n, int k,
                                  int variant, float* d, void* stream);
@@ -202,7 +203,7 @@ int unica_b200_selftest_mma_nvf4(const void* a_image, const void* b_image, const
  * prmt, cvt s32->f32, cvt f32->u32 (per warp instruction per scheduler; n = warps per scheduler, 1..4, else 4).
  * count: instructions in the chain.  Tensor kinds take diagnostic variants in the higher decimal digits of `kind`:
  * + 100 x L: shared-memory layout type L of the descriptor (0: none, as the library uses; 1, 2, 4, 6: the swizzled
- * types, timing only); + 1000: M = 64 instead of 128; + 10000 x R: move to the next accumulator every R instructions
+ * types, timing only; anything else is refused); + 1000: M = 64 instead of 128; + 10000 x R: move to the next accumulator every R instructions
  * (0: one accumulator).  Allocates scratch and synchronises the stream: a measurement tool. */
 int unica_b200_peak(int kind, int n, int count, int blocks, double* cycles_per_instruction, void* stream);
 

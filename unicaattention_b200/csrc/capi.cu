@@ -1,6 +1,7 @@
 // Error reporting and device checks behind the C entry points.
 #include "capi.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 
@@ -18,11 +19,22 @@ int unica_check_launch(const char* what) {
     return UNICA_B200_ERR_CUDA;
 }
 
+// The answer per device is looked up once (two runtime queries) and remembered: 0 unknown, 1 fine, 2 not a B200.
 int unica_check_device() {
-    int device = 0, major = 0;
-    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess)
-        return unica_fail(UNICA_B200_ERR_CUDA, "cannot query the current CUDA device");
-    if (major != 10) return unica_fail(UNICA_B200_ERR_DEVICE, "these kernels are built for sm_100a (B200) only");
+    constexpr int MAX_DEVICES = 64;
+    static std::atomic<signed char> known[MAX_DEVICES];
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return unica_fail(UNICA_B200_ERR_CUDA, "cannot query the current CUDA device");
+    signed char state = device < MAX_DEVICES ? known[device].load(std::memory_order_relaxed) : 0;
+    if (state == 0) {
+        int major = 0, minor = 0;
+        if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess)
+            return unica_fail(UNICA_B200_ERR_CUDA, "cannot query the current CUDA device");
+        state = major == 10 && minor == 0 ? 1 : 2;  // sm_100a code runs on compute capability 10.0 only
+        if (device < MAX_DEVICES) known[device].store(state, std::memory_order_relaxed);
+    }
+    if (state != 1) return unica_fail(UNICA_B200_ERR_DEVICE, "these kernels are built for sm_100a (B200, compute capability 10.0) only");
     return UNICA_B200_OK;
 }
 

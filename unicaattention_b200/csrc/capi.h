@@ -8,7 +8,7 @@
 
 int unica_fail(int code, const char* message);
 int unica_check_launch(const char* what);  // cudaGetLastError after a launch -> 0 or UNICA_B200_ERR_CUDA
-int unica_check_device();                  // the current device must be compute capability 10.x
+int unica_check_device();                  // the current device must be compute capability 10.0 (cached per device)
 
 static inline unica::TokenLayout to_layout(const unica_token_layout& l) {
     unica::TokenLayout t;

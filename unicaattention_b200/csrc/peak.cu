@@ -116,14 +116,25 @@ extern "C" int unica_b200_peak(int kind, int n, int count, int blocks, double* c
     if (!cycles_per_instruction || count <= 0 || blocks <= 0 || blocks > 1024) return unica_fail(UNICA_B200_ERR_ARGUMENT, "peak: bad arguments");
     if (kind % 100 < 0 || kind % 100 > PEAK_F2I) return unica_fail(UNICA_B200_ERR_ARGUMENT, "peak: unknown kind");
     if (kind % 100 <= PEAK_NVF4 && (n < 16 || n > 240 || n % 16)) return unica_fail(UNICA_B200_ERR_ARGUMENT, "peak: n must be a multiple of 16 in 16..240");
+    if (kind % 100 <= PEAK_NVF4) {  // the descriptor's layout-type field takes these values only; + 10: the same with M = 64
+        const int layout = kind / 100 % 100 % 10, m64 = kind / 100 % 100 / 10;
+        if (m64 > 1 || (layout != 0 && layout != 1 && layout != 2 && layout != 4 && layout != 6))
+            return unica_fail(UNICA_B200_ERR_ARGUMENT, "peak: the layout digit must be 0, 1, 2, 4 or 6 (plus 10 for M = 64)");
+    } else if (kind >= 100) {
+        return unica_fail(UNICA_B200_ERR_ARGUMENT, "peak: scalar kinds take no variant digits");
+    }
     if (int e = unica_check_device()) return e;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     long long* cycles = nullptr;
     float* sink = nullptr;
     int* status = nullptr;
+    auto release = [&]() { cudaFree(cycles), cudaFree(sink), cudaFree(status); };  // cudaFree(nullptr) is a no-op
     if (cudaMalloc(&cycles, sizeof(long long) * blocks) != cudaSuccess || cudaMalloc(&sink, sizeof(float) * blocks * 512) != cudaSuccess ||
-        cudaMalloc(&status, sizeof(int)) != cudaSuccess || cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess)
-        return unica_check_launch("peak (scratch)");
+        cudaMalloc(&status, sizeof(int)) != cudaSuccess || cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess) {
+        const int e = unica_check_launch("peak (scratch)");
+        release();
+        return e;
+    }
     for (int rep = 0; rep < 2; ++rep) {  // the second run is the measured one
         if (kind % 100 <= PEAK_NVF4)
             peak_mma_kernel<<<blocks, 128, (128 + n) * 128 + 1024 + 128, s>>>(kind % 100, n, count, kind / 100 % 100, kind / 10000, cycles, status);
@@ -133,7 +144,7 @@ extern "C" int unica_b200_peak(int kind, int n, int count, int blocks, double* c
     long long host[1024];
     cudaError_t e = cudaMemcpyAsync(host, cycles, sizeof(long long) * blocks, cudaMemcpyDeviceToHost, s);
     if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-    cudaFree(cycles), cudaFree(sink), cudaFree(status);
+    release();
     if (e != cudaSuccess) return unica_fail(UNICA_B200_ERR_CUDA, cudaGetErrorString(e));
     for (int i = 1; i < blocks; ++i)  // insertion sort: blocks <= 1024
         for (int j = i; j > 0 && host[j - 1] > host[j]; --j) {

@@ -41,14 +41,10 @@ __global__ void __launch_bounds__(128) selftest_mma_nvf4_kernel(const uint8_t* _
     const uint32_t col_sfa = 160, col_sfb = 192;  // D takes columns 0 .. n - 1 (n <= 160)
     // scale bytes into tensor memory: every 32-lane quarter holds all rows
     for (int s = 0; s < k_steps; ++s) {
-        if (variant == 0) {
+        if (variant == 0)  // variant 2: A's scale words are copied from shared memory by the issuing thread below
             tmem_st4(my + col_sfa + 4 * s, sfa[s * 128 + lane], sfa[s * 128 + 32 + lane], sfa[s * 128 + 64 + lane], sfa[s * 128 + 96 + lane]);
-        } else if (variant == 2) {  // A's scale words are copied from shared memory by the issuing thread below
-        } else {  // diagnostic: row r in lane r, one column per K step
-            tmem_st1(my + col_sfa + 4 * s, sfa[s * 128 + threadIdx.x]);
-        }
         for (int c = 0; c < b_cols; ++c) {
-            const int row = variant != 1 ? 32 * c + lane : threadIdx.x + 128 * c;
+            const int row = 32 * c + lane;
             tmem_st1(my + col_sfb + b_cols * s + c, row < n ? sfb[s * n + row] : 0u);
         }
     }
@@ -94,12 +90,16 @@ extern "C" int unica_b200_selftest_mma_nvf4(const void* a_image, const void* b_i
     if (!a_image || !b_image || !sfa || !sfb || !d) return unica_fail(UNICA_B200_ERR_ARGUMENT, "selftest_mma_nvf4: null pointer");
     if (n < 16 || n > 160 || n % 16 || (k != 64 && k != 128))
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "selftest_mma_nvf4: n must be a multiple of 16 in 16..160, k 64 or 128");
+    if (variant != 0 && variant != 2) return unica_fail(UNICA_B200_ERR_ARGUMENT, "selftest_mma_nvf4: variant must be 0 or 2");
     if (int e = unica_check_device()) return e;
     const size_t smem = size_t(128 + n) * k / 2 + 128;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int* status = nullptr;
-    if (cudaMalloc(&status, sizeof(int)) != cudaSuccess || cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess)
-        return unica_check_launch("selftest_mma_nvf4 (status word)");
+    if (cudaMalloc(&status, sizeof(int)) != cudaSuccess || cudaMemsetAsync(status, 0, sizeof(int), s) != cudaSuccess) {
+        const int e = unica_check_launch("selftest_mma_nvf4 (status word)");
+        cudaFree(status);  // a no-op when the allocation itself failed
+        return e;
+    }
     selftest_mma_nvf4_kernel<<<1, 128, smem, s>>>(static_cast<const uint8_t*>(a_image), static_cast<const uint8_t*>(b_image),
                                                   static_cast<const uint32_t*>(sfa), static_cast<const uint32_t*>(sfb), n, k, variant, d, status);
     int host_status = 0;

@@ -90,10 +90,18 @@ def stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# kernels an entry point launches when it succeeds (the statistics passes: partial sums, then their reduction)
+KERNELS_PER_CALL = {"unica_b200_channel_stats": 2, "unica_b200_channel_stats_rope": 2, "unica_b200_channel_stats_masked": 2,
+                    "unica_b200_channel_stats_static": 2, "unica_b200_version": 0}
+launches = 0  # kernels of this library launched by this process so far (benchmarks report differences of it)
+
+
 def call(name: str, *args) -> None:
     """Run an entry point; ValueError for arguments it does not take, RuntimeError for everything else."""
+    global launches
     code = getattr(library(), name)(*args)
     if code == 0:
+        launches += KERNELS_PER_CALL.get(name, 1)
         return
     message = f"{name}: {last_error()}"
     raise ValueError(message) if code == ERR_ARGUMENT else RuntimeError(message)

@@ -41,14 +41,16 @@ def gather_heads(local: torch.Tensor, out: torch.Tensor, heads: int, rank: int, 
     return out
 
 
-def attention_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, group=None, **preset) -> torch.Tensor:
+def attention_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, group=None, out: torch.Tensor | None = None,
+                      **preset) -> torch.Tensor:
     """q, k, v: this rank's heads [batch, head_slice(heads, rank, world), tokens, 128].  Returns the whole
-    [batch, heads, n_queries, 128] output on every rank."""
+    [batch, heads, n_queries, 128] output on every rank (in `out` when given)."""
     import torch.distributed as dist
 
     import unicaattention_b200 as unica
 
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     local = unica.attention(q, k, v, **preset)
-    out = torch.empty((q.shape[0], heads, q.shape[2], q.shape[3]), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((q.shape[0], heads, q.shape[2], q.shape[3]), dtype=q.dtype, device=q.device)
     return gather_heads(local.contiguous(), out, heads, rank, world, group)
