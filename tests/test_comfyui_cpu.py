@@ -207,3 +207,57 @@ def test_fused_rope_forward(fake_unica):
     unica.attention = broken  # the fixture's monkeypatch restores it
     assert forward(x, freqs) == "model's own forward" and nodes.FAILED
     assert forward(x, freqs) == "model's own forward"
+
+
+def test_measurement_count_runs_per_step_and_block():
+    """The count is step * blocks + block + 1 within a run; calls outside the numbered blocks are not counted once the
+    model is known to number its blocks; a model that numbers none is counted call by call; off, nothing is read
+    (the reference's tests/test_comfyui.py:114-140)."""
+    m = nodes.Measurement("test")
+    m.every = 1000  # counting runs only while measuring
+    sigma = lambda s: {"sigmas": torch.tensor([s])}  # noqa: E731
+    seen = []
+    for s in (1.0, 0.5):  # two steps of a 3-block model, each preceded by a refiner call
+        m.due(sigma(s))
+        for block in range(3):
+            m.due(sigma(s) | {"block_index": block, "total_blocks": 3})
+            seen.append(m.calls)
+    assert seen == [1, 2, 3, 4, 5, 6], seen
+    m.due(sigma(1.0) | {"block_index": 0, "total_blocks": 3})  # sigma rises: a new run
+    assert m.calls == 1
+    plain = nodes.Measurement("test")
+    plain.every = 2
+    assert [plain.due(sigma(1.0)) for _ in range(4)] == [False, True, False, True]
+
+    class Untouchable:
+        def max(self):
+            raise AssertionError("sigma read while not measuring")
+
+    assert not nodes.Measurement("test").due({"sigmas": Untouchable(), "block_index": 0})
+
+
+def test_measurement_writes_a_row_per_measured_call(fake_unica, tmp_path, monkeypatch):
+    """Every second call of the native node is measured: one CSV row with the error of the call as it ran and of every
+    preset against FP32, the input statistics and the routes; with the flag file present the tensors are dumped too."""
+    import csv
+
+    monkeypatch.setenv("UNICA_MEASURE_DIR", str(tmp_path))
+    monkeypatch.delenv("UNICA_EMULATOR", raising=False)
+    (patched,) = nodes.UnicaAttentionNative().patch(Patcher(), True, v_scale="per_channel", measure_every=2, measure_heads=2,
+                                                    measure_tag="stand-in")
+    override = patched.model_options["transformer_options"]["optimized_attention_override"]
+    q = torch.randn(1, 40, 3 * 128)
+    override(model_attention, q, q, q, heads=3)
+    assert not (tmp_path / "attention_errors.csv").exists()
+    (tmp_path / "dumps.flag").touch()
+    override(model_attention, q, q[:, :7], q[:, :7], heads=3)  # passed on: counted as a route, not as a call
+    override(model_attention, q, q, q, heads=3)
+    with (tmp_path / "attention_errors.csv").open() as f:
+        rows = list(csv.DictReader(f))
+    assert len(rows) == 1 and rows[0]["tag"] == "stand-in" and rows[0]["ran"] == "per_channel" and rows[0]["call"] == "2"
+    assert rows[0]["heads_measured"] == "2" and rows[0]["tokens"] == "40" and "cross-attention=1" in rows[0]["routes"]
+    assert float(rows[0]["unica_rel_l2"]) < 0.05 and float(rows[0]["fast_rel_l2"]) < 0.05  # the stand-in is exact up to bf16
+    assert rows[0]["emulated_fast_rel_l2"] == "" and float(rows[0]["q_channel_spread"]) > 1
+    dumps = list((tmp_path / "dumps").glob("*.pt"))
+    assert len(dumps) == 1 and torch.load(dumps[0])["q"].shape == (1, 2, 40, 128)
+    nodes.native_measurement.configure(0, 0)

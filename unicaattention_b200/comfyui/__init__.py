@@ -1,6 +1,6 @@
 """ComfyUI nodes that run a model's self-attention on unicaattention_b200: the drop-in boundary of the reference's
-comfyui/__init__.py (same node classes, inputs, override call convention, routing rules, fallback and fused-RoPE
-forward), without its measurement CSV and RIFE node, which lie outside the attention path.
+comfyui/__init__.py (same node classes, inputs, override call convention, routing rules, fallback, fused-RoPE forward
+and measurement mode, see measure.py), without its SageAttention comparison and RIFE node.
 
     model -> Unica Attention (native)   -> sampler     ComfyUI's own models: an `optimized_attention_override`
     WanVideoModelLoader -> Unica Attention (WanVideo) -> WanVideoSampler   ComfyUI-WanVideoWrapper: `attention` wrapped
@@ -23,6 +23,7 @@ import sys
 import torch
 
 import unicaattention_b200 as unica
+from unicaattention_b200.comfyui.measure import Measurement
 
 HEAD_DIM = 128
 MODE = "unica"  # WanVideoWrapper attention modes: "unica" (per token), "unica_<v_scale>", "unica_fast"
@@ -35,6 +36,15 @@ POSITIONAL = ("heads", "mask", "attn_precision", "skip_reshape", "skip_output_re
 # what unica.attention raises for a call it cannot take (its checks) or cannot run (the library, the driver)
 UNICA_ERRORS = (RuntimeError, ValueError, TypeError)
 FAILED: list = []  # the first error, once a call has failed: from then on nothing is routed to unica
+measurement = Measurement("WanVideo")  # off until a node's measure_every input turns it on
+native_measurement = Measurement("native")
+MEASURE_INPUTS = {
+    "measure_every": ("INT", {"default": 0, "min": 0, "max": 100000,
+                              "tooltip": "Run every n-th self-attention call again with every preset and in FP32, and write "
+                                         "the errors to a CSV (0: off)"}),
+    "measure_heads": ("INT", {"default": 2, "min": 1, "max": 40, "tooltip": "Heads per measured call: the FP32 reference is slow"}),
+    "measure_tag": ("STRING", {"default": "", "tooltip": "Written into the measurement CSV, e.g. the model's name"}),
+}
 
 
 def unica_nhd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, settings: dict) -> torch.Tensor:
@@ -135,6 +145,7 @@ def native_override(previous, settings: dict):
     def override(func, q, k, v, *args, **kwargs):
         named = dict(zip(POSITIONAL, args)) | kwargs  # WAN passes heads by name, most other models by position
         override.last_reason = pass_through_reason(q, k, v, args, named)
+        native_measurement.route(override.last_reason, q, k)
         if override.last_reason is not None:
             return elsewhere(func, q, k, v, args, kwargs)
         heads = named["heads"]
@@ -147,6 +158,7 @@ def native_override(previous, settings: dict):
                 log.error("unica failed, the model's own attention takes over: %s", error)
             FAILED.append(error)
             return elsewhere(func, q, k, v, args, kwargs)
+        native_measurement(*nhd, settings, options=named.get("transformer_options"))
         return out.transpose(1, 2) if keep_heads else out.reshape(out.shape[0], out.shape[1], heads * HEAD_DIM)
 
     override.unica, override.previous, override.last_reason = True, previous, None
@@ -204,7 +216,7 @@ class UnicaAttentionNative:
     def INPUT_TYPES(cls):
         return {"required": {"model": ("MODEL",),
                              "enabled": ("BOOLEAN", {"default": True, "tooltip": "Off: the model as it came, for A/B runs"})},
-                "optional": dict(KERNEL_INPUTS) | {
+                "optional": dict(KERNEL_INPUTS) | MEASURE_INPUTS | {
                     "fuse_rope": ("BOOLEAN", {"default": False,
                                               "tooltip": "WAN models: rotate q and k inside the quantization instead of "
                                                          "in a pass of their own before attention"})}}
@@ -216,10 +228,14 @@ class UnicaAttentionNative:
     DESCRIPTION = ("Self-attention on unica-b200 through optimized_attention_override.  Put it after other attention "
                    "patches: calls it does not take (cross-attention, masks) go to the override before it.")
 
-    def patch(self, model, enabled, v_scale="per_token", mode="accurate", vram_reserve_mb=0, fuse_rope=False, **ignored):
+    def patch(self, model, enabled, v_scale="per_token", mode="accurate", vram_reserve_mb=0, fuse_rope=False, measure_every=0,
+              measure_heads=2, measure_tag="", **ignored):
         if not enabled or checked().status == unica.UNSUPPORTED:
             return (model,)
         settings = choose_kernel(v_scale, mode, vram_reserve_mb)
+        native_measurement.configure(measure_every, measure_heads, measure_tag)
+        native_measurement.routes.clear()
+        native_measurement.sigma, native_measurement.numbered = None, False  # a new model starts its own count
         patched = model.clone()
         options = patched.model_options.setdefault("transformer_options", {})
         previous = options.get("optimized_attention_override")
@@ -249,7 +265,9 @@ def wrap_attention() -> int:
                 return original(q, k, v, *args, attention_mode=attention_mode, **kwargs)
             if not FAILED:
                 try:
-                    return unica_nhd(q, k, v, settings)
+                    out = unica_nhd(q, k, v, settings)
+                    measurement(q, k, v, settings)
+                    return out
                 except UNICA_ERRORS as error:
                     log.error("unica failed, sdpa takes over: %s", error)
                     FAILED.append(error)
@@ -271,7 +289,7 @@ class UnicaAttentionWanVideo:
     def INPUT_TYPES(cls):
         return {"required": {"model": ("WANVIDEOMODEL",),
                              "enabled": ("BOOLEAN", {"default": True, "tooltip": "Off: the model as it came, for A/B runs"})},
-                "optional": dict(KERNEL_INPUTS)}
+                "optional": dict(KERNEL_INPUTS) | MEASURE_INPUTS}
 
     RETURN_TYPES = ("WANVIDEOMODEL",)
     RETURN_NAMES = ("model",)
@@ -279,10 +297,12 @@ class UnicaAttentionWanVideo:
     CATEGORY = "UnicaAttention"
     DESCRIPTION = "Self-attention of a WanVideoWrapper model on unica-b200 (attention mode override)"
 
-    def patch(self, model, enabled, v_scale="per_token", mode="accurate", vram_reserve_mb=0, **ignored):
+    def patch(self, model, enabled, v_scale="per_token", mode="accurate", vram_reserve_mb=0, measure_every=0, measure_heads=2,
+              measure_tag="", **ignored):
         if not enabled or checked().status == unica.UNSUPPORTED:
             return (model,)
         choose_kernel(v_scale, mode, vram_reserve_mb)  # sets the VRAM reserve; the settings travel in the mode's name
+        measurement.configure(measure_every, measure_heads, measure_tag)
         if not wrap_attention() and not _wrapped_already():
             raise RuntimeError("ComfyUI-WanVideoWrapper's wanvideo.modules.model is not loaded")
         patched = model.clone()

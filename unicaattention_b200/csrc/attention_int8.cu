@@ -7,10 +7,12 @@
 //   softmax A, B   key tiles t = 0, 2, 4 .. and 1, 3, 5 ..: the scores S(t) of tensor memory become the bytes
 //                  P^(t) = rint(255 * 2^(x - tile max)) of the A-operand image in shared memory.  They carry nothing from
 //                  tile to tile: the tile maximum and the row sum go to the flush threads through shared memory.
-//   flush 0, 1     output channels 0..63 and 64..127: out = out * alpha + beta * float(acc(t)) for every key tile t, the
-//                  row's 64 outputs in registers; they own the running exponent and the denominator, and write the result.
-//   service        one producer warp (bulk TMA copies of K8 / V8 tiles, contiguous 8 KB images written by the quantizers,
-//                  into a ring of shared-memory stages) and one MMA warp, one elected thread of which issues
+//   flush          out = out * alpha + beta * float(acc(t)) for every key tile t, the row's 128 outputs in registers
+//                  (-DUNICA_FLUSH_GROUPS=2: two warpgroups with 64 channels each); they own the running exponent and the
+//                  denominator, and write the result.
+//   service        four warps, one elected thread each: two (one per key-tile parity) copy K8 / V8 tiles (contiguous 8 KB
+//                  images written by the quantizers) into a ring of shared-memory stages with bulk TMA copies and issue the
+//                  scores, two issue P.V:
 //
 //   S(t)   = Q8 . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, a ring of 4 buffers
 //   acc(t) = P^(t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, two accumulators (t even / odd)
@@ -34,13 +36,36 @@
 
 namespace unica {
 
-constexpr int ATT_WARPS = 20, ATT_THREADS = ATT_WARPS * 32;
-constexpr int FLUSH_WARP = 8, PRODUCER_WARP = 16, MMA_WARP = 17;
-// registers per thread after setmaxnreg: 128 x (2 x 80 + 2 x 144 + 32) = 640 x 96, what the block is launched with
-constexpr int SOFTMAX_REGISTERS = 80, FLUSH_REGISTERS = 144, SERVICE_REGISTERS = 32;
+#ifndef UNICA_FLUSH_GROUPS
+#define UNICA_FLUSH_GROUPS 1
+#endif
+constexpr int FLUSH_GROUPS = UNICA_FLUSH_GROUPS;  // flush warpgroups: 1 (a thread owns the row's 128 outputs) or 2 (64 each)
+constexpr int FLUSH_CHANNELS = HEAD_DIM / FLUSH_GROUPS;
+#ifndef UNICA_FLUSH_MAGIC
+#define UNICA_FLUSH_MAGIC 0
+#endif
+// 1: the accumulators start at MAGIC_BITS like the score buffers (P.V always accumulates, the flush threads put the start
+// value back after reading) and the flush reads floats MAGIC + acc: a packed subtraction on the FMA pipe instead of an
+// int -> float conversion on the ALU pipe per value.  |acc| <= 64 * 255 * 127 < 2^21, so the float is exact.
+constexpr bool FLUSH_MAGIC = UNICA_FLUSH_MAGIC != 0;
+constexpr bool SINGLE_PASS = FLUSH_GROUPS == 1;  // the softmax keeps a row's 64 scores in registers (it has them with one flush warpgroup)
+constexpr int FLUSH_WARP = 8, SERVICE_WARP = FLUSH_WARP + 4 * FLUSH_GROUPS;
+constexpr int ATT_WARPS = SERVICE_WARP + 4, ATT_THREADS = ATT_WARPS * 32;
+// registers per thread after setmaxnreg; the block is launched with ATT_THREADS x LAUNCH_REGISTERS <= 65536
+constexpr int LAUNCH_REGISTERS = FLUSH_GROUPS == 1 ? 128 : 96;
+constexpr int SOFTMAX_REGISTERS = FLUSH_GROUPS == 1 ? 120 : 80, FLUSH_REGISTERS = FLUSH_GROUPS == 1 ? 232 : 144, SERVICE_REGISTERS = 32;
+static_assert(128 * (2 * SOFTMAX_REGISTERS + FLUSH_GROUPS * FLUSH_REGISTERS + SERVICE_REGISTERS) <= ATT_THREADS * LAUNCH_REGISTERS, "the split must fit the launch");
+template <int REGISTERS>
+__device__ __forceinline__ void set_registers() {  // every warp of a warpgroup executes it
+    if constexpr (REGISTERS > LAUNCH_REGISTERS)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGISTERS));
+    else
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGISTERS));
+}
 constexpr int STAGES = 6;   // K8 / V8 tiles in shared memory
 constexpr int S_RING = 4;   // score buffers in tensor memory
-constexpr int P_RING = STAGES;  // P^ images in shared memory: as many as stages (see the P.V issuing thread)
+constexpr int P_RING = STAGES;  // P^ images in shared memory: one per stage (see the P.V issuing thread)
+static_assert(STAGES % 2 == 0 && STAGES > S_RING, "a softmax warpgroup steps through the stages two at a time");
 constexpr int ST_RING = 8;  // (tile maximum, row sum) records on their way from the softmax to the flush threads
 constexpr int Q_BYTES = QUERY_TILE * HEAD_DIM;  // 16384
 constexpr int K_BYTES = KEY_TILE * HEAD_DIM;    // 8192
@@ -59,16 +84,20 @@ struct __align__(128) AttSmem {
     uint8_t p[P_RING][P_BYTES];
     float2 st[ST_RING][QUERY_TILE];
     uint64_t q_full, kv_full[STAGES], kv_empty[STAGES];
-    uint64_t s_ready, s_full[S_RING], soft_done[ST_RING], acc_full[2], acc_free[2], drain[2];
+    uint64_t s_ready, s_full[S_RING], soft_done[ST_RING], acc_free[2], drain[4];
+    int s_done[S_RING], acc_done[2];  // key tile + 1 of the last S / P.V seen complete in each buffer (see flag_publish)
     uint32_t tmem_base;
     int abort_flag;
 };
 
 // -DUNICA_TRACE: thread 0 of each role of block (0, 0) adds up the cycles it spends in each phase of its tile loop (the
 // reference has a TRACE build for the same purpose: csrc/legacy.cu, bench/timeline.py).  Rows of g_trace: softmax A,
-// softmax B, flush 0, MMA thread.  The totals stay in registers until the end: tracing costs a clock read per phase.
+// softmax B, flush 0, P.V-issuing thread, scores-issuing thread.  The totals stay in registers until the end: tracing costs a clock read per phase.
 #ifdef UNICA_TRACE
-__device__ long long g_trace[4][8];
+__device__ long long g_trace[5][8];
+__device__ long long g_events[8][16];  // absolute clocks of events of key tiles EVENT_FIRST .. +15 in block (0, 0)
+constexpr int EVENT_FIRST = 64;
+#define EVENT(kind, tile) do { if (tracing && (tile) >= EVENT_FIRST && (tile) < EVENT_FIRST + 16) g_events[kind][(tile) - EVENT_FIRST] = clock64(); } while (0)
 #define TRACE_DECL(on) long long trace_t0 = clock64(), trace_sum[8] = {}; const bool tracing = blockIdx.x == 0 && blockIdx.y == 0 && (on)
 #define TRACE(phase)                                 \
     do {                                             \
@@ -87,6 +116,7 @@ __device__ long long g_trace[4][8];
 #define TRACE_DECL(on)
 #define TRACE(phase)
 #define TRACE_END(slot)
+#define EVENT(kind, tile)
 #endif
 
 constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
@@ -119,15 +149,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         mbar_init(&sm.s_ready, 256);
         for (int b = 0; b < S_RING; ++b) mbar_init(&sm.s_full[b], 1);
         for (int b = 0; b < ST_RING; ++b) mbar_init(&sm.soft_done[b], 128);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&sm.acc_full[b], 1);
-            mbar_init(&sm.acc_free[b], 256);
-        }
-        mbar_init(&sm.drain[0], 1);
-        mbar_init(&sm.drain[1], 1);
+        for (int b = 0; b < 2; ++b) mbar_init(&sm.acc_free[b], 128 * FLUSH_GROUPS), sm.acc_done[b] = 0;
+        for (int b = 0; b < S_RING; ++b) sm.s_done[b] = 0;
+        for (int i = 0; i < 4; ++i) mbar_init(&sm.drain[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == MMA_WARP) tmem_alloc(&sm.tmem_base, TMEM_COLUMNS);
+    if (warp == SERVICE_WARP) tmem_alloc(&sm.tmem_base, TMEM_COLUMNS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -136,97 +163,128 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     const uint32_t lane_base = uint32_t((warp % 4) * 32) << 16;
     const bool ragged = n_keys % KEY_TILE != 0;  // the last key tile needs masking
 
-    if (warp >= PRODUCER_WARP) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SERVICE_REGISTERS));
-      if (warp == PRODUCER_WARP) {
-        // ------------------------------------------------------------------------------------------------ producer
+    if (warp >= SERVICE_WARP) {
+      set_registers<SERVICE_REGISTERS>();
+      // Four service warps, one elected thread each, two per key-tile parity.  A thread that issues tcgen05.mma runs a
+      // chain of dependent barrier probes and instruction issues that takes several hundred cycles per tile (a probe
+      // alone, by a lone thread, some 250), so the tiles are dealt out: no thread sees more than every other tile.
+      const int parity = (warp - SERVICE_WARP) & 1;
+      if (warp < SERVICE_WARP + 2) {
+        // -------------------------------------------------------------------------- scores S(n), n = parity, parity + 2, ..
+        // S(n) = Q8 . K8(n)^T goes out as soon as K8(n) has landed and the softmax of tile n - 4 (the same warpgroup's
+        // last tile but one) has handed the scores buffer back.
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
-            mbar_expect_tx(&sm.q_full, Q_BYTES);
-            bulk_load(sm.q, q8 + (size_t(head) * q_tiles + q_tile) * Q_BYTES, Q_BYTES, &sm.q_full);
-            int issued = 0;
-            for (int t = 0; t < k_tiles; ++t) {
-                const int s = t % STAGES, use = t / STAGES;
-                if (use > 0 && !mbar_wait(&sm.kv_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) break;
-                mbar_expect_tx(&sm.kv_full[s], K_BYTES + V_BYTES + (V_TOKEN ? TOK_BYTES : 0));
-                bulk_load(sm.k[s], k8 + (size_t(head) * k_tiles + t) * K_BYTES, K_BYTES, &sm.kv_full[s]);
-                bulk_load(sm.v[s], v8 + (size_t(head) * k_tiles + t) * V_BYTES, V_BYTES, &sm.kv_full[s]);
-                if (V_TOKEN) bulk_load(sm.tok[s], v_token + (size_t(head) * k_tiles + t) * (2 * KEY_TILE), TOK_BYTES, &sm.kv_full[s]);
-                issued = t + 1;
+            const uint64_t q_desc0 = smem_desc(smem_u32(sm.q), QUERY_TILE * 16, 128), k_desc0 = smem_desc(smem_u32(sm.k[0]), KEY_TILE * 16, 128);
+            bool ok = mbar_wait2(&sm.q_full, 0, &sm.s_ready, 0, abort_flag, status, STATUS_WAIT_TILE);  // s_ready: the score buffers hold their start value
+            TRACE_DECL(true);
+            for (int n = parity, stage = parity, phase = 0; ok && n < k_tiles; n += 2) {
+                const int buf = n % S_RING;
+                TRACE(7);
+                ok = mbar_wait2(&sm.kv_full[stage], phase, &sm.soft_done[(n - S_RING) & (ST_RING - 1)], n >= S_RING ? ((n - S_RING) / ST_RING) & 1 : -1,
+                                abort_flag, status, STATUS_WAIT_TILE);
+                TRACE(0);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t k_desc = k_desc0 + uint64_t(stage * (K_BYTES / 16));
+#pragma unroll
+                for (int ks = 0; ks < HEAD_DIM / 32; ++ks)
+                    mma_i8_ss(tmem + COL_S + buf * 64, q_desc0 + ks * (2 * QUERY_TILE * 16 / 16), k_desc + ks * (2 * KEY_TILE * 16 / 16), IDESC_QK, true);
+                mma_commit(&sm.s_full[buf]);
+                TRACE(2);
+                EVENT(6, n);
+                // the thread watches its own instructions complete and tells the softmax threads through a word they can
+                // look at cheaply
+                ok = mbar_wait(&sm.s_full[buf], (n / S_RING) & 1, abort_flag, status, STATUS_WAIT_SCORES);
+                if (!ok) break;
+                tc_fence_before();
+                flag_publish(&sm.s_done[buf], n + 1);
+                TRACE(3);
+                stage += 2;
+                if (stage >= STAGES) stage -= STAGES, phase ^= 1;
             }
-            if (*abort_flag) {  // let the copies still in flight land before the block's shared memory goes away
+            if (parity == 0) TRACE_END(4);
+            if (!ok) {  // whatever was issued must finish before tensor memory is freed
                 int never = 0;
-                for (int t = max(0, issued - STAGES); t < issued; ++t) mbar_wait(&sm.kv_full[t % STAGES], (t / STAGES) & 1, &never, nullptr, 0);
-                mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
+                mma_commit(&sm.drain[parity]);
+                mbar_wait(&sm.drain[parity], 0, &never, nullptr, 0);
             }
         }
-      } else if (warp == MMA_WARP) {
-        // ---------------------------------------------------------------------------------------- MMA issue: P.V
-        // One elected thread issues P.V(t) for every key tile as soon as P^(t) is delivered and the flush of tile t - 2
-        // has read the accumulator.  Its commit also hands the K8 / V8 stage back to the producer (the scores of the
-        // tile were issued four tiles earlier), which the P^ ring relies on: scores S(t) can only be issued into a stage
-        // P.V(t - STAGES) has released, so when they complete, the P^ image of tile t - STAGES has been read.
+      } else {
+        // -------------------------------------------------------------------------- P.V(t) and the K8 / V8 copies, t = parity, parity + 2, ..
+        // P.V(t), into accumulator `parity`, goes out as soon as P^(t) is delivered and the flush of tile t - 2 has read the
+        // accumulator.  When it completes, its stage is free and the same thread copies tile t + STAGES into it (contiguous
+        // 8 KB images written by the quantizers, bulk TMA).  The P^ ring relies on that order: scores S(t) can only be issued
+        // once K8(t) has landed in the stage P.V(t - STAGES) has released, so when they complete, the P^ image of tile
+        // t - STAGES has been read.  V8(t) landed before S(t) was issued, which the softmax of tile t waited for before it
+        // delivered P^(t).
         if (elect_one()) {
+            const int8_t* k_src = k8 + size_t(head) * k_tiles * K_BYTES;
+            const int8_t* v_src = v8 + size_t(head) * k_tiles * V_BYTES;
+            const float* tok_src = V_TOKEN ? v_token + size_t(head) * k_tiles * (2 * KEY_TILE) : nullptr;
+            int issued = 0;  // copies of this parity's tiles issued so far
             TRACE_DECL(true);
+            auto copy_tile = [&](int tile, int stage) {
+                mbar_expect_tx(&sm.kv_full[stage], K_BYTES + V_BYTES + (V_TOKEN ? TOK_BYTES : 0));
+                bulk_load(sm.k[stage], k_src + size_t(tile) * K_BYTES, K_BYTES, &sm.kv_full[stage]);
+                bulk_load(sm.v[stage], v_src + size_t(tile) * V_BYTES, V_BYTES, &sm.kv_full[stage]);
+                if (V_TOKEN) bulk_load(sm.tok[stage], tok_src + size_t(tile) * (2 * KEY_TILE), TOK_BYTES, &sm.kv_full[stage]);
+                ++issued;
+                EVENT(7, tile);
+            };
+            if (parity == 0) {
+                mbar_expect_tx(&sm.q_full, Q_BYTES);
+                bulk_load(sm.q, q8 + (size_t(head) * q_tiles + q_tile) * Q_BYTES, Q_BYTES, &sm.q_full);
+            }
+            for (int n = parity; n < min(k_tiles, STAGES); n += 2) copy_tile(n, n);
             bool ok = true;
-            for (int t = 0; ok && t < k_tiles; ++t) {
-                const int stage = t % STAGES, b = t & 1;
+            const int b = parity;
+            const uint64_t p_desc0 = smem_desc(smem_u32(sm.p[0]), QUERY_TILE * 16, 128), v_desc0 = smem_desc(smem_u32(sm.v[0]), HEAD_DIM * 16, 128);
+            for (int t = parity, stage = parity, phase = 0; ok && t < k_tiles; t += 2) {
                 TRACE(7);
-                ok = mbar_wait(&sm.kv_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);  // landed long ago: V8(t) made visible to this thread
-                TRACE(0);
-                if (t >= 2) ok = ok && mbar_wait(&sm.acc_free[b], ((t - 2) >> 1) & 1, abort_flag, status, STATUS_WAIT_FREE);
-                TRACE(2);
-                ok = ok && mbar_wait(&sm.soft_done[t % ST_RING], (t / ST_RING) & 1, abort_flag, status, STATUS_WAIT_P);
+                // acc_free: with start values (FLUSH_MAGIC) phase 0 is the flush threads' first fill; without, the flush of tile t - 2
+                const int free_parity = FLUSH_MAGIC ? (t >> 1) & 1 : t >= 2 ? ((t - 2) >> 1) & 1 : -1;
+                ok = mbar_wait2(&sm.soft_done[t % ST_RING], (t / ST_RING) & 1, &sm.acc_free[b], free_parity, abort_flag, status, STATUS_WAIT_P);
                 TRACE(3);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t p_addr = smem_u32(sm.p[t % P_RING]), v_addr = smem_u32(sm.v[stage]);
+                // a descriptor's address field counts 16-byte units: the images of stage `stage`, K step ks
+                const uint64_t p_desc = p_desc0 + uint64_t(stage * (P_BYTES / 16)), v_desc = v_desc0 + uint64_t(stage * (V_BYTES / 16));
 #pragma unroll
                 for (int ks = 0; ks < KEY_TILE / 32; ++ks)
-                    mma_i8_ss(tmem + COL_ACC + b * 128, smem_desc(p_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                              smem_desc(v_addr + ks * 2 * HEAD_DIM * 16, HEAD_DIM * 16, 128), IDESC_PV, ks > 0);  // the first instruction of a tile overwrites the accumulator
-                mma_commit(&sm.acc_full[b]);
+                    mma_i8_ss(tmem + COL_ACC + b * 128, p_desc + ks * (2 * QUERY_TILE * 16 / 16), v_desc + ks * (2 * HEAD_DIM * 16 / 16), IDESC_PV,
+                              FLUSH_MAGIC || ks > 0);  // without the start value the first instruction of a tile overwrites the accumulator
                 mma_commit(&sm.kv_empty[stage]);
                 TRACE(4);
-            }
-            TRACE_END(3);
-            if (!ok) {  // whatever was issued must finish before tensor memory is freed
-                int never = 0;
-                mma_commit(&sm.drain[0]);
-                mbar_wait(&sm.drain[0], 0, &never, nullptr, 0);
-            }
-        }
-      } else if (warp == MMA_WARP + 1) {
-        // ---------------------------------------------------------------------------------------- MMA issue: scores
-        // A second elected thread issues S(n) = Q8 . K8(n)^T as soon as K8(n) has landed and the softmax of tile n - 4
-        // has handed the scores buffer back.
-        if (elect_one()) {
-            const uint32_t q_addr = smem_u32(sm.q);
-            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
-                      mbar_wait(&sm.s_ready, 0, abort_flag, status, STATUS_WAIT_FREE);  // the score buffers hold their start value
-            for (int n = 0; ok && n < k_tiles; ++n) {
-                const int stage = n % STAGES, buf = n % S_RING;
-                ok = mbar_wait(&sm.kv_full[stage], (n / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
-                if (n >= S_RING)
-                    ok = ok && mbar_wait(&sm.soft_done[(n - S_RING) % ST_RING], ((n - S_RING) / ST_RING) & 1, abort_flag, status, STATUS_WAIT_FREE);
+                EVENT(2, t);
+                // P.V(t) complete: the flush threads are told through a word they can look at cheaply, and the stage is free
+                ok = mbar_wait(&sm.kv_empty[stage], phase, abort_flag, status, STATUS_WAIT_STAGE);
                 if (!ok) break;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(sm.k[stage]);
-#pragma unroll
-                for (int ks = 0; ks < HEAD_DIM / 32; ++ks)
-                    mma_i8_ss(tmem + COL_S + buf * 64, smem_desc(q_addr + ks * 2 * QUERY_TILE * 16, QUERY_TILE * 16, 128),
-                              smem_desc(k_addr + ks * 2 * KEY_TILE * 16, KEY_TILE * 16, 128), IDESC_QK, true);
-                mma_commit(&sm.s_full[buf]);
+                tc_fence_before();
+                flag_publish(&sm.acc_done[b], t + 1);
+                if (t + STAGES < k_tiles) copy_tile(t + STAGES, stage);
+                TRACE(5);
+                stage += 2;
+                if (stage >= STAGES) stage -= STAGES, phase ^= 1;
             }
+            if (parity == 0) TRACE_END(3);
             if (!ok) {
                 int never = 0;
-                mma_commit(&sm.drain[1]);
-                mbar_wait(&sm.drain[1], 0, &never, nullptr, 0);
+                mma_commit(&sm.drain[2 + parity]);
+                mbar_wait(&sm.drain[2 + parity], 0, &never, nullptr, 0);
+            }
+            if (*abort_flag) {  // let the copies still in flight land before the block's shared memory goes away
+                int never = 0;
+                for (int i = max(0, issued - STAGES / 2); i < issued; ++i) {
+                    const int tile = parity + 2 * i;
+                    mbar_wait(&sm.kv_full[tile % STAGES], (tile / STAGES) & 1, &never, nullptr, 0);
+                }
+                mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
       }
     } else if (warp < FLUSH_WARP) {
         // ------------------------------------------------------------------------------------------------ softmax
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGISTERS));
+        set_registers<SOFTMAX_REGISTERS>();
         const int parity = warp / 4;  // this warpgroup's key tiles: t = parity, parity + 2, ..
         const uint32_t t_s = tmem + lane_base + COL_S;
         const float sq = q_scale[size_t(head) * q_tiles + q_tile];
@@ -250,103 +308,73 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 
         TRACE_DECL(row == 0);
         // One key tile: scores -> P^ bytes in shared memory, (tile maximum, row sum) -> the flush threads.
-        auto softmax_tile = [&](auto masked_c, int t, float c) -> bool {
+        auto softmax_tile = [&](auto masked_c, int t, float c, int buf, int stage, int kv_phase, int record) -> bool {
             constexpr bool MASKED = decltype(masked_c)::value;
-            const int buf = t % S_RING, stage = t % STAGES;
-            const int valid = min(KEY_TILE, n_keys - t * KEY_TILE);
+            const int valid = MASKED ? n_keys - t * KEY_TILE : KEY_TILE;
             const uint32_t ts = t_s + buf * 64;
             TRACE(7);
-            if (!mbar_wait_warp(&sm.s_full[buf], (t / S_RING) & 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+            if (!flag_wait_warp(&sm.s_done[buf], t + 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
             TRACE(0);
-            if (V_TOKEN && !mbar_wait_warp(&sm.kv_full[stage], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+            EVENT(0, t);
+            if (V_TOKEN && !mbar_wait_warp(&sm.kv_full[stage], kv_phase, abort_flag, status, STATUS_WAIT_TILE)) return false;
             tc_fence_after();
+#if defined(UNICA_STUB) && (UNICA_STUB & 1)  // measurement only: the protocol without the arithmetic (results are wrong)
+            sm.st[record][row] = make_float2(0.0f, 1.0f);
+            tc_fence_before();
+            fence_proxy_async();
+            mbar_arrive(&sm.soft_done[record]);
+            return true;
+#endif
             const float2 c2 = make_float2(c, c), minus_magic = make_float2(-MAGIC, -MAGIC);
             const float4* log_s4 = reinterpret_cast<const float4*>(sm.tok[stage]);
             const float4* inv_s4 = reinterpret_cast<const float4*>(sm.tok[stage] + KEY_TILE);
-            float2 x[2][8];  // 16 scores in use, 16 on their way
-
-            // Pass 1: the tile maximum (the 64 scores are read again below: they would not fit next to the rest).
-            float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-            tmem_ld16_async(ts, x[0]);
-            tmem_ld16_async(ts + 16, x[1]);
-#pragma unroll
-            for (int step = 0; step < KEY_TILE / 16; ++step) {
-                float2(&y)[8] = x[step % 2];
-                if (step % 2 == 0) tmem_wait_ld();  // both loads in flight
-                reg_fence8(y);
-                if (V_TOKEN) {  // log2 s_j joins the scores before the maximum
-#pragma unroll
-                    for (int j = 0; j < 8; j += 2) {
-                        const float4 l = log_s4[step * 4 + j / 2];
-                        y[j] = fma2(add2(y[j], minus_magic), c2, make_float2(l.x, l.y));
-                        y[j + 1] = fma2(add2(y[j + 1], minus_magic), c2, make_float2(l.z, l.w));
-                    }
-                }
-                if (MASKED) {  // keys past the end: below every real score (|score| < 2^21)
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (step * 16 + j >= valid) (j % 2 ? y[j / 2].y : y[j / 2].x) = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) top[j % 4] = max3(top[j % 4], y[j].x, y[j].y);
-                if (step + 2 < KEY_TILE / 16) {
-                    reg_fence8(y);
-                    tmem_ld16_async(ts + (step + 2) * 16, y);
-                }
-            }
-            float tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-            TRACE(1);
-            if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
-            const float offset = LOG2_255 - tile_max;
-
-            // Pass 2: P^ = rint(255 * 2^(score * c - tile max)), 16 keys at a time.  Per channel the float read back is
-            // MAGIC + score, so the exponent is x * c + (offset - MAGIC * c) in ONE fused multiply-add; what the rounding
-            // of that constant loses (it is about 2^11 in size) is put back exactly: `low` is the lost part, and the
-            // product p * 2^low happens inside the multiply-add that rounds p to a byte.
+            // Sixteen keys: P^ = rint(255 * 2^(score * c - tile max)) into the A-operand image, written stage by stage
+            // (exponents, exponentials, rounding, packing) so that every instruction has fifteen independent ones around
+            // it: the exponential unit takes a warp every 8 cycles and answers after some twenty, and a thread that asks
+            // for one result at a time waits for each.  Per channel the float read back is MAGIC + score, so the exponent is
+            // x * c + (offset - MAGIC * c) in ONE fused multiply-add; what the rounding of that constant loses (it is about
+            // 2^11 in size) is put back exactly: `low` is the lost part, and the product p * 2^low happens inside the
+            // multiply-add that rounds p to a byte.
             float2 base2, k2;
-            if (!V_TOKEN) {
-                const float a_hi = __fmul_rn(-MAGIC, c), a_lo = __fmaf_rn(-MAGIC, c, -a_hi);  // -MAGIC * c = a_hi + a_lo exactly
-                const float s = __fadd_rn(a_hi, offset), bb = __fsub_rn(s, a_hi);
-                const float low = __fadd_rn(__fadd_rn(__fsub_rn(a_hi, __fsub_rn(s, bb)), __fsub_rn(offset, bb)), a_lo);  // a_hi + offset = s + ..
-                const float k = __fmaf_rn(low, 0.693147181f, 1.0f);  // 2^low, |low| < 2^-12
-                base2 = make_float2(s, s), k2 = make_float2(k, k);
-            } else {
-                base2 = make_float2(offset, offset), k2 = make_float2(1.0f, 1.0f);
-            }
             const float2 plus_magic = make_float2(MAGIC, MAGIC);
-            uint8_t* p_row = sm.p[t % P_RING] + row * 16;
+            uint8_t* p_row = sm.p[stage] + row * 16;  // the P^ ring runs with the stages
             unsigned isum[2] = {0, 0};
             float2 fsum = make_float2(0.0f, 0.0f);
-            tmem_ld16_async(ts, x[0]);
-#pragma unroll
-            for (int step = 0; step < KEY_TILE / 16; ++step) {
-                float2(&y)[8] = x[step % 2];
-                tmem_wait_ld();
-                reg_fence8(y);
-                if (step + 1 < KEY_TILE / 16) {
-                    tmem_ld16_async(ts + (step + 1) * 16, x[(step + 1) % 2]);
-                } else {  // every score has been read: the buffer goes back to its start value for S(t + 4)
-                    tmem_fill<KEY_TILE>(ts, magic);
+            auto constants = [&](float tile_max) {
+                const float offset = LOG2_255 - tile_max;
+                if (!V_TOKEN) {
+                    const float a_hi = __fmul_rn(-MAGIC, c), a_lo = __fmaf_rn(-MAGIC, c, -a_hi);  // -MAGIC * c = a_hi + a_lo exactly
+                    const float sum = __fadd_rn(a_hi, offset), bb = __fsub_rn(sum, a_hi);
+                    const float low = __fadd_rn(__fadd_rn(__fsub_rn(a_hi, __fsub_rn(sum, bb)), __fsub_rn(offset, bb)), a_lo);  // a_hi + offset = sum + ..
+                    const float k = __fmaf_rn(low, 0.693147181f, 1.0f);  // 2^low, |low| < 2^-12
+                    base2 = make_float2(sum, sum), k2 = make_float2(k, k);
+                } else {
+                    base2 = make_float2(offset, offset), k2 = make_float2(1.0f, 1.0f);
                 }
+            };
+            // y: per channel MAGIC + score; per token score * c + log2 s_j
+            auto sixteen_keys = [&](const float2 (&y)[8], int step) {
+                float2 e[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = V_TOKEN ? add2(y[j], base2) : fma2(y[j], c2, base2);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = make_float2(ex2(e[j].x), ex2(e[j].y));
+                if (V_TOKEN) {  // the denominator sums p / s_j before rounding
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        const float4 r = inv_s4[step * 4 + j / 2];
+                        fsum = fma2(e[j], make_float2(r.x, r.y), fsum);
+                        fsum = fma2(e[j + 1], make_float2(r.z, r.w), fsum);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) e[j] = V_TOKEN ? add2(e[j], plus_magic) : fma2(e[j], k2, plus_magic);  // the low byte of each is rint(p)
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    uint32_t pair[2];
-                    float4 l = make_float4(0.0f, 0.0f, 0.0f, 0.0f), r = l;  // log2 s and 1 / s of the four keys
-                    if (V_TOKEN) l = log_s4[step * 4 + i], r = inv_s4[step * 4 + i];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {  // a pair of keys
-                        float2 e;
-                        if (V_TOKEN)
-                            e = add2(fma2(add2(y[i * 2 + h], minus_magic), c2, h ? make_float2(l.z, l.w) : make_float2(l.x, l.y)), base2);
-                        else
-                            e = fma2(y[i * 2 + h], c2, base2);
-                        const float2 p = make_float2(ex2(e.x), ex2(e.y));
-                        if (V_TOKEN) fsum = fma2(p, h ? make_float2(r.z, r.w) : make_float2(r.x, r.y), fsum);
-                        const float2 rounded = V_TOKEN ? add2(p, plus_magic) : fma2(p, k2, plus_magic);  // the low byte of each is rint(p)
-                        pair[h] = __byte_perm(__float_as_uint(rounded.x), __float_as_uint(rounded.y), 0x0040);
-                    }
-                    w[i] = __byte_perm(pair[0], pair[1], 0x5410);
+                    const uint32_t lo = __byte_perm(__float_as_uint(e[2 * i].x), __float_as_uint(e[2 * i].y), 0x0040);
+                    const uint32_t hi = __byte_perm(__float_as_uint(e[2 * i + 1].x), __float_as_uint(e[2 * i + 1].y), 0x0040);
+                    w[i] = __byte_perm(lo, hi, 0x5410);
                     if (!V_TOKEN && MASKED) {  // keys past the end weigh nothing
                         const int left = valid - (step * 16 + i * 4);
                         w[i] = left >= 4 ? w[i] : left <= 0 ? 0u : (w[i] & ((1u << (8 * left)) - 1u));
@@ -354,86 +382,205 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
                 }
                 *reinterpret_cast<uint4*>(p_row + step * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            };
+            // log2 s_j joins the scores of a per-token tile before the maximum; keys past the end go below every real score
+            auto prepare = [&](float2 (&y)[8], int step) {
+                if (V_TOKEN) {
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        const float4 l = log_s4[step * 4 + j / 2];
+                        y[j] = fma2(add2(y[j], minus_magic), c2, make_float2(l.x, l.y));
+                        y[j + 1] = fma2(add2(y[j + 1], minus_magic), c2, make_float2(l.z, l.w));
+                    }
+                }
+                if (MASKED) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (step * 16 + j >= valid) (j % 2 ? y[j / 2].y : y[j / 2].x) = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;  // |score| < 2^21
+                }
+            };
+            float tile_max;
+            if constexpr (SINGLE_PASS) {
+                // The row's 64 scores, read once and kept in registers; the buffer goes back to its start value for
+                // S(t + 4) at once (the stores run while the arithmetic does; they are waited for at the hand-over).
+                float2 x[KEY_TILE / 16][8];
+                tmem_ld64_sync(ts, reinterpret_cast<float2(&)[KEY_TILE / 2]>(x));
+#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 2))  // measurement only (wrong results): what each synchronising step costs
+                tmem_fill<KEY_TILE>(ts, magic);
+#endif
+                float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int step = 0; step < KEY_TILE / 16; ++step) {
+                    prepare(x[step], step);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) top[j % 4] = max3(top[j % 4], x[step][j].x, x[step][j].y);
+                }
+                tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
+                TRACE(1);
+                if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
+                constants(tile_max);
+#pragma unroll
+                for (int step = 0; step < KEY_TILE / 16; ++step) sixteen_keys(x[step], step);
+            } else {
+                // Two passes over the scores, 16 at a time (they would not fit next to the rest): the tile maximum, then
+                // the exponentials; the next 16 are on their way while 16 are used.
+                float2 x[2][8];
+                float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                tmem_ld16_async(ts, x[0]);
+                tmem_ld16_async(ts + 16, x[1]);
+#pragma unroll
+                for (int step = 0; step < KEY_TILE / 16; ++step) {
+                    float2(&y)[8] = x[step % 2];
+                    if (step % 2 == 0) tmem_wait_ld();  // both loads in flight
+                    reg_fence8(y);
+                    prepare(y, step);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) top[j % 4] = max3(top[j % 4], y[j].x, y[j].y);
+                    reg_fence8(y);
+                    tmem_ld16_async(ts + ((step + 2) % 4) * 16, y);  // steps 2, 3 fetch the first chunks of the second pass
+                }
+                tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
+                TRACE(1);
+                if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
+                constants(tile_max);
+#pragma unroll
+                for (int step = 0; step < KEY_TILE / 16; ++step) {
+                    float2(&y)[8] = x[step % 2];
+                    if (step % 2 == 0) tmem_wait_ld();
+                    reg_fence8(y);
+                    if (step == 2) tmem_fill<KEY_TILE>(ts, magic);  // every score has been read: the buffer goes back to its start value for S(t + 4)
+                    if (V_TOKEN) prepare(y, step);  // the score with log2 s_j, once more
+                    sixteen_keys(y, step);
+                    if (step + 2 < KEY_TILE / 16) {
+                        reg_fence8(y);
+                        tmem_ld16_async(ts + (step + 2) * 16, y);
+                    }
+                }
             }
             TRACE(2);
-            sm.st[t % ST_RING][row] = make_float2(tile_max, V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1]));
+            sm.st[record][row] = make_float2(tile_max, V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1]));
+#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 2))
             tmem_wait_st();
+#endif
+#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 4))
             tc_fence_before();
+#endif
+#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 1))
             fence_proxy_async();
-            mbar_arrive(&sm.soft_done[t % ST_RING]);  // P^(t) and its record delivered, the scores buffer back at its start value
+#endif
+            mbar_arrive(&sm.soft_done[record]);  // P^(t) and its record delivered, the scores buffer back at its start value
             TRACE(3);
+            EVENT(1, t);
             return true;
         };
 
         bool ok = true;
+        // this warpgroup's tiles advance by two: ring positions and barrier phases are kept as counters
+        int buf = parity, stage = parity, kv_phase = 0, record = parity;
         for (int t = parity; ok && t < k_tiles; t += 2) {
             const float c = (sq * sk_reg) * scale_log2;
             if (t + 2 < k_tiles) sk_reg = load_scale(sk + t + 2);
-            ok = ragged && t + 1 == k_tiles ? softmax_tile(std::true_type{}, t, c) : softmax_tile(std::false_type{}, t, c);
+            ok = ragged && t + 1 == k_tiles ? softmax_tile(std::true_type{}, t, c, buf, stage, kv_phase, record)
+                                            : softmax_tile(std::false_type{}, t, c, buf, stage, kv_phase, record);
+            buf ^= 2;
+            stage += 2;
+            if (stage >= STAGES) stage -= STAGES, kv_phase ^= 1;
+            record = (record + 2) % ST_RING;
         }
         TRACE_END(parity);
     } else {
         // ------------------------------------------------------------------------------------------------ flush
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(FLUSH_REGISTERS));
-        const int half = (warp - FLUSH_WARP) / 4;  // output channels 64 half .. 64 half + 63
-        const uint32_t t_acc = tmem + lane_base + COL_ACC + half * 64;
+        set_registers<FLUSH_REGISTERS>();
+        const int half = (warp - FLUSH_WARP) / 4;  // output channels FLUSH_CHANNELS * half ..
+        const uint32_t t_acc = tmem + lane_base + COL_ACC + half * FLUSH_CHANNELS;
         float m = -INFINITY, den = 0.0f;
-        float2 o[HEAD_DIM / 4];
+        float2 o[FLUSH_CHANNELS / 2];
 #pragma unroll
-        for (int i = 0; i < HEAD_DIM / 4; ++i) o[i] = make_float2(0.0f, 0.0f);
-
-        auto flush_tile = [&](auto rescale_c, const float2 (&a0)[16], const float2 (&a1)[16], float alpha, float beta) {
-            constexpr bool RESCALE = decltype(rescale_c)::value;
-            const float2 alpha2 = make_float2(alpha, alpha), beta2 = make_float2(beta, beta);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {  // the accumulator is overwritten by every tile's P.V: plain integers
-                const float2 raw = i < 16 ? a0[i % 16] : a1[i % 16];
-                const float2 f = make_float2(__int2float_rn(__float_as_int(raw.x)), __int2float_rn(__float_as_int(raw.y)));
-                o[i] = fma2(beta2, f, RESCALE ? mul2(o[i], alpha2) : o[i]);
-            }
-        };
+        for (int i = 0; i < FLUSH_CHANNELS / 2; ++i) o[i] = make_float2(0.0f, 0.0f);
+        uint32_t magic[FILL_BLOCK];
+        const float2 minus_magic = make_float2(-MAGIC, -MAGIC);
+        if (FLUSH_MAGIC) {
+            fill_block_init(magic, MAGIC_BITS);
+            tmem_fill<FLUSH_CHANNELS>(t_acc, magic);
+            tmem_fill<FLUSH_CHANNELS>(t_acc + 128, magic);
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&sm.acc_free[0]);
+            mbar_arrive(&sm.acc_free[1]);
+        }
 
         bool ok = true;
         TRACE_DECL(row == 0 && half == 0);
+        constexpr int PARTS = FLUSH_CHANNELS / 32;
         for (int t = 0; ok && t < k_tiles; ++t) {
             const int b = t & 1;
             TRACE(7);
-            if (!mbar_wait_warp(&sm.soft_done[t % ST_RING], (t / ST_RING) & 1, abort_flag, status, STATUS_WAIT_P)) {
+            // P.V(t) was issued after the softmax of tile t had delivered its record, so the record is there too
+            if (!flag_wait_warp(&sm.acc_done[b], t + 1, abort_flag, status, STATUS_WAIT_PV)) {
                 ok = false;
                 break;
             }
+            tc_fence_after();
+            float2 a[2][16];  // 32 channels each, one pair in flight while the other is used
+            tmem_ld32_async(t_acc + b * 128, a[0]);
+            tmem_ld32_async(t_acc + b * 128 + 32, a[1]);
+            TRACE(1);
+            EVENT(3, t);
+#if defined(UNICA_STUB) && (UNICA_STUB & 2)  // measurement only
+            tmem_wait_ld();
+            tc_fence_before();
+            mbar_arrive(&sm.acc_free[b]);
+            continue;
+#endif
             // `m` is the exponent the row's sums are kept at, not the running maximum: out = sum over tiles of
             // 2^(tile max - m) * acc, the same for the denominator, and the common factor cancels at the end.  The
             // textbook form moves m to every new maximum and multiplies out and den by alpha = 2^(m_old - m_new) each
             // time; here m moves only when a tile maximum is more than 2^REFERENCE_SLACK above it, so that
             // multiplication all but disappears.  The difference is rounding only.
-            TRACE(0);
             const float2 record = sm.st[t % ST_RING][row];  // tile maximum, row sum
             const bool first = m == -INFINITY;
             const float m_new = record.x > m + REFERENCE_SLACK ? record.x : m;
             const float alpha = first ? 1.0f : ex2(m - m_new), beta = ex2(record.x - m_new);
             m = m_new;
             den = den * alpha + record.y * beta;
-            if (!mbar_wait_warp(&sm.acc_full[b], (t >> 1) & 1, abort_flag, status, STATUS_WAIT_PV)) {
-                ok = false;
-                break;
+            const float2 alpha2 = make_float2(alpha, alpha), beta2 = make_float2(beta, beta);
+            const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);
+#pragma unroll
+            for (int part = 0; part < PARTS; ++part) {  // 32 channels at a time
+                float2(&y)[16] = a[part % 2];
+                if (part % 2 == 0) {
+                    tmem_wait_ld();  // both loads in flight
+                    if (part + 2 >= PARTS) {  // the accumulator has been read
+                        if (!FLUSH_MAGIC) {  // P.V(t + 2) may overwrite it
+                            tc_fence_before();
+                            mbar_arrive(&sm.acc_free[b]);
+                            EVENT(4, t);
+                        }
+                    }
+                }
+                reg_fence16(y);
+                if (FLUSH_MAGIC) tmem_fill<32>(t_acc + b * 128 + part * 32, magic);  // read: the start value goes back in
+                if (rescale) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[part * 16 + i] = mul2(o[part * 16 + i], alpha2);
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i)  // without the start value the accumulator is overwritten by every tile's P.V: plain integers
+                    y[i] = FLUSH_MAGIC ? add2(y[i], minus_magic) : make_float2(__int2float_rn(__float_as_int(y[i].x)), __int2float_rn(__float_as_int(y[i].y)));
+#pragma unroll
+                for (int i = 0; i < 16; ++i) o[part * 16 + i] = fma2(beta2, y[i], o[part * 16 + i]);
+                if (part + 2 < PARTS) {
+                    reg_fence16(y);
+                    tmem_ld32_async(t_acc + b * 128 + (part + 2) * 32, y);
+                }
             }
-            TRACE(1);
-            tc_fence_after();
-            float2 a0[16], a1[16];
-            tmem_ld32_async(t_acc + b * 128, a0);
-            tmem_ld32_async(t_acc + b * 128 + 32, a1);
-            tmem_wait_ld();
-            reg_fence16(a0);
-            reg_fence16(a1);
-            tc_fence_before();
-            mbar_arrive(&sm.acc_free[b]);  // P.V(t + 2) may overwrite the accumulator
-            TRACE(2);
-            if (__all_sync(0xffffffffu, alpha == 1.0f))
-                flush_tile(std::false_type{}, a0, a1, alpha, beta);
-            else
-                flush_tile(std::true_type{}, a0, a1, alpha, beta);
+            if (FLUSH_MAGIC) {
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&sm.acc_free[b]);  // P.V(t + 2) may add to the accumulator again
+            }
             TRACE(3);
+            EVENT(5, t);
         }
         TRACE_END(2);
 
@@ -460,19 +607,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     }
                     const float p = ex2(__int2float_rn(dot) * ((sq * sk[key / KEY_TILE]) * scale_log2) - m) * 255.0f;
                     const float2 p2 = make_float2(p, p);
-                    const float2* v_row = reinterpret_cast<const float2*>(outlier_rows + (size_t(head) * n_outliers + i) * HEAD_DIM + half * 64);
+                    const float2* v_row = reinterpret_cast<const float2*>(outlier_rows + (size_t(head) * n_outliers + i) * HEAD_DIM + half * FLUSH_CHANNELS);
 #pragma unroll
-                    for (int j = 0; j < HEAD_DIM / 4; ++j) o[j] = fma2(p2, v_row[j], o[j]);
+                    for (int j = 0; j < FLUSH_CHANNELS / 2; ++j) o[j] = fma2(p2, v_row[j], o[j]);
                 }
             }
         }
 
         if (ok && q_row < n_queries) {
             const float inv = 1.0f / den;
-            __nv_bfloat16* dst = out + out_layout.offset(head, q_row) + half * 64;
-            const float* vs = v_scale + head * HEAD_DIM + half * 64;
+            __nv_bfloat16* dst = out + out_layout.offset(head, q_row) + half * FLUSH_CHANNELS;
+            const float* vs = v_scale + head * HEAD_DIM + half * FLUSH_CHANNELS;
 #pragma unroll
-            for (int chunk = 0; chunk < HEAD_DIM / 16; ++chunk) {
+            for (int chunk = 0; chunk < FLUSH_CHANNELS / 8; ++chunk) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -488,7 +635,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 
     tc_fence_before();
     __syncthreads();
-    if (warp == MMA_WARP) {
+    if (warp == SERVICE_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLUMNS);
     }
@@ -582,7 +729,7 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
                 return unica_check_launch("attention_int8 (shared memory size)");
             cudaFuncAttributes attributes;
             if (cudaFuncGetAttributes(&attributes, kernel) != cudaSuccess) return unica_check_launch("attention_int8 (attributes)");
-            if (attributes.numRegs * ATT_THREADS < 128 * (2 * SOFTMAX_REGISTERS + 2 * FLUSH_REGISTERS + SERVICE_REGISTERS))
+            if (attributes.numRegs * ATT_THREADS < 128 * (2 * SOFTMAX_REGISTERS + FLUSH_GROUPS * FLUSH_REGISTERS + SERVICE_REGISTERS))
                 return unica_fail(UNICA_B200_ERR_KERNEL, "attention_int8: this build holds fewer registers per block than its setmaxnreg split needs");
             if (device < MAX_DEVICES) ready[device].store(1, std::memory_order_release);
         }
@@ -597,10 +744,14 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
 }
 
 #ifdef UNICA_TRACE
-// Trace builds only: copies the per-phase cycle totals of block (0, 0) to `host_out` (4 x 8 long long) and clears them.
+// Trace builds only: copies the per-phase cycle totals of block (0, 0) to `host_out` (5 x 8 long long) and clears them.
+extern "C" int unica_b200_trace_events(long long* host_out) {  // 8 kinds x 16 tiles
+    if (cudaMemcpyFromSymbol(host_out, g_events, sizeof(long long) * 128) != cudaSuccess) return unica_check_launch("trace_events");
+    return UNICA_B200_OK;
+}
 extern "C" int unica_b200_trace_read(long long* host_out) {
-    if (cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 32) != cudaSuccess) return unica_check_launch("trace_read");
-    static const long long zeros[32] = {};
+    if (cudaMemcpyFromSymbol(host_out, g_trace, sizeof(long long) * 40) != cudaSuccess) return unica_check_launch("trace_read");
+    static const long long zeros[40] = {};
     if (cudaMemcpyToSymbol(g_trace, zeros, sizeof zeros) != cudaSuccess) return unica_check_launch("trace_read");
     return UNICA_B200_OK;
 }

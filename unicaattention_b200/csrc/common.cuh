@@ -108,11 +108,42 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
 
 // Waits for the phase of parity `parity`.  abort_flag: a word in shared memory any thread of the block sets when it
 // gave up; everyone else then stops waiting at once.  Returns false when the wait was abandoned.
+// A waiting warp shares its scheduler with computing warps and every instruction of its loop takes an issue slot from
+// them (the probe itself returns within a few dozen cycles when the phase has not completed), so after a failed probe
+// the warp sleeps for WAIT_SLEEP_NS before the next one, and the loop is the probe, the sleep, a counter and a branch,
+// written in PTX so that nothing else gets into it; the abort word and the clock are looked at once in WAIT_PROBES
+// probes.
+#ifndef UNICA_WAIT_SLEEP_NS
+#define UNICA_WAIT_SLEEP_NS 64
+#endif
+constexpr unsigned WAIT_PROBES = 2048, WAIT_SLEEP_NS = UNICA_WAIT_SLEEP_NS;
+__device__ __forceinline__ bool mbar_probe_many(uint64_t* bar, int parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 left;\n\t"
+        "mov.u32 left, %3;\n"
+        "UNICA_WAIT_AGAIN:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra UNICA_WAIT_DONE;\n\t"
+        "nanosleep.u32 %4;\n\t"
+        "sub.u32 left, left, 1;\n\t"
+        "setp.ne.u32 q, left, 0;\n\t"
+        "@q bra UNICA_WAIT_AGAIN;\n"
+        "UNICA_WAIT_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "n"(WAIT_PROBES), "n"(WAIT_SLEEP_NS)
+        : "memory");
+    return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_try(bar, parity)) return true;
+    if (mbar_probe_many(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
-        if (mbar_try(bar, parity)) return true;
+        if (mbar_probe_many(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - start > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
@@ -120,6 +151,77 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile in
             return false;
         }
     }
+}
+
+// Two barriers at once: both probes are in flight together, so a lone thread pays one probe latency (some 250 cycles)
+// instead of two.  parity_b < 0: there is no second barrier.
+__device__ __forceinline__ bool mbar_probe_many2(uint64_t* bar_a, int parity_a, uint64_t* bar_b, int parity_b) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q, r;\n\t"
+        ".reg .u32 left;\n\t"
+        "mov.u32 left, %5;\n"
+        "UNICA_WAIT2_AGAIN:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+        "and.pred r, p, q;\n\t"
+        "@r bra UNICA_WAIT2_DONE;\n\t"
+        "nanosleep.u32 %6;\n\t"
+        "sub.u32 left, left, 1;\n\t"
+        "setp.ne.u32 q, left, 0;\n\t"
+        "@q bra UNICA_WAIT2_AGAIN;\n"
+        "UNICA_WAIT2_DONE:\n\t"
+        "selp.u32 %0, 1, 0, r;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b), "n"(WAIT_PROBES), "n"(WAIT_SLEEP_NS)
+        : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait2(uint64_t* bar_a, int parity_a, uint64_t* bar_b, int parity_b, volatile int* abort_flag, int* status,
+                                           int code) {
+    if (parity_b < 0) return mbar_wait(bar_a, parity_a, abort_flag, status, code);
+    if (mbar_probe_many2(bar_a, parity_a, bar_b, parity_b)) return true;
+    const long long start = clock64();
+    while (true) {
+        if (mbar_probe_many2(bar_a, parity_a, bar_b, parity_b)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - start > WAIT_LIMIT_CYCLES) {
+            *abort_flag = 1;
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+// A word in shared memory that one thread of the block advances and others wait for.  Looking at a word costs a waiting
+// warp an ordinary shared-memory load (some 30 cycles), a tenth of an mbarrier probe, so where the event is first seen by
+// a thread that has to watch it anyway (the completion of tcgen05.mma by the thread that issued them), that thread passes
+// it on through such a word.  Release / acquire at block scope; bounded like every other wait here.
+__device__ __forceinline__ void flag_publish(int* flag, int value) {
+    asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_u32(flag)), "r"(value) : "memory");
+}
+__device__ __forceinline__ bool flag_wait(const int* flag, int at_least, volatile int* abort_flag, int* status, int code) {
+    long long start = 0;
+    for (int looks = 1;; ++looks) {
+        int value;
+        asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(value) : "r"(smem_u32(flag)) : "memory");
+        if (value >= at_least) return true;
+        if (looks % 256 == 0) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (start == 0) start = now;
+            if (now - start > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool flag_wait_warp(const int* flag, int at_least, volatile int* abort_flag, int* status, int code) {
+    return __all_sync(0xffffffffu, flag_wait(flag, at_least, abort_flag, status, code));
 }
 
 // The same for a whole warp: every lane waits, and all get the same answer.  The vote also reconverges the warp, which
