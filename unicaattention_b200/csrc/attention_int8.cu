@@ -1,25 +1,28 @@
 // The accurate mode's flash-attention loop on tcgen05 (replaces the reference's attention_int8pv_tma, csrc/flash.cu:806-959).
 //
-// One block = one tile of 128 query rows of one head, one block per SM, 20 warps in five warpgroups with three kinds of
+// One block = one tile of 128 query rows of one head, one block per SM, 16 warps in four warpgroups with three kinds of
 // work (a thread of a computing warpgroup owns one query row = one tensor-memory lane, so row maxima and sums need no
 // shuffles):
 //
-//   softmax A, B   key tiles t = 0, 2, 4 .. and 1, 3, 5 ..: the scores S(t) of tensor memory become the bytes
-//                  P^(t) = rint(255 * 2^(x - tile max)) of the A-operand image in shared memory.  They carry nothing from
-//                  tile to tile: the tile maximum and the row sum go to the flush threads through shared memory.
-//   flush          out = out * alpha + beta * float(acc(t)) for every key tile t, the row's 128 outputs in registers
-//                  (-DUNICA_FLUSH_GROUPS=2: two warpgroups with 64 channels each); they own the running exponent and the
-//                  denominator, and write the result.
-//   service        four warps, one elected thread each: two (one per key-tile parity) copy K8 / V8 tiles (contiguous 8 KB
-//                  images written by the quantizers) into a ring of shared-memory stages with bulk TMA copies and issue the
-//                  scores, two issue P.V:
+//   softmax A, B   key tiles t = 0, 2, 4 .. and 1, 3, 5 ..: the scores S(t) of tensor memory, read once into registers,
+//                  become the bytes P^(t) = rint(255 * 2^(x - tile max)) of the A-operand image in shared memory; the tile
+//                  maximum and the row sum go to the flush threads through shared memory.  They carry nothing from tile to
+//                  tile.
+//   flush          out = out * alpha + beta * float(acc(t)) for every key tile t, the row's 128 outputs in registers;
+//                  they own the running exponent and the denominator, and write the result.
+//   service        four warps, one elected thread each, two per key-tile parity: one issues the scores, one issues P.V and
+//                  copies K8 / V8 tiles (contiguous 8 KB images written by the quantizers, bulk TMA) into a ring of
+//                  shared-memory stages:
 //
 //   S(t)   = Q8 . K8(t)^T      kind::i8 s8 x s8 -> s32, 128 x 64, 4 instructions of K = 32, a ring of 4 buffers
 //   acc(t) = P^(t) . V8(t)     kind::i8 u8 x s8 -> s32, 128 x 128, 2 instructions of K = 32, two accumulators (t even / odd)
 //
-// Two softmax warpgroups on alternate key tiles keep two warps per scheduler on the exponential unit, the flush runs
-// beside them on the ALU and FMA pipes, and neither waits for the other: the scores of tile t + 4 are issued as soon as
-// tile t's are consumed, P.V(t) as soon as P^(t) is delivered and the flush of tile t - 2 has read its accumulator.
+// What was measured on the way here (B200): the exponentials of two softmax warps per scheduler alone take 567 cycles
+// per 128 x 64 tile and overlap with a flush warp's conversions almost freely, the tensor pipe alone 476; what decides
+// the kernel's speed is the chain of hand-overs between the roles.  A lone thread pays some 250 cycles for an mbarrier
+// probe, so MMA issue is dealt out to four threads, a thread waits for two barriers with both probes in flight, and the
+// completion of tcgen05.mma is passed on by the issuing thread through words in shared memory that a waiting warp
+// reads in 30 cycles.
 //
 // Numerics (bench/emulate.py:298-369 with the accurate contract): scores in the log2 domain, c = (q_scale * k_scale) *
 // log2(e) / sqrt(d); P^ as u8 against the tile's own maximum; the denominator sums the rounded P^ (per channel) or
@@ -36,25 +39,10 @@
 
 namespace unica {
 
-#ifndef UNICA_FLUSH_GROUPS
-#define UNICA_FLUSH_GROUPS 1
-#endif
-constexpr int FLUSH_GROUPS = UNICA_FLUSH_GROUPS;  // flush warpgroups: 1 (a thread owns the row's 128 outputs) or 2 (64 each)
-constexpr int FLUSH_CHANNELS = HEAD_DIM / FLUSH_GROUPS;
-#ifndef UNICA_FLUSH_MAGIC
-#define UNICA_FLUSH_MAGIC 0
-#endif
-// 1: the accumulators start at MAGIC_BITS like the score buffers (P.V always accumulates, the flush threads put the start
-// value back after reading) and the flush reads floats MAGIC + acc: a packed subtraction on the FMA pipe instead of an
-// int -> float conversion on the ALU pipe per value.  |acc| <= 64 * 255 * 127 < 2^21, so the float is exact.
-constexpr bool FLUSH_MAGIC = UNICA_FLUSH_MAGIC != 0;
-constexpr bool SINGLE_PASS = FLUSH_GROUPS == 1;  // the softmax keeps a row's 64 scores in registers (it has them with one flush warpgroup)
-constexpr int FLUSH_WARP = 8, SERVICE_WARP = FLUSH_WARP + 4 * FLUSH_GROUPS;
-constexpr int ATT_WARPS = SERVICE_WARP + 4, ATT_THREADS = ATT_WARPS * 32;
-// registers per thread after setmaxnreg; the block is launched with ATT_THREADS x LAUNCH_REGISTERS <= 65536
-constexpr int LAUNCH_REGISTERS = FLUSH_GROUPS == 1 ? 128 : 96;
-constexpr int SOFTMAX_REGISTERS = FLUSH_GROUPS == 1 ? 120 : 80, FLUSH_REGISTERS = FLUSH_GROUPS == 1 ? 232 : 144, SERVICE_REGISTERS = 32;
-static_assert(128 * (2 * SOFTMAX_REGISTERS + FLUSH_GROUPS * FLUSH_REGISTERS + SERVICE_REGISTERS) <= ATT_THREADS * LAUNCH_REGISTERS, "the split must fit the launch");
+constexpr int FLUSH_WARP = 8, SERVICE_WARP = 12, ATT_WARPS = 16, ATT_THREADS = ATT_WARPS * 32;
+// registers per thread after setmaxnreg; the block is launched with ATT_THREADS x LAUNCH_REGISTERS = 65536
+constexpr int LAUNCH_REGISTERS = 128, SOFTMAX_REGISTERS = 120, FLUSH_REGISTERS = 232, SERVICE_REGISTERS = 32;
+static_assert(128 * (2 * SOFTMAX_REGISTERS + FLUSH_REGISTERS + SERVICE_REGISTERS) <= ATT_THREADS * LAUNCH_REGISTERS, "the split must fit the launch");
 template <int REGISTERS>
 __device__ __forceinline__ void set_registers() {  // every warp of a warpgroup executes it
     if constexpr (REGISTERS > LAUNCH_REGISTERS)
@@ -90,12 +78,17 @@ struct __align__(128) AttSmem {
     int abort_flag;
 };
 
-// -DUNICA_TRACE: thread 0 of each role of block (0, 0) adds up the cycles it spends in each phase of its tile loop (the
-// reference has a TRACE build for the same purpose: csrc/legacy.cu, bench/timeline.py).  Rows of g_trace: softmax A,
-// softmax B, flush 0, P.V-issuing thread, scores-issuing thread.  The totals stay in registers until the end: tracing costs a clock read per phase.
+// -DUNICA_TRACE: thread 0 of each role of block (0, 0) adds up the cycles it spends in each phase of its tile loop and
+// notes when key tiles EVENT_FIRST .. + 15 passed from role to role (the reference has a TRACE build for the same
+// purpose: csrc/legacy.cu, bench/timeline.py).  Rows of g_trace: softmax A, softmax B, flush, P.V-issuing thread,
+// scores-issuing thread.  The totals stay in registers until the end: tracing costs a clock read per phase.
+#ifndef UNICA_SERVICE_SLEEP_NS
+#define UNICA_SERVICE_SLEEP_NS 0
+#endif
+constexpr unsigned SERVICE_SLEEP = UNICA_SERVICE_SLEEP_NS;  // the service threads pass events on: they do not sleep between probes
 #ifdef UNICA_TRACE
 __device__ long long g_trace[5][8];
-__device__ long long g_events[8][16];  // absolute clocks of events of key tiles EVENT_FIRST .. +15 in block (0, 0)
+__device__ long long g_events[8][16];
 constexpr int EVENT_FIRST = 64;
 #define EVENT(kind, tile) do { if (tracing && (tile) >= EVENT_FIRST && (tile) < EVENT_FIRST + 16) g_events[kind][(tile) - EVENT_FIRST] = clock64(); } while (0)
 #define TRACE_DECL(on) long long trace_t0 = clock64(), trace_sum[8] = {}; const bool tracing = blockIdx.x == 0 && blockIdx.y == 0 && (on)
@@ -122,6 +115,32 @@ constexpr int EVENT_FIRST = 64;
 constexpr uint32_t IDESC_QK = idesc_i8(true, QUERY_TILE, KEY_TILE);
 constexpr uint32_t IDESC_PV = idesc_i8(false, QUERY_TILE, HEAD_DIM);
 
+// One step of a row's sums: the reference exponent `m` and the factors of the tile whose maximum is `tile_max`.
+// `m` is the exponent the sums are kept at, not the running maximum: out = sum over tiles of 2^(tile max - m) * acc, the
+// same for the denominator, and the common factor cancels at the end.  The textbook form moves m to every new maximum
+// and multiplies out and den by alpha = 2^(m_old - m_new) each time; here m moves only when a tile maximum is more than
+// 2^REFERENCE_SLACK above it, so that multiplication all but disappears.  The difference is rounding only.
+__device__ __forceinline__ void reference_step(float& m, float tile_max, float& alpha, float& beta) {
+    const bool first = m == -INFINITY;
+    const float m_new = tile_max > m + REFERENCE_SLACK ? tile_max : m;
+    alpha = first ? 1.0f : ex2(m - m_new);
+    beta = ex2(tile_max - m_new);
+    m = m_new;
+}
+
+// 32 accumulator values (plain integers: every tile's P.V overwrites the accumulator) into 32 of a row's sums.
+__device__ __forceinline__ void flush32(float2 (&y)[16], float2* o, float alpha, float beta, bool rescale) {
+    const float2 alpha2 = make_float2(alpha, alpha), beta2 = make_float2(beta, beta);
+    if (rescale) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) o[i] = mul2(o[i], alpha2);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) y[i] = make_float2(__int2float_rn(__float_as_int(y[i].x)), __int2float_rn(__float_as_int(y[i].y)));
+#pragma unroll
+    for (int i = 0; i < 16; ++i) o[i] = fma2(beta2, y[i], o[i]);
+}
+
 template <bool V_TOKEN, bool OUTLIERS>
 __global__ void __launch_bounds__(ATT_THREADS, 1)
     attention_int8_kernel(const int8_t* __restrict__ q8, const float* __restrict__ q_scale, const int8_t* __restrict__ k8,
@@ -147,10 +166,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_init(&sm.kv_empty[s], 1);
         }
         mbar_init(&sm.s_ready, 256);
-        for (int b = 0; b < S_RING; ++b) mbar_init(&sm.s_full[b], 1);
+        for (int b = 0; b < S_RING; ++b) mbar_init(&sm.s_full[b], 1), sm.s_done[b] = 0;
         for (int b = 0; b < ST_RING; ++b) mbar_init(&sm.soft_done[b], 128);
-        for (int b = 0; b < 2; ++b) mbar_init(&sm.acc_free[b], 128 * FLUSH_GROUPS), sm.acc_done[b] = 0;
-        for (int b = 0; b < S_RING; ++b) sm.s_done[b] = 0;
+        for (int b = 0; b < 2; ++b) mbar_init(&sm.acc_free[b], 128), sm.acc_done[b] = 0;
         for (int i = 0; i < 4; ++i) mbar_init(&sm.drain[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -175,12 +193,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         // last tile but one) has handed the scores buffer back.
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
             const uint64_t q_desc0 = smem_desc(smem_u32(sm.q), QUERY_TILE * 16, 128), k_desc0 = smem_desc(smem_u32(sm.k[0]), KEY_TILE * 16, 128);
-            bool ok = mbar_wait2(&sm.q_full, 0, &sm.s_ready, 0, abort_flag, status, STATUS_WAIT_TILE);  // s_ready: the score buffers hold their start value
+            bool ok = mbar_wait2<SERVICE_SLEEP>(&sm.q_full, 0, &sm.s_ready, 0, abort_flag, status, STATUS_WAIT_TILE);  // s_ready: the score buffers hold their start value
             TRACE_DECL(true);
             for (int n = parity, stage = parity, phase = 0; ok && n < k_tiles; n += 2) {
                 const int buf = n % S_RING;
                 TRACE(7);
-                ok = mbar_wait2(&sm.kv_full[stage], phase, &sm.soft_done[(n - S_RING) & (ST_RING - 1)], n >= S_RING ? ((n - S_RING) / ST_RING) & 1 : -1,
+                ok = mbar_wait2<SERVICE_SLEEP>(&sm.kv_full[stage], phase, &sm.soft_done[(n - S_RING) & (ST_RING - 1)], n >= S_RING ? ((n - S_RING) / ST_RING) & 1 : -1,
                                 abort_flag, status, STATUS_WAIT_TILE);
                 TRACE(0);
                 if (!ok) break;
@@ -194,7 +212,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 EVENT(6, n);
                 // the thread watches its own instructions complete and tells the softmax threads through a word they can
                 // look at cheaply
-                ok = mbar_wait(&sm.s_full[buf], (n / S_RING) & 1, abort_flag, status, STATUS_WAIT_SCORES);
+                ok = mbar_wait<SERVICE_SLEEP>(&sm.s_full[buf], (n / S_RING) & 1, abort_flag, status, STATUS_WAIT_SCORES);
                 if (!ok) break;
                 tc_fence_before();
                 flag_publish(&sm.s_done[buf], n + 1);
@@ -241,9 +259,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             const uint64_t p_desc0 = smem_desc(smem_u32(sm.p[0]), QUERY_TILE * 16, 128), v_desc0 = smem_desc(smem_u32(sm.v[0]), HEAD_DIM * 16, 128);
             for (int t = parity, stage = parity, phase = 0; ok && t < k_tiles; t += 2) {
                 TRACE(7);
-                // acc_free: with start values (FLUSH_MAGIC) phase 0 is the flush threads' first fill; without, the flush of tile t - 2
-                const int free_parity = FLUSH_MAGIC ? (t >> 1) & 1 : t >= 2 ? ((t - 2) >> 1) & 1 : -1;
-                ok = mbar_wait2(&sm.soft_done[t % ST_RING], (t / ST_RING) & 1, &sm.acc_free[b], free_parity, abort_flag, status, STATUS_WAIT_P);
+                const int free_parity = t >= 2 ? ((t - 2) >> 1) & 1 : -1;  // the flushes of tile t - 2 have read the accumulator
+                ok = mbar_wait2<SERVICE_SLEEP>(&sm.soft_done[t % ST_RING], (t / ST_RING) & 1, &sm.acc_free[b], free_parity, abort_flag, status, STATUS_WAIT_P);
                 TRACE(3);
                 if (!ok) break;
                 tc_fence_after();
@@ -252,12 +269,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
 #pragma unroll
                 for (int ks = 0; ks < KEY_TILE / 32; ++ks)
                     mma_i8_ss(tmem + COL_ACC + b * 128, p_desc + ks * (2 * QUERY_TILE * 16 / 16), v_desc + ks * (2 * HEAD_DIM * 16 / 16), IDESC_PV,
-                              FLUSH_MAGIC || ks > 0);  // without the start value the first instruction of a tile overwrites the accumulator
+                              ks > 0);  // the first instruction of a tile overwrites the accumulator
                 mma_commit(&sm.kv_empty[stage]);
                 TRACE(4);
                 EVENT(2, t);
                 // P.V(t) complete: the flush threads are told through a word they can look at cheaply, and the stage is free
-                ok = mbar_wait(&sm.kv_empty[stage], phase, abort_flag, status, STATUS_WAIT_STAGE);
+                ok = mbar_wait<SERVICE_SLEEP>(&sm.kv_empty[stage], phase, abort_flag, status, STATUS_WAIT_STAGE);
                 if (!ok) break;
                 tc_fence_before();
                 flag_publish(&sm.acc_done[b], t + 1);
@@ -325,35 +342,59 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_arrive(&sm.soft_done[record]);
             return true;
 #endif
-            const float2 c2 = make_float2(c, c), minus_magic = make_float2(-MAGIC, -MAGIC);
+            const float2 c2 = make_float2(c, c), minus_magic = make_float2(-MAGIC, -MAGIC), plus_magic = make_float2(MAGIC, MAGIC);
             const float4* log_s4 = reinterpret_cast<const float4*>(sm.tok[stage]);
             const float4* inv_s4 = reinterpret_cast<const float4*>(sm.tok[stage] + KEY_TILE);
-            // Sixteen keys: P^ = rint(255 * 2^(score * c - tile max)) into the A-operand image, written stage by stage
-            // (exponents, exponentials, rounding, packing) so that every instruction has fifteen independent ones around
-            // it: the exponential unit takes a warp every 8 cycles and answers after some twenty, and a thread that asks
-            // for one result at a time waits for each.  Per channel the float read back is MAGIC + score, so the exponent is
+            uint8_t* p_row = sm.p[stage] + row * 16;  // the P^ ring runs with the stages
+            // The row's 64 scores, read once and kept in registers; the buffer goes back to its start value for S(t + 4)
+            // at once (the stores run while the arithmetic does; they are waited for at the hand-over).
+            float2 x[KEY_TILE / 16][8];
+            tmem_ld64_sync(ts, reinterpret_cast<float2(&)[KEY_TILE / 2]>(x));
+            tmem_fill<KEY_TILE>(ts, magic);
+            float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int step = 0; step < KEY_TILE / 16; ++step) {
+                float2(&y)[8] = x[step];
+                if (V_TOKEN) {  // log2 s_j joins the scores before the maximum
+#pragma unroll
+                    for (int j = 0; j < 8; j += 2) {
+                        const float4 l = log_s4[step * 4 + j / 2];
+                        y[j] = fma2(add2(y[j], minus_magic), c2, make_float2(l.x, l.y));
+                        y[j + 1] = fma2(add2(y[j + 1], minus_magic), c2, make_float2(l.z, l.w));
+                    }
+                }
+                if (MASKED) {  // keys past the end: below every real score (|score| < 2^21)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (step * 16 + j >= valid) (j % 2 ? y[j / 2].y : y[j / 2].x) = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) top[j % 4] = max3(top[j % 4], y[j].x, y[j].y);
+            }
+            float tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
+            TRACE(1);
+            if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
+            // P^ = rint(255 * 2^(score * c - tile max)).  Per channel the float read back is MAGIC + score, so the exponent is
             // x * c + (offset - MAGIC * c) in ONE fused multiply-add; what the rounding of that constant loses (it is about
             // 2^11 in size) is put back exactly: `low` is the lost part, and the product p * 2^low happens inside the
             // multiply-add that rounds p to a byte.
-            float2 base2, k2;
-            const float2 plus_magic = make_float2(MAGIC, MAGIC);
-            uint8_t* p_row = sm.p[stage] + row * 16;  // the P^ ring runs with the stages
+            const float offset = LOG2_255 - tile_max;
+            float2 base2 = make_float2(offset, offset), k2 = make_float2(1.0f, 1.0f);
+            if (!V_TOKEN) {
+                const float a_hi = __fmul_rn(-MAGIC, c), a_lo = __fmaf_rn(-MAGIC, c, -a_hi);  // -MAGIC * c = a_hi + a_lo exactly
+                const float sum = __fadd_rn(a_hi, offset), bb = __fsub_rn(sum, a_hi);
+                const float low = __fadd_rn(__fadd_rn(__fsub_rn(a_hi, __fsub_rn(sum, bb)), __fsub_rn(offset, bb)), a_lo);  // a_hi + offset = sum + ..
+                const float k = __fmaf_rn(low, 0.693147181f, 1.0f);  // 2^low, |low| < 2^-12
+                base2 = make_float2(sum, sum), k2 = make_float2(k, k);
+            }
             unsigned isum[2] = {0, 0};
             float2 fsum = make_float2(0.0f, 0.0f);
-            auto constants = [&](float tile_max) {
-                const float offset = LOG2_255 - tile_max;
-                if (!V_TOKEN) {
-                    const float a_hi = __fmul_rn(-MAGIC, c), a_lo = __fmaf_rn(-MAGIC, c, -a_hi);  // -MAGIC * c = a_hi + a_lo exactly
-                    const float sum = __fadd_rn(a_hi, offset), bb = __fsub_rn(sum, a_hi);
-                    const float low = __fadd_rn(__fadd_rn(__fsub_rn(a_hi, __fsub_rn(sum, bb)), __fsub_rn(offset, bb)), a_lo);  // a_hi + offset = sum + ..
-                    const float k = __fmaf_rn(low, 0.693147181f, 1.0f);  // 2^low, |low| < 2^-12
-                    base2 = make_float2(sum, sum), k2 = make_float2(k, k);
-                } else {
-                    base2 = make_float2(offset, offset), k2 = make_float2(1.0f, 1.0f);
-                }
-            };
-            // y: per channel MAGIC + score; per token score * c + log2 s_j
-            auto sixteen_keys = [&](const float2 (&y)[8], int step) {
+#pragma unroll
+            for (int step = 0; step < KEY_TILE / 16; ++step) {
+                // Sixteen keys, written stage by stage (exponents, exponentials, rounding, packing) so that every
+                // instruction has fifteen independent ones around it: the exponential unit takes a warp every 8 cycles
+                // and answers after some twenty, and a thread that asks for one result at a time waits for each.
+                float2(&y)[8] = x[step];
                 float2 e[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) e[j] = V_TOKEN ? add2(y[j], base2) : fma2(y[j], c2, base2);
@@ -382,92 +423,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     if (!V_TOKEN) isum[i % 2] = __dp4a(w[i], 0x01010101u, isum[i % 2]);
                 }
                 *reinterpret_cast<uint4*>(p_row + step * (QUERY_TILE * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
-            };
-            // log2 s_j joins the scores of a per-token tile before the maximum; keys past the end go below every real score
-            auto prepare = [&](float2 (&y)[8], int step) {
-                if (V_TOKEN) {
-#pragma unroll
-                    for (int j = 0; j < 8; j += 2) {
-                        const float4 l = log_s4[step * 4 + j / 2];
-                        y[j] = fma2(add2(y[j], minus_magic), c2, make_float2(l.x, l.y));
-                        y[j + 1] = fma2(add2(y[j + 1], minus_magic), c2, make_float2(l.z, l.w));
-                    }
-                }
-                if (MASKED) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (step * 16 + j >= valid) (j % 2 ? y[j / 2].y : y[j / 2].x) = V_TOKEN ? -INFINITY : MAGIC - 4194303.0f;  // |score| < 2^21
-                }
-            };
-            float tile_max;
-            if constexpr (SINGLE_PASS) {
-                // The row's 64 scores, read once and kept in registers; the buffer goes back to its start value for
-                // S(t + 4) at once (the stores run while the arithmetic does; they are waited for at the hand-over).
-                float2 x[KEY_TILE / 16][8];
-                tmem_ld64_sync(ts, reinterpret_cast<float2(&)[KEY_TILE / 2]>(x));
-#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 2))  // measurement only (wrong results): what each synchronising step costs
-                tmem_fill<KEY_TILE>(ts, magic);
-#endif
-                float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                for (int step = 0; step < KEY_TILE / 16; ++step) {
-                    prepare(x[step], step);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) top[j % 4] = max3(top[j % 4], x[step][j].x, x[step][j].y);
-                }
-                tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-                TRACE(1);
-                if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
-                constants(tile_max);
-#pragma unroll
-                for (int step = 0; step < KEY_TILE / 16; ++step) sixteen_keys(x[step], step);
-            } else {
-                // Two passes over the scores, 16 at a time (they would not fit next to the rest): the tile maximum, then
-                // the exponentials; the next 16 are on their way while 16 are used.
-                float2 x[2][8];
-                float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                tmem_ld16_async(ts, x[0]);
-                tmem_ld16_async(ts + 16, x[1]);
-#pragma unroll
-                for (int step = 0; step < KEY_TILE / 16; ++step) {
-                    float2(&y)[8] = x[step % 2];
-                    if (step % 2 == 0) tmem_wait_ld();  // both loads in flight
-                    reg_fence8(y);
-                    prepare(y, step);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) top[j % 4] = max3(top[j % 4], y[j].x, y[j].y);
-                    reg_fence8(y);
-                    tmem_ld16_async(ts + ((step + 2) % 4) * 16, y);  // steps 2, 3 fetch the first chunks of the second pass
-                }
-                tile_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3]));
-                TRACE(1);
-                if (!V_TOKEN) tile_max = (tile_max - MAGIC) * c;
-                constants(tile_max);
-#pragma unroll
-                for (int step = 0; step < KEY_TILE / 16; ++step) {
-                    float2(&y)[8] = x[step % 2];
-                    if (step % 2 == 0) tmem_wait_ld();
-                    reg_fence8(y);
-                    if (step == 2) tmem_fill<KEY_TILE>(ts, magic);  // every score has been read: the buffer goes back to its start value for S(t + 4)
-                    if (V_TOKEN) prepare(y, step);  // the score with log2 s_j, once more
-                    sixteen_keys(y, step);
-                    if (step + 2 < KEY_TILE / 16) {
-                        reg_fence8(y);
-                        tmem_ld16_async(ts + (step + 2) * 16, y);
-                    }
-                }
             }
             TRACE(2);
             sm.st[record][row] = make_float2(tile_max, V_TOKEN ? fsum.x + fsum.y : __uint2float_rn(isum[0] + isum[1]));
-#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 2))
             tmem_wait_st();
-#endif
-#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 4))
             tc_fence_before();
-#endif
-#if !(defined(UNICA_SKIP) && (UNICA_SKIP & 1))
             fence_proxy_async();
-#endif
             mbar_arrive(&sm.soft_done[record]);  // P^(t) and its record delivered, the scores buffer back at its start value
             TRACE(3);
             EVENT(1, t);
@@ -491,27 +452,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     } else {
         // ------------------------------------------------------------------------------------------------ flush
         set_registers<FLUSH_REGISTERS>();
-        const int half = (warp - FLUSH_WARP) / 4;  // output channels FLUSH_CHANNELS * half ..
-        const uint32_t t_acc = tmem + lane_base + COL_ACC + half * FLUSH_CHANNELS;
+        const uint32_t t_acc = tmem + lane_base + COL_ACC;
         float m = -INFINITY, den = 0.0f;
-        float2 o[FLUSH_CHANNELS / 2];
+        float2 o[HEAD_DIM / 2];
 #pragma unroll
-        for (int i = 0; i < FLUSH_CHANNELS / 2; ++i) o[i] = make_float2(0.0f, 0.0f);
-        uint32_t magic[FILL_BLOCK];
-        const float2 minus_magic = make_float2(-MAGIC, -MAGIC);
-        if (FLUSH_MAGIC) {
-            fill_block_init(magic, MAGIC_BITS);
-            tmem_fill<FLUSH_CHANNELS>(t_acc, magic);
-            tmem_fill<FLUSH_CHANNELS>(t_acc + 128, magic);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&sm.acc_free[0]);
-            mbar_arrive(&sm.acc_free[1]);
-        }
+        for (int i = 0; i < HEAD_DIM / 2; ++i) o[i] = make_float2(0.0f, 0.0f);
 
         bool ok = true;
-        TRACE_DECL(row == 0 && half == 0);
-        constexpr int PARTS = FLUSH_CHANNELS / 32;
+        TRACE_DECL(row == 0);
         for (int t = 0; ok && t < k_tiles; ++t) {
             const int b = t & 1;
             TRACE(7);
@@ -521,9 +469,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 break;
             }
             tc_fence_after();
-            float2 a[2][16];  // 32 channels each, one pair in flight while the other is used
+            // 32 channels per load, three loads out at once and the fourth as soon as the first values are used: the
+            // accumulator is handed back a few hundred cycles after it was seen, long before the arithmetic is done
+            float2 a[3][16];
             tmem_ld32_async(t_acc + b * 128, a[0]);
             tmem_ld32_async(t_acc + b * 128 + 32, a[1]);
+            tmem_ld32_async(t_acc + b * 128 + 64, a[2]);
             TRACE(1);
             EVENT(3, t);
 #if defined(UNICA_STUB) && (UNICA_STUB & 2)  // measurement only
@@ -532,53 +483,26 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             mbar_arrive(&sm.acc_free[b]);
             continue;
 #endif
-            // `m` is the exponent the row's sums are kept at, not the running maximum: out = sum over tiles of
-            // 2^(tile max - m) * acc, the same for the denominator, and the common factor cancels at the end.  The
-            // textbook form moves m to every new maximum and multiplies out and den by alpha = 2^(m_old - m_new) each
-            // time; here m moves only when a tile maximum is more than 2^REFERENCE_SLACK above it, so that
-            // multiplication all but disappears.  The difference is rounding only.
             const float2 record = sm.st[t % ST_RING][row];  // tile maximum, row sum
-            const bool first = m == -INFINITY;
-            const float m_new = record.x > m + REFERENCE_SLACK ? record.x : m;
-            const float alpha = first ? 1.0f : ex2(m - m_new), beta = ex2(record.x - m_new);
-            m = m_new;
+            float alpha, beta;
+            reference_step(m, record.x, alpha, beta);
             den = den * alpha + record.y * beta;
-            const float2 alpha2 = make_float2(alpha, alpha), beta2 = make_float2(beta, beta);
             const bool rescale = !__all_sync(0xffffffffu, alpha == 1.0f);
-#pragma unroll
-            for (int part = 0; part < PARTS; ++part) {  // 32 channels at a time
-                float2(&y)[16] = a[part % 2];
-                if (part % 2 == 0) {
-                    tmem_wait_ld();  // both loads in flight
-                    if (part + 2 >= PARTS) {  // the accumulator has been read
-                        if (!FLUSH_MAGIC) {  // P.V(t + 2) may overwrite it
-                            tc_fence_before();
-                            mbar_arrive(&sm.acc_free[b]);
-                            EVENT(4, t);
-                        }
-                    }
-                }
-                reg_fence16(y);
-                if (FLUSH_MAGIC) tmem_fill<32>(t_acc + b * 128 + part * 32, magic);  // read: the start value goes back in
-                if (rescale) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) o[part * 16 + i] = mul2(o[part * 16 + i], alpha2);
-                }
-#pragma unroll
-                for (int i = 0; i < 16; ++i)  // without the start value the accumulator is overwritten by every tile's P.V: plain integers
-                    y[i] = FLUSH_MAGIC ? add2(y[i], minus_magic) : make_float2(__int2float_rn(__float_as_int(y[i].x)), __int2float_rn(__float_as_int(y[i].y)));
-#pragma unroll
-                for (int i = 0; i < 16; ++i) o[part * 16 + i] = fma2(beta2, y[i], o[part * 16 + i]);
-                if (part + 2 < PARTS) {
-                    reg_fence16(y);
-                    tmem_ld32_async(t_acc + b * 128 + (part + 2) * 32, y);
-                }
-            }
-            if (FLUSH_MAGIC) {
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&sm.acc_free[b]);  // P.V(t + 2) may add to the accumulator again
-            }
+            tmem_wait_ld();
+            reg_fence16(a[0]);
+            reg_fence16(a[1]);
+            reg_fence16(a[2]);
+            flush32(a[0], o, alpha, beta, rescale);
+            reg_fence16(a[0]);
+            tmem_ld32_async(t_acc + b * 128 + 96, a[0]);
+            tmem_wait_ld();
+            reg_fence16(a[0]);
+            tc_fence_before();
+            mbar_arrive(&sm.acc_free[b]);  // the accumulator has been read: P.V(t + 2) may overwrite it
+            EVENT(4, t);
+            flush32(a[1], o + 16, alpha, beta, rescale);
+            flush32(a[2], o + 32, alpha, beta, rescale);
+            flush32(a[0], o + 48, alpha, beta, rescale);
             TRACE(3);
             EVENT(5, t);
         }
@@ -607,19 +531,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     }
                     const float p = ex2(__int2float_rn(dot) * ((sq * sk[key / KEY_TILE]) * scale_log2) - m) * 255.0f;
                     const float2 p2 = make_float2(p, p);
-                    const float2* v_row = reinterpret_cast<const float2*>(outlier_rows + (size_t(head) * n_outliers + i) * HEAD_DIM + half * FLUSH_CHANNELS);
+                    const float2* v_row = reinterpret_cast<const float2*>(outlier_rows + (size_t(head) * n_outliers + i) * HEAD_DIM);
 #pragma unroll
-                    for (int j = 0; j < FLUSH_CHANNELS / 2; ++j) o[j] = fma2(p2, v_row[j], o[j]);
+                    for (int j = 0; j < HEAD_DIM / 2; ++j) o[j] = fma2(p2, v_row[j], o[j]);
                 }
             }
         }
 
         if (ok && q_row < n_queries) {
             const float inv = 1.0f / den;
-            __nv_bfloat16* dst = out + out_layout.offset(head, q_row) + half * FLUSH_CHANNELS;
-            const float* vs = v_scale + head * HEAD_DIM + half * FLUSH_CHANNELS;
+            __nv_bfloat16* dst = out + out_layout.offset(head, q_row);
+            const float* vs = v_scale + head * HEAD_DIM;
 #pragma unroll
-            for (int chunk = 0; chunk < FLUSH_CHANNELS / 8; ++chunk) {
+            for (int chunk = 0; chunk < HEAD_DIM / 8; ++chunk) {
                 uint32_t w[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -729,7 +653,7 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
                 return unica_check_launch("attention_int8 (shared memory size)");
             cudaFuncAttributes attributes;
             if (cudaFuncGetAttributes(&attributes, kernel) != cudaSuccess) return unica_check_launch("attention_int8 (attributes)");
-            if (attributes.numRegs * ATT_THREADS < 128 * (2 * SOFTMAX_REGISTERS + FLUSH_GROUPS * FLUSH_REGISTERS + SERVICE_REGISTERS))
+            if (attributes.numRegs * ATT_THREADS < 128 * (2 * SOFTMAX_REGISTERS + FLUSH_REGISTERS + SERVICE_REGISTERS))
                 return unica_fail(UNICA_B200_ERR_KERNEL, "attention_int8: this build holds fewer registers per block than its setmaxnreg split needs");
             if (device < MAX_DEVICES) ready[device].store(1, std::memory_order_release);
         }

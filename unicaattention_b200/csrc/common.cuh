@@ -117,6 +117,7 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
 #define UNICA_WAIT_SLEEP_NS 64
 #endif
 constexpr unsigned WAIT_PROBES = 2048, WAIT_SLEEP_NS = UNICA_WAIT_SLEEP_NS;
+template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_probe_many(uint64_t* bar, int parity) {
     uint32_t done;
     asm volatile(
@@ -135,15 +136,17 @@ __device__ __forceinline__ bool mbar_probe_many(uint64_t* bar, int parity) {
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity), "n"(WAIT_PROBES), "n"(WAIT_SLEEP_NS)
+        : "r"(smem_u32(bar)), "r"(parity), "n"(WAIT_PROBES), "n"(SLEEP_NS)
         : "memory");
     return done != 0;
 }
+// SLEEP_NS 0: for the threads that pass events on (their wake-up time is on everybody's critical path)
+template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_probe_many(bar, parity)) return true;
+    if (mbar_probe_many<SLEEP_NS>(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
-        if (mbar_probe_many(bar, parity)) return true;
+        if (mbar_probe_many<SLEEP_NS>(bar, parity)) return true;
         if (*abort_flag) return false;
         if (clock64() - start > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
@@ -155,6 +158,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile in
 
 // Two barriers at once: both probes are in flight together, so a lone thread pays one probe latency (some 250 cycles)
 // instead of two.  parity_b < 0: there is no second barrier.
+template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_probe_many2(uint64_t* bar_a, int parity_a, uint64_t* bar_b, int parity_b) {
     uint32_t done;
     asm volatile(
@@ -175,17 +179,18 @@ __device__ __forceinline__ bool mbar_probe_many2(uint64_t* bar_a, int parity_a, 
         "selp.u32 %0, 1, 0, r;\n\t"
         "}"
         : "=r"(done)
-        : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b), "n"(WAIT_PROBES), "n"(WAIT_SLEEP_NS)
+        : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b), "n"(WAIT_PROBES), "n"(SLEEP_NS)
         : "memory");
     return done != 0;
 }
+template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait2(uint64_t* bar_a, int parity_a, uint64_t* bar_b, int parity_b, volatile int* abort_flag, int* status,
                                            int code) {
-    if (parity_b < 0) return mbar_wait(bar_a, parity_a, abort_flag, status, code);
-    if (mbar_probe_many2(bar_a, parity_a, bar_b, parity_b)) return true;
+    if (parity_b < 0) return mbar_wait<SLEEP_NS>(bar_a, parity_a, abort_flag, status, code);
+    if (mbar_probe_many2<SLEEP_NS>(bar_a, parity_a, bar_b, parity_b)) return true;
     const long long start = clock64();
     while (true) {
-        if (mbar_probe_many2(bar_a, parity_a, bar_b, parity_b)) return true;
+        if (mbar_probe_many2<SLEEP_NS>(bar_a, parity_a, bar_b, parity_b)) return true;
         if (*abort_flag) return false;
         if (clock64() - start > WAIT_LIMIT_CYCLES) {
             *abort_flag = 1;
