@@ -22,7 +22,7 @@
 // and V's as the quantizers laid them out, P's as the computing threads wrote them a moment earlier.
 //
 // Tensor memory per query tile (256 columns): S 0..63 | O 64..207 | SF of Q 208..215, K 216..219, P 220..223, V 224..231.
-// All waits are bounded (common.cuh).
+// All waits are bounded (common.cuh); none sleeps between probes: every hand-over here is on the loop's critical path.
 #include <cuda_fp8.h>
 
 #include "capi.h"
@@ -175,11 +175,11 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
             for (int t = 0; t < k_tiles; ++t) {
                 const int s = t % F4_STAGES, use = t / F4_STAGES;
                 const size_t tile = size_t(head) * k_tiles + t;
-                if (use > 0 && !mbar_wait(&sm.k_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) break;
+                if (use > 0 && !mbar_wait<0>(&sm.k_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) break;
                 mbar_expect_tx(&sm.k_full[s], K4_BYTES + SFK_BYTES);
                 bulk_load(sm.k[s], k4 + tile * K4_BYTES, K4_BYTES, &sm.k_full[s]);
                 bulk_load(sm.sfk[s], sfk + tile * (SFK_BYTES / 4), SFK_BYTES, &sm.k_full[s]);
-                if (use > 0 && !mbar_wait(&sm.v_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) {
+                if (use > 0 && !mbar_wait<0>(&sm.v_empty[s], (use - 1) & 1, abort_flag, status, STATUS_WAIT_STAGE)) {
                     issued = t + 1;
                     break;
                 }
@@ -192,8 +192,8 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
             if (*abort_flag) {
                 int never = 0;
                 for (int t = max(0, issued - F4_STAGES); t < issued; ++t)
-                    mbar_wait(&sm.k_full[t % F4_STAGES], (t / F4_STAGES) & 1, &never, nullptr, 0);
-                mbar_wait(&sm.q_full, 0, &never, nullptr, 0);
+                    mbar_wait<0>(&sm.k_full[t % F4_STAGES], (t / F4_STAGES) & 1, &never, nullptr, 0);
+                mbar_wait<0>(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
     } else if (warp >= F4_MMA_WARP && warp < F4_MMA_WARP + F4_TILES) {
@@ -206,8 +206,8 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
             const uint32_t q_addr = smem_u32(sm.q[g]), base = tmem + g * 256;
             auto scores = [&](int n) -> bool {
                 const int stage = n % F4_STAGES;
-                if (!mbar_wait(&sm.k_full[stage], (n / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
-                if (!mbar_wait(&sm.s_free[g], n & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
+                if (!mbar_wait<0>(&sm.k_full[stage], (n / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE)) return false;
+                if (!mbar_wait<0>(&sm.s_free[g], n & 1, abort_flag, status, STATUS_WAIT_FREE)) return false;
                 tc_fence_after();
                 const uint32_t k_addr = smem_u32(sm.k[stage]);
                 tmem_cp_32x128b(base + F4_SFK, smem_u32(sm.sfk[stage]));  // K's scale bytes; ordered before the MMAs below
@@ -220,12 +220,12 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
                 mma_commit(&sm.k_empty[stage]);
                 return true;
             };
-            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) && scores(0);
+            bool ok = mbar_wait<0>(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) && scores(0);
             for (int t = 0; ok && t < k_tiles; ++t) {
                 if (t + 1 < k_tiles) ok = scores(t + 1);
                 const int stage = t % F4_STAGES;
-                ok = ok && mbar_wait(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE) &&
-                     mbar_wait(&sm.p_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
+                ok = ok && mbar_wait<0>(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE) &&
+                     mbar_wait<0>(&sm.p_ready[g], t & 1, abort_flag, status, STATUS_WAIT_P);
                 if (!ok) break;
                 tc_fence_after();
                 tmem_cp_32x128b(base + F4_SFP, smem_u32(sm.sfp[g]));  // the scale bytes of P^ and of V
@@ -239,7 +239,7 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
             if (!ok) {
                 int never = 0;
                 mma_commit(&sm.drain[g]);
-                mbar_wait(&sm.drain[g], 0, &never, nullptr, 0);
+                mbar_wait<0>(&sm.drain[g], 0, &never, nullptr, 0);
             }
         }
     } else if (warp < F4_COMPUTE_WARPS) {
@@ -254,8 +254,8 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         const float2 c2 = make_float2(c, c);
         const bool smoothed = bias != nullptr;
         float m = -INFINITY;
-        bool ok = mbar_wait_warp(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
-                  mbar_wait_warp(&sm.k_full[0], 0, abort_flag, status, STATUS_WAIT_TILE);
+        bool ok = mbar_wait_warp<0>(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
+                  mbar_wait_warp<0>(&sm.k_full[0], 0, abort_flag, status, STATUS_WAIT_TILE);
         if (ok) {  // scale bytes of Q (for the whole loop) and of the first K tile
             if (half == 0) {
 #pragma unroll
@@ -298,8 +298,8 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         for (int t = 0; ok && t < k_tiles; ++t) {
             const int stage = t % F4_STAGES;
             F4_TRACE(F4_TR_OTHER);
-            ok = mbar_wait_warp(&sm.s_full[g], t & 1, abort_flag, status, STATUS_WAIT_SCORES) &&
-                 mbar_wait_warp(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+            ok = mbar_wait_warp<0>(&sm.s_full[g], t & 1, abort_flag, status, STATUS_WAIT_SCORES) &&
+                 mbar_wait_warp<0>(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
             if (!ok) break;
             tc_fence_after();
             F4_TRACE(F4_TR_WAIT_S);
@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
             F4_TRACE(F4_TR_QUANTIZE);
 
             if (t > 0) {  // P.V of the previous tile must have read P, its scales and V's, and written O
-                ok = mbar_wait_warp(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
+                ok = mbar_wait_warp<0>(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
                 if (!ok) break;
                 tc_fence_after();
                 F4_TRACE(F4_TR_WAIT_O);
@@ -413,7 +413,7 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         }
         F4_TRACE_END(g);
 
-        if (ok) ok = mbar_wait_warp(&sm.o_full[g], (k_tiles - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
+        if (ok) ok = mbar_wait_warp<0>(&sm.o_full[g], (k_tiles - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
         if (ok) {
             tc_fence_after();
             const bool valid_row = q_row < n_queries;

@@ -120,38 +120,74 @@ constexpr unsigned WAIT_PROBES = 2048, WAIT_SLEEP_NS = UNICA_WAIT_SLEEP_NS;
 template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_probe_many(uint64_t* bar, int parity) {
     uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        ".reg .u32 left;\n\t"
-        "mov.u32 left, %3;\n"
-        "UNICA_WAIT_AGAIN:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "@p bra UNICA_WAIT_DONE;\n\t"
-        "nanosleep.u32 %4;\n\t"
-        "sub.u32 left, left, 1;\n\t"
-        "setp.ne.u32 q, left, 0;\n\t"
-        "@q bra UNICA_WAIT_AGAIN;\n"
-        "UNICA_WAIT_DONE:\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity), "n"(WAIT_PROBES), "n"(SLEEP_NS)
-        : "memory");
+    if constexpr (SLEEP_NS > 0) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            ".reg .u32 left;\n\t"
+            "mov.u32 left, %3;\n"
+            "UNICA_WAIT_AGAIN:\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "@p bra UNICA_WAIT_DONE;\n\t"
+            "nanosleep.u32 %4;\n\t"
+            "sub.u32 left, left, 1;\n\t"
+            "setp.ne.u32 q, left, 0;\n\t"
+            "@q bra UNICA_WAIT_AGAIN;\n"
+            "UNICA_WAIT_DONE:\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(smem_u32(bar)), "r"(parity), "n"(WAIT_PROBES), "n"(SLEEP_NS)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            ".reg .u32 left;\n\t"
+            "mov.u32 left, %3;\n"
+            "UNICA_SPIN_AGAIN:\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "@p bra UNICA_SPIN_DONE;\n\t"
+            "sub.u32 left, left, 1;\n\t"
+            "setp.ne.u32 q, left, 0;\n\t"
+            "@q bra UNICA_SPIN_AGAIN;\n"
+            "UNICA_SPIN_DONE:\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(smem_u32(bar)), "r"(parity), "n"(WAIT_PROBES)
+            : "memory");
+    }
     return done != 0;
 }
-// SLEEP_NS 0: for the threads that pass events on (their wake-up time is on everybody's critical path)
+// SLEEP_NS 0: for waits whose end is on everybody's critical path; the loop then is the plain one (probe, abort word,
+// clock), which measured faster than a bare run of probes: back-to-back probes crowd the queue that shared-memory
+// accesses and exponentials of the computing warps go through.
 template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile int* abort_flag, int* status, int code) {
-    if (mbar_probe_many<SLEEP_NS>(bar, parity)) return true;
-    const long long start = clock64();
-    while (true) {
+    if constexpr (SLEEP_NS == 0) {
+        if (mbar_try(bar, parity)) return true;
+        const long long start = clock64();
+        while (true) {
+            if (mbar_try(bar, parity)) return true;
+            if (*abort_flag) return false;
+            if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    } else {
         if (mbar_probe_many<SLEEP_NS>(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - start > WAIT_LIMIT_CYCLES) {
-            *abort_flag = 1;
-            if (status) atomicCAS(status, 0, code);
-            return false;
+        const long long start = clock64();
+        while (true) {
+            if (mbar_probe_many<SLEEP_NS>(bar, parity)) return true;
+            if (*abort_flag) return false;
+            if (clock64() - start > WAIT_LIMIT_CYCLES) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
         }
     }
 }
@@ -161,26 +197,48 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile in
 template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_probe_many2(uint64_t* bar_a, int parity_a, uint64_t* bar_b, int parity_b) {
     uint32_t done;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q, r;\n\t"
-        ".reg .u32 left;\n\t"
-        "mov.u32 left, %5;\n"
-        "UNICA_WAIT2_AGAIN:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
-        "and.pred r, p, q;\n\t"
-        "@r bra UNICA_WAIT2_DONE;\n\t"
-        "nanosleep.u32 %6;\n\t"
-        "sub.u32 left, left, 1;\n\t"
-        "setp.ne.u32 q, left, 0;\n\t"
-        "@q bra UNICA_WAIT2_AGAIN;\n"
-        "UNICA_WAIT2_DONE:\n\t"
-        "selp.u32 %0, 1, 0, r;\n\t"
-        "}"
-        : "=r"(done)
-        : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b), "n"(WAIT_PROBES), "n"(SLEEP_NS)
-        : "memory");
+    if constexpr (SLEEP_NS > 0) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q, r;\n\t"
+            ".reg .u32 left;\n\t"
+            "mov.u32 left, %5;\n"
+            "UNICA_WAIT2_AGAIN:\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+            "and.pred r, p, q;\n\t"
+            "@r bra UNICA_WAIT2_DONE;\n\t"
+            "nanosleep.u32 %6;\n\t"
+            "sub.u32 left, left, 1;\n\t"
+            "setp.ne.u32 q, left, 0;\n\t"
+            "@q bra UNICA_WAIT2_AGAIN;\n"
+            "UNICA_WAIT2_DONE:\n\t"
+            "selp.u32 %0, 1, 0, r;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b), "n"(WAIT_PROBES), "n"(SLEEP_NS)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q, r;\n\t"
+            ".reg .u32 left;\n\t"
+            "mov.u32 left, %5;\n"
+            "UNICA_SPIN2_AGAIN:\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+            "and.pred r, p, q;\n\t"
+            "@r bra UNICA_SPIN2_DONE;\n\t"
+            "sub.u32 left, left, 1;\n\t"
+            "setp.ne.u32 q, left, 0;\n\t"
+            "@q bra UNICA_SPIN2_AGAIN;\n"
+            "UNICA_SPIN2_DONE:\n\t"
+            "selp.u32 %0, 1, 0, r;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b), "n"(WAIT_PROBES)
+            : "memory");
+    }
     return done != 0;
 }
 template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
@@ -204,6 +262,9 @@ __device__ __forceinline__ bool mbar_wait2(uint64_t* bar_a, int parity_a, uint64
 // warp an ordinary shared-memory load (some 30 cycles), a tenth of an mbarrier probe, so where the event is first seen by
 // a thread that has to watch it anyway (the completion of tcgen05.mma by the thread that issued them), that thread passes
 // it on through such a word.  Release / acquire at block scope; bounded like every other wait here.
+#ifndef UNICA_FLAG_SLEEP_NS
+#define UNICA_FLAG_SLEEP_NS 0
+#endif
 __device__ __forceinline__ void flag_publish(int* flag, int value) {
     asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(smem_u32(flag)), "r"(value) : "memory");
 }
@@ -213,6 +274,9 @@ __device__ __forceinline__ bool flag_wait(const int* flag, int at_least, volatil
         int value;
         asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(value) : "r"(smem_u32(flag)) : "memory");
         if (value >= at_least) return true;
+#if UNICA_FLAG_SLEEP_NS > 0
+        __nanosleep(UNICA_FLAG_SLEEP_NS);  // back-to-back looks crowd the queue the computing warps' exponentials go through
+#endif
         if (looks % 256 == 0) {
             if (*abort_flag) return false;
             const long long now = clock64();
@@ -232,8 +296,9 @@ __device__ __forceinline__ bool flag_wait_warp(const int* flag, int at_least, vo
 // The same for a whole warp: every lane waits, and all get the same answer.  The vote also reconverges the warp, which
 // the .sync.aligned tensor-memory instructions that usually follow require: a tcgen05.ld executed by part of a warp
 // never completes.
+template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, int parity, volatile int* abort_flag, int* status, int code) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code));
+    return __all_sync(0xffffffffu, mbar_wait<SLEEP_NS>(bar, parity, abort_flag, status, code));
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
