@@ -44,3 +44,13 @@ def test_gather_heads_two_ranks(heads, batch):
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
     mp.spawn(_worker, args=(2, port, heads, batch), nprocs=2, join=True)
+
+
+def test_slice_heads_on_plain_tuples():
+    from collections import namedtuple
+
+    Pair = namedtuple("Pair", "codes sf")
+    a, b = torch.zeros(1, 4, 3), torch.ones(1, 4, 2, 2)
+    got = shard.slice_heads((a, Pair(a, b), (a, b), None, 512), slice(1, 3))
+    assert got[0].shape == (1, 2, 3) and isinstance(got[1], Pair) and got[1].sf.shape == (1, 2, 2, 2)
+    assert got[2][1].shape == (1, 2, 2, 2) and got[3] is None and got[4] == 512

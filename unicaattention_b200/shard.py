@@ -41,16 +41,68 @@ def gather_heads(local: torch.Tensor, out: torch.Tensor, heads: int, rank: int, 
     return out
 
 
+def slice_heads(inputs, heads: slice):
+    """The operands kernel_inputs() returned, narrowed to a slice of their heads (every tensor in them is
+    [batch, heads, ...]; tuples keep their type; numbers pass through)."""
+    if isinstance(inputs, torch.Tensor):
+        return inputs[:, heads] if inputs.dim() >= 2 else inputs
+    if isinstance(inputs, tuple):
+        parts = [slice_heads(x, heads) for x in inputs]
+        return type(inputs)(*parts) if hasattr(inputs, "_fields") else tuple(parts)
+    return inputs
+
+
+_SIDE_STREAMS: dict = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    if device not in _SIDE_STREAMS:
+        _SIDE_STREAMS[device] = torch.cuda.Stream(device, priority=-1)  # its few blocks go ahead of the attention kernel's
+    return _SIDE_STREAMS[device]
+
+
 def attention_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, group=None, out: torch.Tensor | None = None,
-                      **preset) -> torch.Tensor:
+                      head_groups: int | None = None, attention=None, kernel_inputs=None, **preset) -> torch.Tensor:
     """q, k, v: this rank's heads [batch, head_slice(heads, rank, world), tokens, 128].  Returns the whole
-    [batch, heads, n_queries, 128] output on every rank (in `out` when given)."""
+    [batch, heads, n_queries, 128] output on every rank (in `out` when given).
+
+    The rank's heads are quantized once and then run through the attention kernel in `head_groups` groups (default: up to
+    5); each group's output is gathered (one all-gather into a staging buffer, one strided copy into place) on a side
+    stream while the next group's kernel runs, so that only the last group's gather is exposed.  Every head has its own
+    statistics and scales, so the result is bit for bit that of one launch.  With a batch dimension, uneven head slices
+    or head_groups = 1 the heads go through in one launch and one gather.
+    attention / kernel_inputs: the functions to call (default: this package's; tests pass stand-ins)."""
     import torch.distributed as dist
 
     import unicaattention_b200 as unica
 
+    attention = attention or unica.attention
+    kernel_inputs = kernel_inputs or unica.kernel_inputs
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    local = unica.attention(q, k, v, **preset)
+    batch, local_heads = q.shape[:2]
     if out is None:
-        out = torch.empty((q.shape[0], heads, q.shape[2], q.shape[3]), dtype=q.dtype, device=q.device)
-    return gather_heads(local.contiguous(), out, heads, rank, world, group)
+        out = torch.empty((batch, heads, q.shape[2], q.shape[3]), dtype=q.dtype, device=q.device)
+    groups = min(local_heads, 5) if head_groups is None else max(1, min(local_heads, head_groups))
+    if groups == 1 or batch != 1 or heads % world or not q.is_cuda or not out.is_contiguous():
+        return gather_heads(attention(q, k, v, **preset).contiguous(), out, heads, rank, world, group)
+    inputs = kernel_inputs(q, k, v, **preset)
+    current, side = torch.cuda.current_stream(q.device), _side_stream(q.device)
+    side.wait_stream(current)  # `out` may still be read by work queued before this call
+    placed = out.view(world, local_heads, *out.shape[2:])  # [rank, head of the rank, token, channel]
+    base, extra = divmod(local_heads, groups)
+    first = 0
+    for g in range(groups):
+        piece = slice(first, first + base + (1 if g < extra else 0))
+        first = piece.stop
+        local = attention(q[:, piece], k[:, piece], v[:, piece], inputs=slice_heads(inputs, piece), **preset)
+        done = torch.cuda.Event()
+        done.record(current)
+        with torch.cuda.stream(side):
+            side.wait_event(done)
+            staged = torch.empty((world, piece.stop - piece.start, *out.shape[2:]), dtype=out.dtype, device=out.device)
+            dist.all_gather_into_tensor(staged.view(-1), local.view(-1), group=group)
+            placed[:, piece].copy_(staged)
+        local.record_stream(side)
+        staged.record_stream(current)
+    current.wait_stream(side)
+    return out
