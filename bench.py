@@ -216,6 +216,8 @@ class Bench:
         from unicaattention_b200 import shard
 
         self.args, self.unica, self.shard = args, unica, shard
+        self.gather_note = ("each attention kernel stores its output rows into every rank's copy over NVLink (peer stores), two barriers"
+                            if args.gather == "peer" else "NCCL all-gathers of head groups on a side stream")
         self.rank, self.world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
         self.local = int(os.environ.get("LOCAL_RANK", "0"))
         if self.world != args.gpus:
@@ -264,8 +266,16 @@ class Bench:
         host = build_inputs(workload, batch, my_heads, n)
         dev = [x.to(self.device, non_blocking=True) for x in host]
         torch.cuda.synchronize()
+        gathered = None
+        if self.world > 1 and self.args.gather == "peer":
+            try:  # the same outcome on every rank
+                gathered = self.shard.SharedOutput(batch, all_heads, n)
+            except RuntimeError as error:
+                self.gather_note = f"NCCL all-gathers of head groups on a side stream (no shared output: {error})"
+        if self.world > 1 and gathered is None:
+            gathered = torch.empty((batch, all_heads, n, 128), dtype=torch.bfloat16, device=self.device)
         return {"workload": workload, "batch": batch, "heads": all_heads, "tokens": n, "my_heads": my_heads, "host": host, "dev": dev,
-                "gathered": torch.empty((batch, all_heads, n, 128), dtype=torch.bfloat16, device=self.device) if self.world > 1 else None}
+                "gathered": gathered}
 
     def step_fn(self, data, mode):
         unica, preset = self.unica, self.unica.PRESETS[mode]
@@ -415,7 +425,7 @@ class Bench:
             line = {"metric": metric_name(args.mode, batch, heads, tokens), "value": head["value"], "unit": "TOPS", "n_gpus": self.world,
                     "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
                     "scaling": "strong", "vs_baseline": None, "dtype": dtype_of(args.mode), "data": "synthetic",
-                    "config": config_of(args, batch, heads, tokens) | {"input_channel_spread": spreads}, "clocks": clocks, "e2e": e2e,
+                    "config": config_of(args, batch, heads, tokens) | {"input_channel_spread": spreads} | ({"gather": self.gather_note} if self.world > 1 else {}), "clocks": clocks, "e2e": e2e,
                     "gpu_launches": head["gpu_launches"], "roofline": head["roofline"], "quantization": head["quantization"],
                     "accuracy": head.get("accuracy"), "modes": modes, "configs": configs,
                     "published_other_hardware": {"rtx5080_tops": PUBLISHED_RTX5080_TOPS.get(args.mode)}}
@@ -441,6 +451,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-to-host leg")
     ap.add_argument("--no-modes", action="store_true", help="skip the other presets")
     ap.add_argument("--no-configs", action="store_true", help="skip the image and hires signatures")
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: output rows stored to every rank by the attention kernel (peer), or NCCL all-gathers of head groups")
     ap.add_argument("--heads", type=int, default=0, help="override the workload's head count (profiling on a small case)")
     ap.add_argument("--tokens", type=int, default=0, help="override the workload's token count (profiling on a small case)")
     ap.add_argument("--hires-tokens", type=int, default=0, help="override the hires signature's token count")

@@ -167,6 +167,19 @@ int unica_b200_smooth_bias_rope(const void* k, unica_token_layout layout, const 
                                 const void* rope, long long rope_batch_stride, int heads, int q_blocks, int n_keys,
                                 float scale_log2, float* bias, void* stream);
 
+/* No counterpart in the reference (which runs on one GPU).  unica_b200_attention_int8 for a job that shards the heads
+ * over several GPUs and wants every GPU to end up with all heads: each output row is stored to `out` and, at the same
+ * offsets, to the n_peers (0..7) tensors of peer_out, which are this process's mappings of the other GPUs' output tensors
+ * (peer access or an imported IPC / fabric handle; `out` and each peer_out[i] already offset to this call's first head).
+ * The kernel only stores to peer memory, with plain stores, and reads nothing from it.  Ordering against the peers'
+ * own streams is the caller's business: nobody may read or overwrite those rows between this call's launch and a
+ * barrier after its completion.  peer_out is read before the call returns (host memory). */
+int unica_b200_attention_int8_peers(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
+                                    const int8_t* v8, const float* v_scale, const float* v_token, int v_mode,
+                                    const int* outlier_keys, const float* outlier_rows, int n_outliers, void* out,
+                                    void* const* peer_out, int n_peers, unica_token_layout out_layout, int heads, int n_queries,
+                                    int n_keys, float scale_log2, int* status, void* stream);
+
 /* Hardware self-test of the tensor-core path (the idea of the reference's tests/test_mma.py: small integers make every
  * result exact, so a wrong lane or layout cannot hide).  One tcgen05.mma kind::i8 chain D[128 x n] = A[128 x k] . B[n x k]^T
  * with A (u8 if a_unsigned, else s8) and B (s8) given as the shared-memory images described above
@@ -186,6 +199,12 @@ int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* 
                              const void* sfv, const float* qk_outer, const float* v_outer, const float* bias, int q_blocks,
                              int smooth_q, void* out, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
                              float scale_log2, int* status, void* stream);
+
+/* No counterpart in the reference: unica_b200_attention_fp4 with peer outputs, as unica_b200_attention_int8_peers. */
+int unica_b200_attention_fp4_peers(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
+                                   const void* sfv, const float* qk_outer, const float* v_outer, const float* bias, int q_blocks,
+                                   int smooth_q, void* out, void* const* peer_out, int n_peers, unica_token_layout out_layout,
+                                   int heads, int n_queries, int n_keys, float scale_log2, int* status, void* stream);
 
 /* The same for the block-scaled FP4 path: D[128 x n] = (A . sfa) . (B . sfb)^T with one tcgen05.mma
  * kind::mxf4nvf4.block_scale.scale_vec::4X per 64 elements of k (k = 64 or 128).  a_image [k / 32][128][16],

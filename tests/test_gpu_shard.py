@@ -53,3 +53,20 @@ def test_slice_heads_keeps_the_operands_types():
     inputs = unica.kernel_inputs(q, k, v, **unica.PRESETS["outliers"])
     keys, rows = shard.slice_heads(inputs, slice(0, 1))[6]
     assert keys.shape[1] == 1 and rows.shape[1] == 1
+
+
+def test_shared_output_in_a_group_of_one(one_rank_group):
+    """SharedOutput and its two barriers with a one-rank group: no peers, the same bits as a plain call."""
+    import unicaattention_b200 as unica
+    from unicaattention_b200 import shard
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v = (torch.randn((1, 4, 700, 128), device="cuda", dtype=torch.bfloat16, generator=g) for _ in range(3))
+    try:
+        shared = shard.SharedOutput(1, 4, 700)
+    except RuntimeError as error:
+        pytest.skip(f"symmetric memory unavailable: {error}")
+    for preset in ("per_channel", "fast"):
+        got = shard.attention_sharded(q, k, v, 4, out=shared, **unica.PRESETS[preset])
+        assert got is shared.tensor and torch.equal(got, unica.attention(q, k, v, **unica.PRESETS[preset]))
+    unica.check_status()

@@ -17,12 +17,14 @@ only steered the sm_120 kernels (WARPS_PER_BLOCK, PRODUCER, WAVE_DISPATCH) are a
 
 from __future__ import annotations
 
+import ctypes
 import functools
 import math
 import os
 import time
 import warnings
 import weakref
+from typing import Sequence
 
 import torch
 
@@ -378,12 +380,22 @@ def _settings(kernel: str, tile: dict) -> dict:
 
 @on_their_device
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = DEFAULT_KERNEL,
-              inputs: tuple | None = None, rope: torch.Tensor | None = None, **tile: int) -> torch.Tensor:
+              inputs: tuple | None = None, rope: torch.Tensor | None = None, out: torch.Tensor | None = None,
+              peer_out: Sequence[int] = (), **tile: int) -> torch.Tensor:
     """softmax(q k^T / sqrt(d)) v, non-causal.  q [batch, heads, n_queries, 128]; k, v [batch, heads, n_keys, 128]; all
     bfloat16 or all float16, on a B200.  Returns a tensor like q (dtype and strides).  kernel / tile pick the mode, as
     in PRESETS.  inputs: what kernel_inputs() returned for these q, k, v; the kernel then runs alone.
+    out: where to write, a bfloat16 tensor of q's shape (any strides the kernels can address: see readable()), returned.
+    peer_out: with out, up to 7 device addresses of tensors laid out like out in other GPUs' memory, mapped into this
+    process; the kernel stores every row there as well (see shard.SharedOutput, which also does the barriers this needs).
     Same checks and exceptions as the reference (unica/__init__.py:126-190)."""
     settings = _settings(kernel, tile)
+    if out is not None:
+        if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or out.shape != q.shape or out.device != q.device or readable(out) is not out:
+            raise ValueError("out must be a bfloat16 tensor of q's shape on q's device, 16-byte aligned rows with contiguous "
+                             "channels, and q, k, v bfloat16")
+    elif peer_out:
+        raise ValueError("peer_out needs out")
     if not (q.dtype == k.dtype == v.dtype and q.dtype in (torch.bfloat16, torch.float16)):
         raise TypeError(f"q, k, v must all be bfloat16 or all float16, got {q.dtype}, {k.dtype}, {v.dtype}")
     if inputs is not None and q.dtype != torch.bfloat16:
@@ -402,25 +414,27 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
     if rope is not None:
         rope_table(rope, batch, n_queries, n_keys)
     if inputs is None and (q.dtype != torch.bfloat16 or heads_per_call(q, k, kernel, tile) < heads):
-        return in_pieces(q, k, v, kernel, rope, tile)
+        return in_pieces(q, k, v, kernel, rope, tile, out, peer_out)
     q, k, v = readable(q), readable(k), readable(v)
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    peers = (ctypes.c_void_p * len(peer_out))(*peer_out) if peer_out else None
     if n_queries == 0:
         return out
     if inputs is None:
         inputs = kernel_inputs(q, k, v, kernel, rope, **tile)
     if kernel == "attention_fp4":
         q4, k4, v4, qk_outer, v_outer, bias, smooth = inputs
-        lib.call("unica_b200_attention_fp4", lib.ptr(q4.codes), lib.ptr(q4.sf), lib.ptr(k4.codes), lib.ptr(k4.sf), lib.ptr(v4.codes),
-                 lib.ptr(v4.sf), lib.ptr(qk_outer), lib.ptr(v_outer), lib.ptr(bias), 0 if bias is None else bias.shape[2], smooth,
-                 lib.ptr(out), token_layout(out), batch * heads, n_queries, n_keys, HEAD_DIM**-0.5 * LOG2E,
-                 lib.ptr(status_word(q.device)), lib.stream())
+        lib.call("unica_b200_attention_fp4_peers", lib.ptr(q4.codes), lib.ptr(q4.sf), lib.ptr(k4.codes), lib.ptr(k4.sf),
+                 lib.ptr(v4.codes), lib.ptr(v4.sf), lib.ptr(qk_outer), lib.ptr(v_outer), lib.ptr(bias),
+                 0 if bias is None else bias.shape[2], smooth, lib.ptr(out), peers, len(peer_out), token_layout(out), batch * heads,
+                 n_queries, n_keys, HEAD_DIM**-0.5 * LOG2E, lib.ptr(status_word(q.device)), lib.stream())
         return out
     q8, q_scale, k8, k_scale, v8, v_scale, v_token, v_mode = inputs
     keys, rows = v_token if v_mode == lib.V_OUTLIERS else (None, None)
-    lib.call("unica_b200_attention_int8", lib.ptr(q8), lib.ptr(q_scale), lib.ptr(k8), lib.ptr(k_scale), lib.ptr(v8),
+    lib.call("unica_b200_attention_int8_peers", lib.ptr(q8), lib.ptr(q_scale), lib.ptr(k8), lib.ptr(k_scale), lib.ptr(v8),
              lib.ptr(v_scale), lib.ptr(v_token if v_mode == lib.V_TOKEN else None), v_mode, lib.ptr(keys), lib.ptr(rows),
-             0 if keys is None else keys.shape[-1], lib.ptr(out), token_layout(out), batch * heads, n_queries,
+             0 if keys is None else keys.shape[-1], lib.ptr(out), peers, len(peer_out), token_layout(out), batch * heads, n_queries,
              n_keys, HEAD_DIM**-0.5 * LOG2E, lib.ptr(status_word(q.device)), lib.stream())
     del settings
     return out
@@ -474,12 +488,18 @@ def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) ->
     return step
 
 
-def in_pieces(q, k, v, kernel: str, rope, tile: dict) -> torch.Tensor:
+def in_pieces(q, k, v, kernel: str, rope, tile: dict, out: torch.Tensor | None = None, peer_out: Sequence[int] = ()) -> torch.Tensor:
     """attention() a few heads at a time, each piece converted to bfloat16 on its own, into one output in q's dtype and
-    layout.  Every head has its own statistics and scales, summed in a fixed order, so the result is bit for bit that
-    of one call."""
-    out = torch.empty_like(q)
+    layout (or into `out` and its peers, piece by piece).  Every head has its own statistics and scales, summed in a
+    fixed order, so the result is bit for bit that of one call."""
     step = heads_per_call(q, k, kernel, tile)
+    if out is not None:
+        for first in range(0, q.shape[1], step):
+            piece = slice(first, first + step)
+            ahead = first * out.stride(1) * out.element_size()
+            attention(q[:, piece], k[:, piece], v[:, piece], kernel, None, rope, out[:, piece], [p + ahead for p in peer_out], **tile)
+        return out
+    out = torch.empty_like(q)
     for first in range(0, q.shape[1], step):
         piece = slice(first, first + step)
         out[:, piece] = attention(*(x[:, piece].to(torch.bfloat16) for x in (q, k, v)), kernel, None, rope, **tile)

@@ -123,7 +123,7 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
     attention_fp4_kernel(const uint8_t* __restrict__ q4, const uint32_t* __restrict__ sfq, const uint8_t* __restrict__ k4,
                          const uint32_t* __restrict__ sfk, const uint8_t* __restrict__ v4, const uint32_t* __restrict__ sfv,
                          const float* __restrict__ qk_outer, const float* __restrict__ v_outer, const float* __restrict__ bias,
-                         int q_blocks, int smooth_q, __nv_bfloat16* __restrict__ out, TokenLayout out_layout, int n_queries,
+                         int q_blocks, int smooth_q, __nv_bfloat16* __restrict__ out, TokenLayout out_layout, PeerOutputs peers, int n_queries,
                          int n_keys, float scale_log2, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Fp4Smem& sm = *reinterpret_cast<Fp4Smem*>(smem_raw);
@@ -417,7 +417,8 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         if (ok) {
             tc_fence_after();
             const bool valid_row = q_row < n_queries;
-            __nv_bfloat16* dst = out + out_layout.offset(head, valid_row ? q_row : 0) + half * (HEAD_DIM / 2);
+            const size_t at = out_layout.offset(head, valid_row ? q_row : 0) + half * (HEAD_DIM / 2);
+            __nv_bfloat16* dst = out + at;
             const float* scale = v_outer + head * HEAD_DIM + half * (HEAD_DIM / 2);
             float2 last[8];
             tmem_ld16_sync(my + F4_O + HEAD_DIM, last);  // column 128: the sum of P^
@@ -436,6 +437,11 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
                 if (valid_row) {
                     *reinterpret_cast<uint4*>(dst + part * 16) = make_uint4(w[0], w[1], w[2], w[3]);
                     *reinterpret_cast<uint4*>(dst + part * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                    for (int peer = 0; peer < peers.count; ++peer) {  // the same row in the other GPUs' copies of the output
+                        __nv_bfloat16* there = peers.out[peer] + at + part * 16;
+                        *reinterpret_cast<uint4*>(there) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(there + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
                 }
             }
         }
@@ -463,15 +469,17 @@ extern "C" int unica_b200_trace_read_fp4(long long* host_out) {
 }
 #endif
 
-extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
-                                        const void* sfv, const float* qk_outer, const float* v_outer, const float* bias,
-                                        int q_blocks, int smooth_q, void* out, unica_token_layout out_layout, int heads,
-                                        int n_queries, int n_keys, float scale_log2, int* status, void* stream) {
+static int attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4, const void* sfv,
+                         const float* qk_outer, const float* v_outer, const float* bias, int q_blocks, int smooth_q, void* out,
+                         void* const* peer_out, int n_peers, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
+                         float scale_log2, int* status, void* stream) {
     if (!q4 || !sfq || !k4 || !sfk || !v4 || !sfv || !qk_outer || !v_outer || !out) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: null pointer");
     if (heads <= 0 || heads > 65535 || n_queries <= 0 || n_keys <= 0)
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: heads must be in 1..65535, n_queries and n_keys positive");
     if (bias && (smooth_q <= 0 || smooth_q % 256 || q_blocks != (n_queries + smooth_q - 1) / smooth_q))
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: with a smoothing term, smooth_q must be a multiple of 256 and q_blocks = ceil(n_queries / smooth_q)");
+    PeerOutputs peers = {};
+    if (int e = unica_peer_outputs(out, peer_out, n_peers, &peers)) return e;
     if (int e = unica_check_device()) return e;
     const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE) * (2 / F4_TILES), heads);  // Q4 holds an even number of tiles
     const size_t smem = sizeof(Fp4Smem) + 128;
@@ -480,7 +488,24 @@ extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, cons
         return unica_check_launch("attention_fp4 (shared memory size)");
     attention_fp4_kernel<<<grid, F4_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
         q4, static_cast<const uint32_t*>(sfq), k4, static_cast<const uint32_t*>(sfk), v4, static_cast<const uint32_t*>(sfv), qk_outer,
-        v_outer, bias, q_blocks, smooth_q > 0 ? smooth_q : 1, static_cast<__nv_bfloat16*>(out), to_layout(out_layout), n_queries, n_keys,
-        scale_log2, status);
+        v_outer, bias, q_blocks, smooth_q > 0 ? smooth_q : 1, static_cast<__nv_bfloat16*>(out), to_layout(out_layout), peers, n_queries,
+        n_keys, scale_log2, status);
     return unica_check_launch("attention_fp4");
+}
+
+extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
+                                        const void* sfv, const float* qk_outer, const float* v_outer, const float* bias,
+                                        int q_blocks, int smooth_q, void* out, unica_token_layout out_layout, int heads,
+                                        int n_queries, int n_keys, float scale_log2, int* status, void* stream) {
+    return attention_fp4(q4, sfq, k4, sfk, v4, sfv, qk_outer, v_outer, bias, q_blocks, smooth_q, out, nullptr, 0, out_layout, heads,
+                         n_queries, n_keys, scale_log2, status, stream);
+}
+
+extern "C" int unica_b200_attention_fp4_peers(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk,
+                                              const uint8_t* v4, const void* sfv, const float* qk_outer, const float* v_outer,
+                                              const float* bias, int q_blocks, int smooth_q, void* out, void* const* peer_out,
+                                              int n_peers, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
+                                              float scale_log2, int* status, void* stream) {
+    return attention_fp4(q4, sfq, k4, sfk, v4, sfv, qk_outer, v_outer, bias, q_blocks, smooth_q, out, peer_out, n_peers, out_layout, heads,
+                         n_queries, n_keys, scale_log2, status, stream);
 }

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                           const float* __restrict__ k_scale, const int8_t* __restrict__ v8, const float* __restrict__ v_scale,
                           const float* __restrict__ v_token, const int* __restrict__ outlier_keys,
                           const float* __restrict__ outlier_rows, int n_outliers, __nv_bfloat16* __restrict__ out,
-                          TokenLayout out_layout, int n_queries, int n_keys, float scale_log2, int* status) {
+                          TokenLayout out_layout, PeerOutputs peers, int n_queries, int n_keys, float scale_log2, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     AttSmem& sm = *reinterpret_cast<AttSmem*>(smem_raw);
     const int warp = threadIdx.x / 32;
@@ -538,9 +538,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
         }
 
-        if (ok && q_row < n_queries) {
+        // Out through shared memory, so that a warp writes whole 256-byte rows (two per instruction) instead of 32 pieces
+        // of 16 bytes: that matters little for this GPU's memory and much for rows that cross NVLink to a peer.  The
+        // warp's 32 rows take one P^ slot: the last P.V, which the loop above has seen complete, was its last reader.
+        if (__all_sync(0xffffffffu, ok)) {
+            const int lane = threadIdx.x % 32;
+            uint8_t* staged = sm.p[warp - FLUSH_WARP];
             const float inv = 1.0f / den;
-            __nv_bfloat16* dst = out + out_layout.offset(head, q_row);
             const float* vs = v_scale + head * HEAD_DIM;
 #pragma unroll
             for (int chunk = 0; chunk < HEAD_DIM / 8; ++chunk) {
@@ -552,7 +556,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     const __nv_bfloat162 pair = __floats2bfloat162_rn(v.x * vs[c0] * inv, v.y * vs[c0 + 1] * inv);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pair);
                 }
-                *reinterpret_cast<uint4*>(dst + chunk * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                // 16-byte pieces of a row swapped about by the row number: no bank conflicts either way
+                *reinterpret_cast<uint4*>(staged + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            __syncwarp();
+            const int piece = lane % 16;
+#pragma unroll 4
+            for (int pair = 0; pair < 16; ++pair) {
+                const int r = 2 * pair + lane / 16;
+                const int out_row = q_tile * QUERY_TILE + (warp - FLUSH_WARP) * 32 + r;
+                const uint4 value = *reinterpret_cast<const uint4*>(staged + r * 256 + ((piece ^ (r & 15)) * 16));
+                if (out_row < n_queries) {
+                    const size_t at = out_layout.offset(head, out_row) + piece * 8;
+                    *reinterpret_cast<uint4*>(out + at) = value;
+                    for (int peer = 0; peer < peers.count; ++peer) *reinterpret_cast<uint4*>(peers.out[peer] + at) = value;
+                }
             }
         }
     }
@@ -621,11 +639,10 @@ __global__ void __launch_bounds__(128) selftest_mma_i8_kernel(const uint8_t* __r
 
 using namespace unica;
 
-extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
-                                         const int8_t* v8, const float* v_scale, const float* v_token, int v_mode,
-                                         const int* outlier_keys, const float* outlier_rows, int n_outliers, void* out,
-                                         unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
-                                         int* status, void* stream) {
+static int attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale, const int8_t* v8,
+                          const float* v_scale, const float* v_token, int v_mode, const int* outlier_keys, const float* outlier_rows,
+                          int n_outliers, void* out, void* const* peer_out, int n_peers, unica_token_layout out_layout, int heads,
+                          int n_queries, int n_keys, float scale_log2, int* status, void* stream) {
     if (!q8 || !q_scale || !k8 || !k_scale || !v8 || !v_scale || !out) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: null pointer");
     if (heads <= 0 || heads > 65535 || n_queries <= 0 || n_keys <= 0)
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: heads must be in 1..65535, n_queries and n_keys positive");
@@ -634,6 +651,8 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
     if (v_mode == UNICA_B200_V_OUTLIERS && (!outlier_keys || !outlier_rows || n_outliers < 1 || n_outliers > 8))
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: the outliers mode needs outlier_keys, outlier_rows and 1..8 outliers");
     if (v_mode == UNICA_B200_V_TOKEN && !v_token) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_int8: per-token mode needs v_token");
+    PeerOutputs peers = {};
+    if (int e = unica_peer_outputs(out, peer_out, n_peers, &peers)) return e;
     if (int e = unica_check_device()) return e;
     const dim3 grid((n_queries + 2 * QUERY_TILE - 1) / (2 * QUERY_TILE) * 2, heads);  // Q8 holds an even number of tiles
     const size_t smem = sizeof(AttSmem) + 128;
@@ -658,13 +677,31 @@ extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale,
             if (device < MAX_DEVICES) ready[device].store(1, std::memory_order_release);
         }
         kernel<<<grid, ATT_THREADS, smem, s>>>(q8, q_scale, k8, k_scale, v8, v_scale, v_token, outlier_keys, outlier_rows, n_outliers,
-                                               static_cast<__nv_bfloat16*>(out), to_layout(out_layout), n_queries, n_keys, scale_log2,
-                                               status);
+                                               static_cast<__nv_bfloat16*>(out), to_layout(out_layout), peers, n_queries, n_keys,
+                                               scale_log2, status);
         return unica_check_launch("attention_int8");
     };
     return v_mode == UNICA_B200_V_TOKEN      ? launch(attention_int8_kernel<true, false>, 1)
            : v_mode == UNICA_B200_V_OUTLIERS ? launch(attention_int8_kernel<false, true>, 2)
                                              : launch(attention_int8_kernel<false, false>, 0);
+}
+
+extern "C" int unica_b200_attention_int8(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
+                                         const int8_t* v8, const float* v_scale, const float* v_token, int v_mode,
+                                         const int* outlier_keys, const float* outlier_rows, int n_outliers, void* out,
+                                         unica_token_layout out_layout, int heads, int n_queries, int n_keys, float scale_log2,
+                                         int* status, void* stream) {
+    return attention_int8(q8, q_scale, k8, k_scale, v8, v_scale, v_token, v_mode, outlier_keys, outlier_rows, n_outliers, out, nullptr, 0,
+                          out_layout, heads, n_queries, n_keys, scale_log2, status, stream);
+}
+
+extern "C" int unica_b200_attention_int8_peers(const int8_t* q8, const float* q_scale, const int8_t* k8, const float* k_scale,
+                                               const int8_t* v8, const float* v_scale, const float* v_token, int v_mode,
+                                               const int* outlier_keys, const float* outlier_rows, int n_outliers, void* out,
+                                               void* const* peer_out, int n_peers, unica_token_layout out_layout, int heads,
+                                               int n_queries, int n_keys, float scale_log2, int* status, void* stream) {
+    return attention_int8(q8, q_scale, k8, k_scale, v8, v_scale, v_token, v_mode, outlier_keys, outlier_rows, n_outliers, out, peer_out,
+                          n_peers, out_layout, heads, n_queries, n_keys, scale_log2, status, stream);
 }
 
 #ifdef UNICA_TRACE

@@ -33,6 +33,14 @@ struct TokenLayout {
     }
 };
 
+// The same output tensor on other GPUs (peer mappings of their memory): the attention kernels store every output row
+// they compute to `out` and to each of these, at the same offsets.  Plain stores only; nothing is read from a peer.
+constexpr int MAX_PEER_OUTPUTS = 7;
+struct PeerOutputs {
+    __nv_bfloat16* out[MAX_PEER_OUTPUTS];
+    int count;
+};
+
 // RoPE inside the quantizers (the reference's rope_chunk, csrc/flash.cu:250-268): (cos, sin) per pair of channels in fp16,
 // [batch or 1][n_tokens][64][2]; batch_stride in halves, 0 when one table serves every batch.  table null: no rotation.
 struct RopeTable {
