@@ -143,7 +143,9 @@ int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layout, const fl
                               int n_tokens, uint8_t* codes, uint8_t* sf, float* v_outer, void* stream);
 
 /* Replaces smooth_bias (csrc/flash.cu:1254-1322; unica/__init__.py:503-521): q_mean[block] . (k - k_mean) in FP32 for
- * every block of smoothed queries and every key, times scale_log2.  q_mean [heads][q_blocks][128], k_mean [heads][128]. */
+ * every block of smoothed queries and every key, times scale_log2.  q_mean [heads][q_blocks][128], k_mean [heads][128].
+ * bias [heads][q_blocks][ceil(n_keys / 64) * 64] in the slot order of K4's tiles; the slots past the last key hold -inf
+ * (the attention kernel adds the table to the scores, which takes those slots out of the softmax). */
 int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean, int heads,
                            int q_blocks, int n_keys, float scale_log2, float* bias, void* stream);
 

@@ -101,4 +101,4 @@ def test_smooth_bias_is_exact_to_float():
     want = expected[..., order[valid]]
     bound = (q_mean.abs().double() @ centred.abs().transpose(-1, -2))[..., order[valid]] * 2.0**-20 + 1e-6
     assert ((got - want).abs() <= bound).all(), ((got - want).abs() / bound).max()
-    assert not bias[..., ~valid].any()
+    assert bool(torch.isneginf(bias[..., ~valid]).all())  # slots past the last key

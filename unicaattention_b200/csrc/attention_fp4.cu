@@ -5,16 +5,18 @@
 //   S[g]  = Q4[g] . K4(t)^T     128 x 64,  2 instructions of K = 64 channels
 //   O[g] += P4[g](t) . V4(t)    128 x 144, 1 instruction of K = 64 keys; columns 0..127 are the output channels, column
 //                               128 multiplies P by a row of ones: the running softmax denominator, rescaled with O
-// One block = F4_TILES (2) tiles of 128 query rows of one head sharing every K and V tile, two threads per query row
-// (both on the row's tensor-memory lane, 32 key slots and 64 output channels each); the last warpgroup holds the
-// producer warp (bulk TMA copies) and one MMA warp per query tile, one elected thread of which issues that tile's
-// instructions and copies K's, V's and P's scale bytes into tensor memory.
+// One block = F4_TILES (2) tiles of 128 query rows of one head sharing every K and V tile, one thread per query row
+// (on the row's tensor-memory lane: all 64 key slots of a tile in its registers, so a row's maximum needs no exchange
+// between threads); the last warpgroup holds the producer warp (bulk TMA copies) and one MMA warp per query tile,
+// one elected thread of which issues that tile's instructions and copies K's, V's and P's scale bytes into tensor
+// memory.
 //
 // Numerics (bench/emulate.py:298-369 with the fast contract): scores x = S * (q_outer k_outer log2(e)/sqrt(d)) + bias,
 // bias the exact q_mean . (k - k_mean) term of Q smoothing; running maximum m; P = 1024 * 2^(x - m) in NVFP4 along the
-// keys of the tile in slot order with a fixed outer scale of 1: per 16 slots sp = e4m3(max P / 6), codes e2m1(P / sp);
-// O = O * 2^(m_old - m) + P^ . V^; out = O / (sum of P^) * v_outer.  The exponentials are ex2.approx, so a code of P
-// can land on the other side of a rounding tie than the emulation's: results agree to rounding, not bit for bit.
+// keys of the tile in slot order with a fixed outer scale of 1: per 16 slots sp = e4m3(max P / 6), codes e2m1(P / sp),
+// P / sp taken as 2^(x - m + 10 - log2 sp) in one ex2.approx; O = O * 2^(m_old - m) + P^ . V^; out = O / (sum of P^) *
+// v_outer.  A code of P can therefore land on the other side of a rounding boundary than the emulation's (P / sp is off
+// by some 1e-6 relative): results agree to rounding, not bit for bit.
 //
 // Scale bytes live in tensor memory, row r of an operand in lane r % 32 of column r / 32 of every 32-lane quarter.  Q's
 // are stored once by the computing warps (tcgen05.st); K's, V's and P's are copied from shared memory by the issuing
@@ -30,16 +32,12 @@
 
 namespace unica {
 
-#ifndef UNICA_F4_TILES
-#define UNICA_F4_TILES 2
-#endif
-constexpr int F4_TILES = UNICA_F4_TILES;  // query tiles of 128 rows per block: 2 (one block per SM; 22.5 ms at 40 x 32760) or 1 (two
-                                          // blocks per SM at 80 registers: 26.5 ms)
-constexpr int F4_COMPUTE_WARPS = 8 * F4_TILES;  // query tiles x 2 threads per row x 4 warps
+constexpr int F4_TILES = 2;  // query tiles of 128 rows per block (tensor memory holds two: 2 x 232 of 512 columns)
+constexpr int F4_COMPUTE_WARPS = 4 * F4_TILES;  // query tiles x 4 warps, a thread per row
 constexpr int F4_THREADS = (F4_COMPUTE_WARPS + 4) * 32;
 constexpr int F4_PRODUCER_WARP = F4_COMPUTE_WARPS, F4_MMA_WARP = F4_COMPUTE_WARPS + 1;
-constexpr int F4_HALF_SLOTS = KEY_TILE / 2;  // what one of a row's two threads takes
-constexpr int F4_STAGES = 3;
+constexpr int F4_HALF_SLOTS = KEY_TILE / 2;  // one 16-byte piece of a row of P^: two scale blocks of 16 slots
+constexpr int F4_STAGES = 4;
 constexpr int Q4_BYTES = QUERY_TILE * HEAD_DIM / 2;  // 8192
 constexpr int SFQ_BYTES = 2 * QUERY_TILE * 4;        // 1024
 constexpr int K4_BYTES = KEY_TILE * HEAD_DIM / 2;    // 4096
@@ -85,12 +83,14 @@ struct __align__(128) Fp4Smem {
     uint8_t v[F4_STAGES][V4_BYTES];
     uint32_t sfv[F4_STAGES][2][32][4];  // block 0: channel c = word c / 32 of lane c % 32; block 1: the ones rows
     float bias[F4_STAGES][KEY_TILE];
+    float mask[2][KEY_TILE];  // what is added to the scores where there is no smoothing term: zeros / -inf in the last tile's empty slots
     uint8_t p[F4_TILES][P4_BYTES];
     uint32_t sfp[F4_TILES][32][4];  // P's scale words of a query tile: row r = word r / 32 of lane r % 32
-    uint2 exchange[F4_TILES][2][2][QUERY_TILE];  // [query tile][tag parity][thread of the row][row] = {tag, value}
-    float inv_e4m3[128];                  // 1 / value of every non-negative e4m3 byte, correctly rounded; 0 for the byte 0
+    uint8_t staged[F4_COMPUTE_WARPS][32 * HEAD_DIM * 2];  // output rows on their way out (see store_staged_rows)
+    float log2_e4m3[128];  // log2 of every non-negative e4m3 byte's value; +inf for the byte 0, so that 2^(x - that) = 0
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
     uint64_t s_full[F4_TILES], s_free[F4_TILES], p_ready[F4_TILES], o_full[F4_TILES], drain[F4_TILES];
+    int turn[4];  // per scheduler: whose exponentials are next (see the softmax threads)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -119,21 +119,21 @@ __device__ __forceinline__ uint32_t e2m1x8(const float2 (&v)[4]) {
     return word;
 }
 
-__global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
+__global__ void __launch_bounds__(F4_THREADS, 1)
     attention_fp4_kernel(const uint8_t* __restrict__ q4, const uint32_t* __restrict__ sfq, const uint8_t* __restrict__ k4,
                          const uint32_t* __restrict__ sfk, const uint8_t* __restrict__ v4, const uint32_t* __restrict__ sfv,
                          const float* __restrict__ qk_outer, const float* __restrict__ v_outer, const float* __restrict__ bias,
-                         int q_blocks, int smooth_q, __nv_bfloat16* __restrict__ out, TokenLayout out_layout, PeerOutputs peers, int n_queries,
+                         int q_blocks, int smooth_q, __nv_bfloat16* __restrict__ out, TokenLayout out_layout, const __grid_constant__ PeerOutputs peers, int n_queries,
                          int n_keys, float scale_log2, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Fp4Smem& sm = *reinterpret_cast<Fp4Smem*>(smem_raw);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int head = blockIdx.y;
     const int q_tiles = F4_TILES * gridDim.x;  // allocated Q tiles per head (even)
-    if (F4_TILES == 1 && blockIdx.x * QUERY_TILE >= n_queries) return;  // the padding tile of an odd count: nothing to do
     const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
     volatile int* abort_flag = &sm.abort_flag;
 
+    if (threadIdx.x < 4) sm.turn[threadIdx.x] = 0;
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
         mbar_init(&sm.q_full, 1);
@@ -145,17 +145,22 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         }
         for (int g = 0; g < F4_TILES; ++g) {
             mbar_init(&sm.s_full[g], 1);
-            mbar_init(&sm.s_free[g], 2 * QUERY_TILE);  // both threads of every row
-            mbar_init(&sm.p_ready[g], 2 * QUERY_TILE);
+            mbar_init(&sm.s_free[g], QUERY_TILE);  // every row's thread
+            mbar_init(&sm.p_ready[g], QUERY_TILE);
             mbar_init(&sm.o_full[g], 1);
         }
         for (int g = 0; g < F4_TILES; ++g) mbar_init(&sm.drain[g], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int i = threadIdx.x; i < F4_TILES * 2 * 2 * QUERY_TILE; i += F4_THREADS) (&sm.exchange[0][0][0][0])[i] = make_uint2(0xffffffffu, 0u);  // no tag
     if (threadIdx.x < 128) {
         const float value = __half2float(__half(__nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(threadIdx.x), __NV_E4M3)));
-        sm.inv_e4m3[threadIdx.x] = value > 0.0f ? __fdiv_rn(1.0f, value) : 0.0f;  // byte 127 is NaN: never produced (satfinite)
+        sm.log2_e4m3[threadIdx.x] = value > 0.0f ? log2f(value) : INFINITY;  // byte 127 is NaN: never produced (satfinite)
+    }
+    if (threadIdx.x >= 128 && threadIdx.x < 128 + KEY_TILE) {
+        const int slot = threadIdx.x - 128, j = slot % F4_HALF_SLOTS;
+        const int key = (k_tiles - 1) * KEY_TILE + F4_HALF_SLOTS * (slot / F4_HALF_SLOTS) + 8 * (j % 8 / 2) + 2 * (j / 8) + j % 2;  // slot -> key
+        sm.mask[0][slot] = 0.0f;
+        sm.mask[1][slot] = key < n_keys ? 0.0f : -INFINITY;
     }
     if (warp == F4_MMA_WARP) tmem_alloc(&sm.tmem_base, F4_TMEM_COLUMNS);
     tc_fence_before();
@@ -171,7 +176,7 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
             bulk_load(sm.q[0], q4 + q_first * Q4_BYTES, F4_TILES * Q4_BYTES, &sm.q_full);
             bulk_load(sm.sfq[0], sfq + q_first * (SFQ_BYTES / 4), F4_TILES * SFQ_BYTES, &sm.q_full);
             const float* bias_row = bias ? bias + (size_t(head) * q_blocks + (F4_TILES * blockIdx.x * QUERY_TILE) / smooth_q) * (size_t(k_tiles) * KEY_TILE) : nullptr;
-            int issued = 0;
+            int issued = 0, issued_v = 0;  // K tiles / V tiles whose copies have been started
             for (int t = 0; t < k_tiles; ++t) {
                 const int s = t % F4_STAGES, use = t / F4_STAGES;
                 const size_t tile = size_t(head) * k_tiles + t;
@@ -187,20 +192,22 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
                 bulk_load(sm.v[s], v4 + tile * V4_BYTES, V4_BYTES, &sm.v_full[s]);
                 bulk_load(sm.sfv[s], sfv + tile * (SFV_BYTES / 4), SFV_BYTES, &sm.v_full[s]);
                 if (bias_row) bulk_load(sm.bias[s], bias_row + size_t(t) * KEY_TILE, BIAS_BYTES, &sm.v_full[s]);
-                issued = t + 1;
+                issued = issued_v = t + 1;
             }
-            if (*abort_flag) {
+            if (*abort_flag) {  // no copy may still be writing this block's shared memory when the block ends
                 int never = 0;
                 for (int t = max(0, issued - F4_STAGES); t < issued; ++t)
                     mbar_wait<0>(&sm.k_full[t % F4_STAGES], (t / F4_STAGES) & 1, &never, nullptr, 0);
+                for (int t = max(0, issued_v - F4_STAGES); t < issued_v; ++t)
+                    mbar_wait<0>(&sm.v_full[t % F4_STAGES], (t / F4_STAGES) & 1, &never, nullptr, 0);
                 mbar_wait<0>(&sm.q_full, 0, &never, nullptr, 0);
             }
         }
     } else if (warp >= F4_MMA_WARP && warp < F4_MMA_WARP + F4_TILES) {
         // ------------------------------------------------------------------------------------------------ MMA issue
-        // One elected thread per query tile (warp 9: tile 0, warp 10: tile 1), blocking on each operand in the order they
-        // become ready: the scores of key tile t + 1 once the softmax threads have taken those of tile t and put K(t + 1)'s
-        // scale bytes in tensor memory; then P.V of tile t once P4(t) and the scale bytes of P and V are in place.
+        // One elected thread per query tile, blocking on each operand in the order they become ready: the scores of key
+        // tile t + 1 once the softmax threads have taken those of tile t; then P.V of tile t once P4(t) and the scale
+        // bytes of P and V are in place.
         if (elect_one()) {  // one elected lane of a converged warp: see elect_one() in common.cuh
             const int g = warp - F4_MMA_WARP;
             const uint32_t q_addr = smem_u32(sm.q[g]), base = tmem + g * 256;
@@ -244,10 +251,8 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         }
     } else if (warp < F4_COMPUTE_WARPS) {
         // ------------------------------------------------------------------------------------------------ softmax
-        // Two threads per query row: warp = 8 g + 4 half + quarter, both on tensor-memory lane 32 quarter + lane.  Thread
-        // `half` takes slots 32 half .. 32 half + 31 of every tile (two scale blocks of P) and output channels 64 half ..
-        // 64 half + 63; the two meet in one number per tile, the maximum of their scores (a tagged word in shared memory).
-        const int g = warp / 8, half = (warp / 4) % 2, row = (warp % 4) * 32 + lane;
+        // One thread per query row: warp = 4 g + quarter on tensor-memory lanes 32 quarter .. + 31.
+        const int g = warp / 4, row = (warp % 4) * 32 + lane;
         const int q_row = (F4_TILES * blockIdx.x + g) * QUERY_TILE + row;
         const uint32_t my = tmem + (uint32_t((warp % 4) * 32) << 16) + g * 256;
         const float c = qk_outer[head] * scale_log2;
@@ -256,154 +261,130 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         float m = -INFINITY;
         bool ok = mbar_wait_warp<0>(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE) &&
                   mbar_wait_warp<0>(&sm.k_full[0], 0, abort_flag, status, STATUS_WAIT_TILE);
-        if (ok) {  // scale bytes of Q (for the whole loop) and of the first K tile
-            if (half == 0) {
+        if (ok) {  // scale bytes of Q, for the whole loop
 #pragma unroll
-                for (int s = 0; s < 2; ++s)
-                    tmem_st4(my + F4_SFQ + 4 * s, sm.sfq[g][s][lane], sm.sfq[g][s][32 + lane], sm.sfq[g][s][64 + lane], sm.sfq[g][s][96 + lane]);
-                tmem_wait_st();
-            }
+            for (int s = 0; s < 2; ++s)
+                tmem_st4(my + F4_SFQ + 4 * s, sm.sfq[g][s][lane], sm.sfq[g][s][32 + lane], sm.sfq[g][s][64 + lane], sm.sfq[g][s][96 + lane]);
+            tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&sm.s_free[g]);
         }
-
-        // This thread's `value` for `tag` goes to its partner, the partner's comes back (false: gave up waiting).
-        // One 8-byte word {tag, value} per thread and tag parity: a word is written again two tags later, after the
-        // partner has read it (the partner reads tag n before it writes tag n + 1, which this thread waits for).
-        auto exchange = [&](int tag, float value, float& partner) -> bool {
-            const uint32_t mine = smem_u32(&sm.exchange[g][tag & 1][half][row]);
-            const uint32_t theirs = smem_u32(&sm.exchange[g][tag & 1][half ^ 1][row]);
-            asm volatile("st.volatile.shared.v2.u32 [%0], {%1, %2};" ::"r"(mine), "r"(uint32_t(tag)), "r"(__float_as_uint(value)) : "memory");
-            bool got = false;
-            const long long start = clock64();
-            while (true) {
-                uint2 w;
-                asm volatile("ld.volatile.shared.v2.u32 {%0, %1}, [%2];" : "=r"(w.x), "=r"(w.y) : "r"(theirs) : "memory");
-                if (w.x == uint32_t(tag)) {
-                    partner = __uint_as_float(w.y);
-                    got = true;
-                    break;
-                }
-                if (*abort_flag) break;
-                if (clock64() - start > WAIT_LIMIT_CYCLES) {
-                    *abort_flag = 1;
-                    if (status) atomicCAS(status, 0, int(STATUS_WAIT_PARTNER));
-                    break;
-                }
-            }
-            return __all_sync(0xffffffffu, got);
-        };
 
         F4_TRACE_DECL;
         for (int t = 0; ok && t < k_tiles; ++t) {
             const int stage = t % F4_STAGES;
             F4_TRACE(F4_TR_OTHER);
-            ok = mbar_wait_warp<0>(&sm.s_full[g], t & 1, abort_flag, status, STATUS_WAIT_SCORES) &&
-                 mbar_wait_warp<0>(&sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status, STATUS_WAIT_TILE);
+            // the scores, and V's tile, with which the smoothing term arrives: both probes in flight together
+            ok = __all_sync(0xffffffffu, mbar_wait2<0>(&sm.s_full[g], t & 1, &sm.v_full[stage], (t / F4_STAGES) & 1, abort_flag, status,
+                                                       STATUS_WAIT_SCORES));
             if (!ok) break;
             tc_fence_after();
             F4_TRACE(F4_TR_WAIT_S);
-            float2 x[F4_HALF_SLOTS / 2];
-            tmem_ld32_async(my + F4_S + half * F4_HALF_SLOTS, x);
-            tmem_wait_ld();
-            reg_fence16(x);
+            float2 x[KEY_TILE / 2];
+            tmem_ld64_sync(my + F4_S, x);
             tc_fence_before();
             mbar_arrive(&sm.s_free[g]);  // the scores are in registers: the buffer goes back
+            // Has P.V of the previous tile completed?  Asked now, looked at after the exponentials: it usually has, and
+            // the probe's latency (a few hundred cycles for a first look) is hidden behind them.
+            const bool pv_done = t == 0 || mbar_try(&sm.o_full[g], (t - 1) & 1);
             F4_TRACE(F4_TR_LOAD_S);
 
-            // scores in the log2 domain, the smoothing term added back, slots past the last key out of the maximum
-            if (smoothed) {
-                const float2* b2 = reinterpret_cast<const float2*>(sm.bias[stage]) + half * (F4_HALF_SLOTS / 2);
+            // Scores in the log2 domain plus the smoothing term (or zeros); -inf in the slots past the last key, which
+            // keeps them out of the maxima and makes their P zero.
+            {
+                const float* added = smoothed ? sm.bias[stage] : sm.mask[(t + 1) * KEY_TILE > n_keys];
+                const float2* b2 = reinterpret_cast<const float2*>(added);
 #pragma unroll
-                for (int j = 0; j < F4_HALF_SLOTS / 2; ++j) x[j] = fma2(x[j], c2, b2[j]);
-            } else {
-#pragma unroll
-                for (int j = 0; j < F4_HALF_SLOTS / 2; ++j) x[j] = mul2(x[j], c2);
+                for (int j = 0; j < KEY_TILE / 2; ++j) x[j] = fma2(x[j], c2, b2[j]);
             }
-            if ((t + 1) * KEY_TILE > n_keys) {
+            float block_max[4];
 #pragma unroll
-                for (int j = 0; j < F4_HALF_SLOTS; ++j) {
-                    const int key = t * KEY_TILE + 32 * half + 8 * (j % 8 / 2) + 2 * (j / 8) + j % 2;  // slot 32 half + j -> key
-                    if (key >= n_keys) (j % 2 ? x[j / 2].y : x[j / 2].x) = -INFINITY;
-                }
-            }
-            float block_max[2];
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
+            for (int b = 0; b < 4; ++b) {
                 float top = fmaxf(x[8 * b].x, x[8 * b].y);
 #pragma unroll
                 for (int i = 1; i < 8; ++i) top = max3(top, x[8 * b + i].x, x[8 * b + i].y);
                 block_max[b] = top;
             }
-            const float mine = fmaxf(block_max[0], block_max[1]);
-            float theirs = mine;
-            ok = exchange(t, mine, theirs);
-            if (!ok) break;
-            const float m_new = fmaxf(m, fmaxf(mine, theirs));
+            const float m_new = fmaxf(max3(m, block_max[0], block_max[1]), fmaxf(block_max[2], block_max[3]));
             const float alpha = ex2(m - m_new);
             m = m_new;
             F4_TRACE(F4_TR_MAX);
 
-            // P in NVFP4: per 16 slots a scale byte e4m3(max P / 6), then the codes straight out of the exponent
-            uint32_t codes[4], sf_pair = 0;
-            const float2 gain2 = make_float2(P_LOG2_GAIN - m_new, P_LOG2_GAIN - m_new);
+            // P in NVFP4: per 16 slots a scale byte sp = e4m3(max P / 6) with P = 1024 * 2^(x - m), then the codes of
+            // P / sp = 2^(x - m + 10 - log2 sp) straight out of the exponent unit; log2 of every e4m3 value comes from a
+            // table (a logarithm here would double the block's dependent chain).
+            uint32_t codes[8], sf_word = 0;
+            const float gain = P_LOG2_GAIN - m_new;
+#ifdef UNICA_F4_TURNS
+            // The two warps of a scheduler (one per query tile) take turns at the exponentials, so that one's run of them
+            // overlaps the other's waits and loads instead of colliding with its run.
+            ok = flag_wait_warp(&sm.turn[warp % 4], 2 * t + g, abort_flag, status, STATUS_WAIT_PARTNER);
+            if (!ok) break;
+#endif
 #pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                const float top = ex2(block_max[b] - m_new + P_LOG2_GAIN) * (1.0f / 6.0f);
+            for (int b = 0; b < 4; ++b) {
+                const float top = ex2(block_max[b] + gain) * (1.0f / 6.0f);
                 const uint32_t byte = __nv_cvt_float_to_fp8(top, __NV_SATFINITE, __NV_E4M3);
-                // P / sp as the emulation takes it, 1024 * 2^(x - m) times 1 / sp: a product of two correctly rounded
-                // factors lands on the other side of an e2m1 tie far less often than 2^(x - m + 10 - log2 sp) does.
-                // 1 / sp comes from a table of the 127 e4m3 values: a division here would put a branch (its slow path)
-                // into the middle of the exponentials.
-                const float inv = sm.inv_e4m3[byte];
-                const float2 inv2 = make_float2(inv, inv);
-                sf_pair |= byte << (8 * b);
+                const float shift = gain - sm.log2_e4m3[byte];  // byte 0 (every P below e4m3's range): -inf, all codes zero
+                const float2 shift2 = make_float2(shift, shift);
+                sf_word |= byte << (8 * b);
 #pragma unroll
                 for (int w = 0; w < 2; ++w) {
                     float2 r[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const float2 e = add2(x[8 * b + 4 * w + i], gain2);
-                        r[i] = mul2(make_float2(ex2(e.x), ex2(e.y)), inv2);
+                        const float2 e = add2(x[8 * b + 4 * w + i], shift2);
+                        r[i] = make_float2(ex2(e.x), ex2(e.y));
                     }
                     codes[2 * b + w] = e2m1x8(r);
                 }
             }
+#ifdef UNICA_F4_TURNS
+            {
+                uint32_t all = codes[0] ^ codes[1] ^ codes[2] ^ codes[3] ^ codes[4] ^ codes[5] ^ codes[6] ^ codes[7];
+                asm volatile("" : "+r"(all));  // the codes exist: the exponentials have been through
+                if (lane == 0) flag_publish(&sm.turn[warp % 4], 2 * t + g + 1);
+            }
+#endif
             F4_TRACE(F4_TR_QUANTIZE);
 
             if (t > 0) {  // P.V of the previous tile must have read P, its scales and V's, and written O
-                ok = mbar_wait_warp<0>(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
-                if (!ok) break;
+                if (!__all_sync(0xffffffffu, pv_done)) {
+                    ok = mbar_wait_warp<0>(&sm.o_full[g], (t - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
+                    if (!ok) break;
+                }
                 tc_fence_after();
                 F4_TRACE(F4_TR_WAIT_O);
                 if (!__all_sync(0xffffffffu, alpha == 1.0f)) {  // the maximum moved: O and the denominator shrink
                     const float2 alpha2 = make_float2(alpha, alpha);
-                    const uint32_t mine_o = my + F4_O + half * (V4_TILE_ROWS / 2);  // 72 columns each: 32 + 40
-                    float2 o[2][8], tail[4];
+                    // 128 channels, then the denominator's column (the 15 after it stay zero)
 #pragma unroll
-                    for (int round = 0; round < 2; ++round) {
-                        tmem_ld16_async(mine_o + round * 32, o[0]);
-                        tmem_ld16_async(mine_o + round * 32 + 16, o[1]);
-                        if (round) tmem_ld8_async(mine_o + 64, tail);
+                    for (int first = 0; first < HEAD_DIM; first += 64) {
+                        float2 o[4][8];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) tmem_ld16_async(my + F4_O + first + 16 * i, o[i]);
                         tmem_wait_ld();
-                        reg_fence8(o[0]);
-                        reg_fence8(o[1]);
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i / 8][i % 8] = mul2(o[i / 8][i % 8], alpha2);
-                        tmem_st16(mine_o + round * 32, o[0]);
-                        tmem_st16(mine_o + round * 32 + 16, o[1]);
-                        if (round) {
-                            reg_fence4(tail);
+                        for (int i = 0; i < 4; ++i) {
+                            reg_fence8(o[i]);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) tail[i] = mul2(tail[i], alpha2);
-                            tmem_st8(mine_o + 64, tail);
+                            for (int j = 0; j < 8; ++j) o[i][j] = mul2(o[i][j], alpha2);
+                            tmem_st16(my + F4_O + first + 16 * i, o[i]);
                         }
                     }
+                    float2 sum[4];
+                    tmem_ld8_async(my + F4_O + HEAD_DIM, sum);
+                    tmem_wait_ld();
+                    reg_fence4(sum);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) sum[j] = mul2(sum[j], alpha2);
+                    tmem_st8(my + F4_O + HEAD_DIM, sum);
                 }
             }
             // P.V of the previous tile has read P^: this tile's codes and scale bytes may take its place
-            *reinterpret_cast<uint4*>(sm.p[g] + half * (QUERY_TILE * 16) + row * 16) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-            reinterpret_cast<uint16_t*>(&sm.sfp[g][row % 32][row / 32])[half] = uint16_t(sf_pair);  // bytes 2 half, 2 half + 1 of the row's word
+            *reinterpret_cast<uint4*>(sm.p[g] + row * 16) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+            *reinterpret_cast<uint4*>(sm.p[g] + QUERY_TILE * 16 + row * 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+            sm.sfp[g][row % 32][row / 32] = sf_word;  // byte 2 piece + block
             F4_TRACE(F4_TR_RESCALE);
             tmem_wait_st();  // the rescaled O, if any
             tc_fence_before();
@@ -416,17 +397,17 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
         if (ok) ok = mbar_wait_warp<0>(&sm.o_full[g], (k_tiles - 1) & 1, abort_flag, status, STATUS_WAIT_PV);
         if (ok) {
             tc_fence_after();
-            const bool valid_row = q_row < n_queries;
-            const size_t at = out_layout.offset(head, valid_row ? q_row : 0) + half * (HEAD_DIM / 2);
-            __nv_bfloat16* dst = out + at;
-            const float* scale = v_outer + head * HEAD_DIM + half * (HEAD_DIM / 2);
-            float2 last[8];
-            tmem_ld16_sync(my + F4_O + HEAD_DIM, last);  // column 128: the sum of P^
+            const float* scale = v_outer + head * HEAD_DIM;
+            float2 last[4];
+            tmem_ld8_async(my + F4_O + HEAD_DIM, last);  // column 128: the sum of P^
+            tmem_wait_ld();
+            reg_fence4(last);
             const float inv = 1.0f / last[0].x;
+            uint8_t* staged = sm.staged[warp];
 #pragma unroll
-            for (int part = 0; part < HEAD_DIM / 32; ++part) {
+            for (int part = 0; part < HEAD_DIM / 16; ++part) {
                 float2 o[8];
-                tmem_ld16_sync(my + F4_O + half * (HEAD_DIM / 2) + part * 16, o);
+                tmem_ld16_sync(my + F4_O + part * 16, o);
                 uint32_t w[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -434,16 +415,11 @@ __global__ void __launch_bounds__(F4_THREADS, 3 - F4_TILES)
                     const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i].x * scale[c0] * inv, o[i].y * scale[c0 + 1] * inv);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pair);
                 }
-                if (valid_row) {
-                    *reinterpret_cast<uint4*>(dst + part * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(dst + part * 16 + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-                    for (int peer = 0; peer < peers.count; ++peer) {  // the same row in the other GPUs' copies of the output
-                        __nv_bfloat16* there = peers.out[peer] + at + part * 16;
-                        *reinterpret_cast<uint4*>(there) = make_uint4(w[0], w[1], w[2], w[3]);
-                        *reinterpret_cast<uint4*>(there + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-                    }
-                }
+                stage_piece(staged, lane, 2 * part, make_uint4(w[0], w[1], w[2], w[3]));
+                stage_piece(staged, lane, 2 * part + 1, make_uint4(w[4], w[5], w[6], w[7]));
             }
+            __syncwarp();
+            store_staged_rows(staged, lane, q_row - lane, n_queries, head, out, out_layout, peers);
         }
     }
 

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                           const float* __restrict__ k_scale, const int8_t* __restrict__ v8, const float* __restrict__ v_scale,
                           const float* __restrict__ v_token, const int* __restrict__ outlier_keys,
                           const float* __restrict__ outlier_rows, int n_outliers, __nv_bfloat16* __restrict__ out,
-                          TokenLayout out_layout, PeerOutputs peers, int n_queries, int n_keys, float scale_log2, int* status) {
+                          TokenLayout out_layout, const __grid_constant__ PeerOutputs peers, int n_queries, int n_keys, float scale_log2, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     AttSmem& sm = *reinterpret_cast<AttSmem*>(smem_raw);
     const int warp = threadIdx.x / 32;
@@ -538,9 +538,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             }
         }
 
-        // Out through shared memory, so that a warp writes whole 256-byte rows (two per instruction) instead of 32 pieces
-        // of 16 bytes: that matters little for this GPU's memory and much for rows that cross NVLink to a peer.  The
-        // warp's 32 rows take one P^ slot: the last P.V, which the loop above has seen complete, was its last reader.
+        // Out through shared memory (stage_piece / store_staged_rows).  The warp's 32 rows take one P^ slot: the last
+        // P.V, which the loop above has seen complete, was its last reader.
         if (__all_sync(0xffffffffu, ok)) {
             const int lane = threadIdx.x % 32;
             uint8_t* staged = sm.p[warp - FLUSH_WARP];
@@ -556,22 +555,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     const __nv_bfloat162 pair = __floats2bfloat162_rn(v.x * vs[c0] * inv, v.y * vs[c0 + 1] * inv);
                     w[i] = *reinterpret_cast<const uint32_t*>(&pair);
                 }
-                // 16-byte pieces of a row swapped about by the row number: no bank conflicts either way
-                *reinterpret_cast<uint4*>(staged + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                stage_piece(staged, lane, chunk, make_uint4(w[0], w[1], w[2], w[3]));
             }
             __syncwarp();
-            const int piece = lane % 16;
-#pragma unroll 4
-            for (int pair = 0; pair < 16; ++pair) {
-                const int r = 2 * pair + lane / 16;
-                const int out_row = q_tile * QUERY_TILE + (warp - FLUSH_WARP) * 32 + r;
-                const uint4 value = *reinterpret_cast<const uint4*>(staged + r * 256 + ((piece ^ (r & 15)) * 16));
-                if (out_row < n_queries) {
-                    const size_t at = out_layout.offset(head, out_row) + piece * 8;
-                    *reinterpret_cast<uint4*>(out + at) = value;
-                    for (int peer = 0; peer < peers.count; ++peer) *reinterpret_cast<uint4*>(peers.out[peer] + at) = value;
-                }
-            }
+            store_staged_rows(staged, lane, q_tile * QUERY_TILE + (warp - FLUSH_WARP) * 32, n_queries, head, out, out_layout, peers);
         }
     }
 

@@ -41,6 +41,29 @@ struct PeerOutputs {
     int count;
 };
 
+// Output rows on their way out through shared memory, so that a warp writes whole 256-byte rows (two per instruction)
+// instead of 32 separate pieces of 16 bytes: that matters little for this GPU's memory and much for rows that cross
+// NVLink to a peer.  A warp owns 32 rows of 128 bf16 in `staged` (8 KB); the 16-byte pieces of a row are swapped about
+// by the row number, so neither the row-per-thread writes nor the row-per-half-warp reads meet bank conflicts.
+__device__ __forceinline__ void stage_piece(uint8_t* staged, int row_in_warp, int piece, uint4 value) {
+    *reinterpret_cast<uint4*>(staged + row_in_warp * 256 + ((piece ^ (row_in_warp & 15)) * 16)) = value;
+}
+// The warp's 32 staged rows (query rows first_row ..) to `out` and to every peer; all lanes call it after __syncwarp().
+__device__ __forceinline__ void store_staged_rows(const uint8_t* staged, int lane, int first_row, int n_queries, int head,
+                                                  __nv_bfloat16* out, const TokenLayout& layout, const PeerOutputs& peers) {
+    const int piece = lane % 16;
+#pragma unroll 4
+    for (int pair = 0; pair < 16; ++pair) {
+        const int r = 2 * pair + lane / 16;
+        const uint4 value = *reinterpret_cast<const uint4*>(staged + r * 256 + ((piece ^ (r & 15)) * 16));
+        if (first_row + r < n_queries) {
+            const size_t at = layout.offset(head, first_row + r) + piece * 8;
+            *reinterpret_cast<uint4*>(out + at) = value;
+            for (int peer = 0; peer < peers.count; ++peer) *reinterpret_cast<uint4*>(peers.out[peer] + at) = value;
+        }
+    }
+}
+
 // RoPE inside the quantizers (the reference's rope_chunk, csrc/flash.cu:250-268): (cos, sin) per pair of channels in fp16,
 // [batch or 1][n_tokens][64][2]; batch_stride in halves, 0 when one table serves every batch.  table null: no rotation.
 struct RopeTable {

@@ -238,8 +238,9 @@ __global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfl
             const int b = b0 + group * MINE + j;
             if (b < q_blocks) {
                 float* row = bias + (size_t(head) * q_blocks + b) * (size_t(k_tiles) * KEY_TILE) + t * KEY_TILE;
-                row[slot] = dot[0][j] * scale_log2;
-                row[slot + KEY_TILE / KEYS] = dot[1][j] * scale_log2;
+                // slots past the last key get -inf: added to a score it keeps the slot out of the softmax
+                row[slot] = t * KEY_TILE + slot_key(slot) < n_keys ? dot[0][j] * scale_log2 : -INFINITY;
+                row[slot + KEY_TILE / KEYS] = t * KEY_TILE + slot_key(slot + KEY_TILE / KEYS) < n_keys ? dot[1][j] * scale_log2 : -INFINITY;
             }
         }
     }
