@@ -208,6 +208,16 @@ int unica_b200_attention_fp4_peers(const uint8_t* q4, const void* sfq, const uin
                                    int smooth_q, void* out, void* const* peer_out, int n_peers, unica_token_layout out_layout,
                                    int heads, int n_queries, int n_keys, float scale_log2, int* status, void* stream);
 
+/* No counterpart in the reference (its emulator shows P^, its kernel does not): unica_b200_attention_fp4 that also
+ * leaves every row's quantized probabilities in p_words, uint32 [heads][n_queries][ceil(n_keys / 64)][9]: per key tile
+ * eight words of e2m1 codes (slot s of the tile in nibble s % 8 of word s / 8) and one word with the four e4m3 scale
+ * bytes (slots 16 b .. 16 b + 15 in byte b).  For tests that count how many codes differ from an emulation's; the
+ * extra stores make it slower than the plain entry. */
+int unica_b200_attention_fp4_codes(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4,
+                                   const void* sfv, const float* qk_outer, const float* v_outer, const float* bias, int q_blocks,
+                                   int smooth_q, void* out, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
+                                   float scale_log2, uint32_t* p_words, int* status, void* stream);
+
 /* The same for the block-scaled FP4 path: D[128 x n] = (A . sfa) . (B . sfb)^T with one tcgen05.mma
  * kind::mxf4nvf4.block_scale.scale_vec::4X per 64 elements of k (k = 64 or 128).  a_image [k / 32][128][16],
  * b_image [k / 32][n][16] bytes (two e2m1 codes per byte, low nibble first); sfa uint32 [k / 64][128], sfb uint32

@@ -259,6 +259,22 @@ def attention_fast(q, k, v, smooth_q: int = 512, recip: bool = True, k_mean=None
     return out
 
 
+def attention_fast_codes(q, k, v, smooth_q: int = 512, recip: bool = True, k_mean=None, q_mean=None):
+    """attention_fast() over all rows, and the quantized probabilities it formed on the way: (out, codes uint8
+    [heads, nq, tiles, 64] in slot order, scale bytes uint8 [heads, nq, tiles, 4])."""
+    q, k, v = bf16_bits(q), bf16_bits(k), bf16_bits(v)
+    heads, nq, _ = q.shape
+    tiles = -(-k.shape[1] // 64)
+    k_mean = _f32(k_mean, (heads, D))
+    if q_mean is not None:
+        q_mean = _f32(q_mean, (heads, -(-nq // smooth_q), D))
+    out = np.empty((heads, nq, D), np.float32)
+    record = np.zeros((heads, nq, tiles, 68), np.uint8)
+    lib().uo_attention_fast_codes(_p(q), _p(k), _p(v), heads, nq, k.shape[1], smooth_q, int(recip), _p(k_mean), _p(q_mean), _p(out),
+                                  _p(record))
+    return out, record[..., :64], record[..., 64:]
+
+
 def rel_l2(a, b) -> float:
     a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
     return float(np.linalg.norm((a - b).ravel()) / np.linalg.norm(b.ravel()))

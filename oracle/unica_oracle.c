@@ -559,9 +559,11 @@ void uo_attention_accurate(const uint16_t* q, const uint16_t* k, const uint16_t*
 /* NVFP4 Q.K^T and P.V, Q mean-smoothed per `smooth_q` queries (0: no smoothing), keys in slot order, P in NVFP4
  * with outer scale 1 against p_mul = 1024.  k_mean [heads][128] / q_mean [heads][ceil(nq / smooth_q)][128] or NULL
  * (then uo_channel_stats's). */
-void uo_attention_fast_rope(const uint16_t* q, const uint16_t* k, const uint16_t* v, const float* rope, int heads_per_table,
-                            int heads, int nq, int nk, int smooth_q, int recip, const float* k_mean, const float* q_mean,
-                            int q_first, int q_count, float* out) {
+/* p_codes (or NULL): the quantized probabilities of every row and key tile as the loop forms them, uint8
+ * [heads][q_count][tiles][68]: 64 e2m1 codes in slot order, then the four e4m3 scale bytes. */
+static void attention_fast_impl(const uint16_t* q, const uint16_t* k, const uint16_t* v, const float* rope, int heads_per_table,
+                                int heads, int nq, int nk, int smooth_q, int recip, const float* k_mean, const float* q_mean,
+                                int q_first, int q_count, float* out, uint8_t* p_codes) {
     const float scale = (float)(1.0 / sqrt((double)D) * LOG2E);
     const float p_mul = 1024.0f;
     float* k_rot = to_float_rotated(k, rope, heads_per_table, heads, nk); /* the smoothing term takes k in float */
@@ -653,9 +655,14 @@ void uo_attention_fast_rope(const uint16_t* q, const uint16_t* k, const uint16_t
                         p[i] = exp2f(s[16 * b + i] - m_new) * p_mul;
                         a16 = fmaxf(a16, p[i]);
                     }
-                    float sp = e4m3_to_float(float_to_e4m3(fminf(scalar_div(a16, 6.0f, recip), 448.0f)));
+                    uint8_t sp_byte = float_to_e4m3(fminf(scalar_div(a16, 6.0f, recip), 448.0f));
+                    float sp = e4m3_to_float(sp_byte);
+                    uint8_t* rec = p_codes ? p_codes + ((((size_t)h * q_count + r) * tiles + tile) * 68) : NULL;
+                    if (rec) rec[64 + b] = sp_byte;
                     for (int i = 0; i < 16; ++i) {
-                        ph[16 * b + i] = e2m1_to_float(float_to_e2m1(p[i] / fmaxf(sp, 1e-30f))) * sp;
+                        uint8_t code = float_to_e2m1(p[i] / fmaxf(sp, 1e-30f));
+                        if (rec) rec[16 * b + i] = code;
+                        ph[16 * b + i] = e2m1_to_float(code) * sp;
                         row_sum += ph[16 * b + i];
                     }
                 }
@@ -673,6 +680,18 @@ void uo_attention_fast_rope(const uint16_t* q, const uint16_t* k, const uint16_t
         }
     free(kmean); free(scratch); free(qmean); free(qc); free(kc); free(vc); free(qsf); free(ksf); free(vsf);
     free(qo); free(ko); free(vo); free(kd); free(vd); free(k_rot);
+}
+
+void uo_attention_fast_rope(const uint16_t* q, const uint16_t* k, const uint16_t* v, const float* rope, int heads_per_table,
+                            int heads, int nq, int nk, int smooth_q, int recip, const float* k_mean, const float* q_mean,
+                            int q_first, int q_count, float* out) {
+    attention_fast_impl(q, k, v, rope, heads_per_table, heads, nq, nk, smooth_q, recip, k_mean, q_mean, q_first, q_count, out, NULL);
+}
+
+/* The same, also returning the P^ codes (see attention_fast_impl). */
+void uo_attention_fast_codes(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk, int smooth_q,
+                             int recip, const float* k_mean, const float* q_mean, float* out, uint8_t* p_codes) {
+    attention_fast_impl(q, k, v, NULL, 1, heads, nq, nk, smooth_q, recip, k_mean, q_mean, 0, nq, out, p_codes);
 }
 
 void uo_attention_fast(const uint16_t* q, const uint16_t* k, const uint16_t* v, int heads, int nq, int nk, int smooth_q,

@@ -90,7 +90,6 @@ struct __align__(128) Fp4Smem {
     float log2_e4m3[128];  // log2 of every non-negative e4m3 byte's value; +inf for the byte 0, so that 2^(x - that) = 0
     uint64_t q_full, k_full[F4_STAGES], k_empty[F4_STAGES], v_full[F4_STAGES], v_empty[F4_STAGES];
     uint64_t s_full[F4_TILES], s_free[F4_TILES], p_ready[F4_TILES], o_full[F4_TILES], drain[F4_TILES];
-    int turn[4];  // per scheduler: whose exponentials are next (see the softmax threads)
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -124,7 +123,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                          const uint32_t* __restrict__ sfk, const uint8_t* __restrict__ v4, const uint32_t* __restrict__ sfv,
                          const float* __restrict__ qk_outer, const float* __restrict__ v_outer, const float* __restrict__ bias,
                          int q_blocks, int smooth_q, __nv_bfloat16* __restrict__ out, TokenLayout out_layout, const __grid_constant__ PeerOutputs peers, int n_queries,
-                         int n_keys, float scale_log2, int* status) {
+                         int n_keys, float scale_log2, uint32_t* __restrict__ p_words, int* status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     Fp4Smem& sm = *reinterpret_cast<Fp4Smem*>(smem_raw);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -133,7 +132,6 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
     const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
     volatile int* abort_flag = &sm.abort_flag;
 
-    if (threadIdx.x < 4) sm.turn[threadIdx.x] = 0;
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
         mbar_init(&sm.q_full, 1);
@@ -315,12 +313,6 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
             // table (a logarithm here would double the block's dependent chain).
             uint32_t codes[8], sf_word = 0;
             const float gain = P_LOG2_GAIN - m_new;
-#ifdef UNICA_F4_TURNS
-            // The two warps of a scheduler (one per query tile) take turns at the exponentials, so that one's run of them
-            // overlaps the other's waits and loads instead of colliding with its run.
-            ok = flag_wait_warp(&sm.turn[warp % 4], 2 * t + g, abort_flag, status, STATUS_WAIT_PARTNER);
-            if (!ok) break;
-#endif
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
                 const float top = ex2(block_max[b] + gain) * (1.0f / 6.0f);
@@ -339,13 +331,12 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
                     codes[2 * b + w] = e2m1x8(r);
                 }
             }
-#ifdef UNICA_F4_TURNS
-            {
-                uint32_t all = codes[0] ^ codes[1] ^ codes[2] ^ codes[3] ^ codes[4] ^ codes[5] ^ codes[6] ^ codes[7];
-                asm volatile("" : "+r"(all));  // the codes exist: the exponentials have been through
-                if (lane == 0) flag_publish(&sm.turn[warp % 4], 2 * t + g + 1);
+            if (p_words && q_row < n_queries) {  // diagnostics: this row's P^ of the tile, 8 words of codes and the 4 scale bytes
+                uint32_t* dst = p_words + ((size_t(head) * n_queries + q_row) * k_tiles + t) * 9;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) dst[i] = codes[i];
+                dst[8] = sf_word;
             }
-#endif
             F4_TRACE(F4_TR_QUANTIZE);
 
             if (t > 0) {  // P.V of the previous tile must have read P, its scales and V's, and written O
@@ -448,7 +439,7 @@ extern "C" int unica_b200_trace_read_fp4(long long* host_out) {
 static int attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk, const uint8_t* v4, const void* sfv,
                          const float* qk_outer, const float* v_outer, const float* bias, int q_blocks, int smooth_q, void* out,
                          void* const* peer_out, int n_peers, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
-                         float scale_log2, int* status, void* stream) {
+                         float scale_log2, uint32_t* p_words, int* status, void* stream) {
     if (!q4 || !sfq || !k4 || !sfk || !v4 || !sfv || !qk_outer || !v_outer || !out) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: null pointer");
     if (heads <= 0 || heads > 65535 || n_queries <= 0 || n_keys <= 0)
         return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4: heads must be in 1..65535, n_queries and n_keys positive");
@@ -465,7 +456,7 @@ static int attention_fp4(const uint8_t* q4, const void* sfq, const uint8_t* k4, 
     attention_fp4_kernel<<<grid, F4_THREADS, smem, static_cast<cudaStream_t>(stream)>>>(
         q4, static_cast<const uint32_t*>(sfq), k4, static_cast<const uint32_t*>(sfk), v4, static_cast<const uint32_t*>(sfv), qk_outer,
         v_outer, bias, q_blocks, smooth_q > 0 ? smooth_q : 1, static_cast<__nv_bfloat16*>(out), to_layout(out_layout), peers, n_queries,
-        n_keys, scale_log2, status);
+        n_keys, scale_log2, p_words, status);
     return unica_check_launch("attention_fp4");
 }
 
@@ -474,7 +465,7 @@ extern "C" int unica_b200_attention_fp4(const uint8_t* q4, const void* sfq, cons
                                         int q_blocks, int smooth_q, void* out, unica_token_layout out_layout, int heads,
                                         int n_queries, int n_keys, float scale_log2, int* status, void* stream) {
     return attention_fp4(q4, sfq, k4, sfk, v4, sfv, qk_outer, v_outer, bias, q_blocks, smooth_q, out, nullptr, 0, out_layout, heads,
-                         n_queries, n_keys, scale_log2, status, stream);
+                         n_queries, n_keys, scale_log2, nullptr, status, stream);
 }
 
 extern "C" int unica_b200_attention_fp4_peers(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk,
@@ -483,5 +474,15 @@ extern "C" int unica_b200_attention_fp4_peers(const uint8_t* q4, const void* sfq
                                               int n_peers, unica_token_layout out_layout, int heads, int n_queries, int n_keys,
                                               float scale_log2, int* status, void* stream) {
     return attention_fp4(q4, sfq, k4, sfk, v4, sfv, qk_outer, v_outer, bias, q_blocks, smooth_q, out, peer_out, n_peers, out_layout, heads,
-                         n_queries, n_keys, scale_log2, status, stream);
+                         n_queries, n_keys, scale_log2, nullptr, status, stream);
+}
+
+extern "C" int unica_b200_attention_fp4_codes(const uint8_t* q4, const void* sfq, const uint8_t* k4, const void* sfk,
+                                              const uint8_t* v4, const void* sfv, const float* qk_outer, const float* v_outer,
+                                              const float* bias, int q_blocks, int smooth_q, void* out, unica_token_layout out_layout,
+                                              int heads, int n_queries, int n_keys, float scale_log2, uint32_t* p_words, int* status,
+                                              void* stream) {
+    if (!p_words) return unica_fail(UNICA_B200_ERR_ARGUMENT, "attention_fp4_codes: null pointer");
+    return attention_fp4(q4, sfq, k4, sfk, v4, sfv, qk_outer, v_outer, bias, q_blocks, smooth_q, out, nullptr, 0, out_layout, heads,
+                         n_queries, n_keys, scale_log2, p_words, status, stream);
 }

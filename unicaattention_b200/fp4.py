@@ -154,3 +154,27 @@ def decode_v4(v4: FP4V) -> tuple[torch.Tensor, torch.Tensor]:
     s = sf[:, :, :, :HEAD_DIM].view(batch, heads, tiles, 32, 4, 4).permute(0, 1, 2, 4, 3, 5).reshape(batch, heads, tiles, HEAD_DIM, 4)
     s = s.transpose(-1, -2)  # channel c = 32 (c / 32) + lane -> [.., tiles, 4, 128]
     return c, s
+
+
+def probability_codes(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_q: int = 512) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The fast kernel run on bfloat16 q, k, v [batch, heads, tokens, 128] with its quantized probabilities kept
+    (unica_b200_attention_fp4_codes): (out, e2m1 codes uint8 [batch, heads, n_queries, tiles, 64] in slot order, e4m3
+    scale bytes uint8 [batch, heads, n_queries, tiles, 4]).  A diagnostic for tests, not a fast path."""
+    import unicaattention_b200 as unica
+
+    q, k, v = unica.readable(q), unica.readable(k), unica.readable(v)
+    batch, heads, n_queries, _ = q.shape
+    n_keys = k.shape[2]
+    tiles = -(-n_keys // 64)
+    q4, k4, v4, qk_outer, v_outer, bias, smooth = unica.kernel_inputs(q, k, v, "attention_fp4", SMOOTH_Q=smooth_q)
+    out = torch.empty_like(q)
+    words = torch.zeros((batch, heads, n_queries, tiles, 9), dtype=torch.int32, device=q.device)
+    with torch.cuda.device(q.device):
+        lib.call("unica_b200_attention_fp4_codes", lib.ptr(q4.codes), lib.ptr(q4.sf), lib.ptr(k4.codes), lib.ptr(k4.sf), lib.ptr(v4.codes),
+                 lib.ptr(v4.sf), lib.ptr(qk_outer), lib.ptr(v_outer), lib.ptr(bias), 0 if bias is None else bias.shape[2], smooth,
+                 lib.ptr(out), unica.token_layout(out), batch * heads, n_queries, n_keys, unica.HEAD_DIM**-0.5 * unica.LOG2E,
+                 lib.ptr(words), lib.ptr(unica.status_word(q.device)), lib.stream())
+    shifts = torch.arange(8, device=q.device, dtype=torch.int32) * 4
+    codes = ((words[..., :8, None] >> shifts) & 15).to(torch.uint8).reshape(batch, heads, n_queries, tiles, 64)
+    scale_bytes = ((words[..., 8:, None] >> (shifts[:4] * 2)) & 255).to(torch.uint8).reshape(batch, heads, n_queries, tiles, 4)
+    return out, codes, scale_bytes

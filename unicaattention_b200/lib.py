@@ -45,6 +45,7 @@ SIGNATURES = {
     "unica_b200_channel_stats_masked": [_P, TokenLayout, _P, _I, _I, _P, _P, _P, _P, _P],
     "unica_b200_selftest_mma_i8": [_P, _P, _I, _I, _I, _I, _P, _P],
     "unica_b200_attention_fp4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
+    "unica_b200_attention_fp4_codes": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P, _P],
     "unica_b200_selftest_mma_nvf4": [_P, _P, _P, _P, _I, _I, _I, _P, _P],
     "unica_b200_peak": [_I, _I, _I, _I, _P, _P],
     "unica_b200_nvfp4_outer": [_P, _P, _P, _I, _I, _P, _P],
