@@ -10,7 +10,7 @@
  *   - every pointer is a device pointer on the current CUDA device unless said otherwise; nothing here allocates,
  *     frees or synchronises (except where an entry point says so); work is queued on `stream` (a cudaStream_t; NULL
  *     is the default stream);
- *   - `heads` is batch * heads; inputs are bf16 [batch, heads, tokens, 128] in any strides with a contiguous last
+ *   - `heads` is batch * heads; inputs are bf16 (or float16) [batch, heads, tokens, 128] in any strides with a contiguous last
  *     dimension and 16-byte aligned tokens, described by unica_token_layout;
  *   - return value 0 = queued; otherwise one of the UNICA_B200_ERR_* codes, and unica_b200_last_error() gives the
  *     message (thread-local).
@@ -37,7 +37,14 @@ extern "C" {
 typedef struct {
     long long batch, head, token;
     int heads;
+    int dtype; /* UNICA_B200_BFLOAT16 (0) or UNICA_B200_FLOAT16: see below */
 } unica_token_layout;
+
+/* Element types of the q, k, v a quantizer or statistics pass reads and of the output an attention kernel writes.
+ * float16 input is rounded to bfloat16 as it is read (the reference converts the tensor first,
+ * unica/__init__.py:236: same numbers, one pass through memory less); a float16 output gets the float16 of the
+ * bfloat16 result. */
+enum { UNICA_B200_BFLOAT16 = 0, UNICA_B200_FLOAT16 = 1 };
 
 enum {
     UNICA_B200_OK = 0,

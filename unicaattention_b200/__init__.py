@@ -77,7 +77,7 @@ if os.environ.get("UNICA_QUIET") != "1" and torch.cuda.is_available():
 
 
 def token_layout(x: torch.Tensor) -> TokenLayout:
-    return TokenLayout(x.stride(0), x.stride(1), x.stride(2), x.shape[1])
+    return TokenLayout(x.stride(0), x.stride(1), x.stride(2), x.shape[1], int(x.dtype == torch.float16))
 
 
 def readable(x: torch.Tensor) -> torch.Tensor:
@@ -102,8 +102,8 @@ def on_their_device(function):
 def _check_input(x: torch.Tensor, what: str) -> None:
     if not x.is_cuda:
         raise ValueError(f"{what} must be on the GPU")
-    if x.dtype != torch.bfloat16:
-        raise TypeError(f"{what} must be bfloat16, got {x.dtype}")
+    if x.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError(f"{what} must be bfloat16 or float16, got {x.dtype}")
     if x.dim() != 4 or x.shape[-1] != HEAD_DIM:
         raise ValueError(f"{what} must be [batch, heads, tokens, {HEAD_DIM}], got {tuple(x.shape)}")
     if x.shape[2] == 0:
@@ -303,7 +303,7 @@ def quantize_v(v: torch.Tensor, layout: int = 2, per_token: bool = False, outlie
     if per_token:
         return v8, scale, tokens
     if outliers:
-        rows = v.gather(-2, keys[..., None].expand(-1, -1, -1, HEAD_DIM)).float() / scale[..., None, :]
+        rows = v.gather(-2, keys[..., None].expand(-1, -1, -1, HEAD_DIM)).to(torch.bfloat16).float() / scale[..., None, :]
         missing = outliers - keys.shape[-1]  # fewer keys than outliers: the rest are none (-1) and zeros
         keys = torch.nn.functional.pad(keys, (0, missing), value=-1)
         rows = torch.nn.functional.pad(rows, (0, 0, 0, missing))
@@ -315,7 +315,7 @@ def v_outliers(v: torch.Tensor, count: int) -> torch.Tensor:
     """The `count` keys of each head with the largest max |v|, int64 [batch, heads, min(count, N)]
     (unica/__init__.py:384-390; the scale of the other keys comes from unica_b200_channel_stats_masked)."""
     low, high = torch.aminmax(v, dim=-1)  # per token, no copy of v
-    return torch.maximum(high, -low).float().topk(min(count, v.shape[-2]), -1).indices
+    return torch.maximum(high, -low).to(torch.bfloat16).float().topk(min(count, v.shape[-2]), -1).indices  # float16 counts as its bfloat16 rounding
 
 
 def decode_v8(v8: torch.Tensor, n: int) -> torch.Tensor:
@@ -385,21 +385,20 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
     """softmax(q k^T / sqrt(d)) v, non-causal.  q [batch, heads, n_queries, 128]; k, v [batch, heads, n_keys, 128]; all
     bfloat16 or all float16, on a B200.  Returns a tensor like q (dtype and strides).  kernel / tile pick the mode, as
     in PRESETS.  inputs: what kernel_inputs() returned for these q, k, v; the kernel then runs alone.
-    out: where to write, a bfloat16 tensor of q's shape (any strides the kernels can address: see readable()), returned.
+    float16 tensors are read as they are, each element rounded to bfloat16 on its way into the quantizers: the result is
+    bit for bit that of converting q, k, v first (what the reference does), without the copies.
+    out: where to write, a tensor of q's shape and dtype (any strides the kernels can address: see readable()), returned.
     peer_out: with out, up to 7 device addresses of tensors laid out like out in other GPUs' memory, mapped into this
     process; the kernel stores every row there as well (see shard.SharedOutput, which also does the barriers this needs).
     Same checks and exceptions as the reference (unica/__init__.py:126-190)."""
     settings = _settings(kernel, tile)
     if out is not None:
-        if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or out.shape != q.shape or out.device != q.device or readable(out) is not out:
-            raise ValueError("out must be a bfloat16 tensor of q's shape on q's device, 16-byte aligned rows with contiguous "
-                             "channels, and q, k, v bfloat16")
+        if out.dtype != q.dtype or out.shape != q.shape or out.device != q.device or readable(out) is not out:
+            raise ValueError("out must be a tensor of q's shape and dtype on q's device, 16-byte aligned rows with contiguous channels")
     elif peer_out:
         raise ValueError("peer_out needs out")
     if not (q.dtype == k.dtype == v.dtype and q.dtype in (torch.bfloat16, torch.float16)):
         raise TypeError(f"q, k, v must all be bfloat16 or all float16, got {q.dtype}, {k.dtype}, {v.dtype}")
-    if inputs is not None and q.dtype != torch.bfloat16:
-        raise TypeError("with inputs=, q, k, v must be bfloat16")
     if not (q.is_cuda and k.is_cuda and v.is_cuda):
         raise ValueError("q, k, v must be on the GPU")
     if q.dim() != 4 or q.shape[-1] != HEAD_DIM:
@@ -413,7 +412,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
         raise ValueError("k and v must hold at least one token")
     if rope is not None:
         rope_table(rope, batch, n_queries, n_keys)
-    if inputs is None and (q.dtype != torch.bfloat16 or heads_per_call(q, k, kernel, tile) < heads):
+    if inputs is None and heads_per_call(q, k, kernel, tile) < heads:
         return in_pieces(q, k, v, kernel, rope, tile, out, peer_out)
     q, k, v = readable(q), readable(k), readable(v)
     if out is None:
@@ -467,13 +466,13 @@ def vram_reserve(device: torch.device) -> int:
 
 def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) -> int:
     """How many heads one call takes without its temporary buffers reaching the reserve.  Per head: the quantized q, k,
-    v and the output, at most 2 bytes per element of q, k, v; 2 more for bf16 copies of float16 inputs; in the fast
+    v and the output, at most 2 bytes per element of q, k, v (float16 inputs are read in place, like bfloat16); in the fast
     mode the smoothing table, one float per key and block of SMOOTH_Q queries (unica/__init__.py:208-232 counts the same
     things).  A small call runs whole."""
     batch, heads, n_queries, _ = q.shape
     n_keys = k.shape[2]
     elements = batch * HEAD_DIM * (n_queries + 2 * n_keys)
-    per_head = max(1, elements * (2 + (2 if q.dtype != torch.bfloat16 else 0)))
+    per_head = max(1, elements * 2)
     smooth = (TILE | tile).get("SMOOTH_Q", 0) if kernel == "attention_fp4" else 0
     if smooth:
         per_head += batch * 4 * math.ceil(n_queries / smooth) * n_keys
@@ -489,8 +488,8 @@ def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) ->
 
 
 def in_pieces(q, k, v, kernel: str, rope, tile: dict, out: torch.Tensor | None = None, peer_out: Sequence[int] = ()) -> torch.Tensor:
-    """attention() a few heads at a time, each piece converted to bfloat16 on its own, into one output in q's dtype and
-    layout (or into `out` and its peers, piece by piece).  Every head has its own statistics and scales, summed in a
+    """attention() a few heads at a time into one output in q's dtype and layout (or into `out` and its peers, piece by
+    piece).  Every head has its own statistics and scales, summed in a
     fixed order, so the result is bit for bit that of one call."""
     step = heads_per_call(q, k, kernel, tile)
     if out is not None:
@@ -500,10 +499,12 @@ def in_pieces(q, k, v, kernel: str, rope, tile: dict, out: torch.Tensor | None =
             attention(q[:, piece], k[:, piece], v[:, piece], kernel, None, rope, out[:, piece], [p + ahead for p in peer_out], **tile)
         return out
     out = torch.empty_like(q)
-    for first in range(0, q.shape[1], step):
-        piece = slice(first, first + step)
-        out[:, piece] = attention(*(x[:, piece].to(torch.bfloat16) for x in (q, k, v)), kernel, None, rope, **tile)
-    return out
+    if readable(out) is not out:  # q in a layout the kernels cannot write: pieces through temporaries
+        for first in range(0, q.shape[1], step):
+            piece = slice(first, first + step)
+            out[:, piece] = attention(q[:, piece], k[:, piece], v[:, piece], kernel, None, rope, **tile)
+        return out
+    return in_pieces(q, k, v, kernel, rope, tile, out)
 
 
 _SM_COUNTS: dict = {}

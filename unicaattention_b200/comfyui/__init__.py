@@ -182,7 +182,8 @@ def fused_rope_forward(module, original, settings: dict):
         k = module.norm_k(module.k(x)).view(batch, tokens, heads, dim)
         v = module.v(x).view(batch, tokens, heads, dim)
         try:
-            out = unica.attention(*(t.transpose(1, 2).to(torch.bfloat16) for t in (q, k, v)), rope=freqs, **settings)
+            half = q.dtype if q.dtype in (torch.bfloat16, torch.float16) else torch.bfloat16
+            out = unica.attention(*(t.transpose(1, 2).to(half) for t in (q, k, v)), rope=freqs, **settings)
         except UNICA_ERRORS as error:
             log.error("unica failed, the model's own attention takes over: %s", error)
             FAILED.append(error)

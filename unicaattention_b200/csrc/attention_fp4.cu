@@ -403,8 +403,7 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int c0 = part * 16 + 2 * i;
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(o[i].x * scale[c0] * inv, o[i].y * scale[c0 + 1] * inv);
-                    w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                    w[i] = output_pair(o[i].x * scale[c0] * inv, o[i].y * scale[c0 + 1] * inv, out_layout.half);
                 }
                 stage_piece(staged, lane, 2 * part, make_uint4(w[0], w[1], w[2], w[3]));
                 stage_piece(staged, lane, 2 * part + 1, make_uint4(w[4], w[5], w[6], w[7]));

@@ -552,8 +552,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 for (int i = 0; i < 4; ++i) {
                     const int c0 = chunk * 8 + 2 * i;
                     const float2 v = o[chunk * 4 + i];
-                    const __nv_bfloat162 pair = __floats2bfloat162_rn(v.x * vs[c0] * inv, v.y * vs[c0 + 1] * inv);
-                    w[i] = *reinterpret_cast<const uint32_t*>(&pair);
+                    w[i] = output_pair(v.x * vs[c0] * inv, v.y * vs[c0 + 1] * inv, out_layout.half);
                 }
                 stage_piece(staged, lane, chunk, make_uint4(w[0], w[1], w[2], w[3]));
             }

@@ -28,6 +28,6 @@ static inline int unica_peer_outputs(const void* out, void* const* peer_out, int
 
 static inline unica::TokenLayout to_layout(const unica_token_layout& l) {
     unica::TokenLayout t;
-    t.batch = l.batch, t.head = l.head, t.token = l.token, t.heads = l.heads;
+    t.batch = l.batch, t.head = l.head, t.token = l.token, t.heads = l.heads, t.half = l.dtype == UNICA_B200_FLOAT16;
     return t;
 }

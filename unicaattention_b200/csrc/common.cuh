@@ -28,10 +28,37 @@ constexpr float LOG2_255 = 7.99435343685886f;
 struct TokenLayout {
     long long batch, head, token;
     int heads;
+    int half;  // the elements are float16, not bfloat16 (see load_bf16x8 / the kernels' epilogues)
     __host__ __device__ __forceinline__ size_t offset(int head_index, int token_index) const {
         return size_t(head_index / heads) * batch + size_t(head_index % heads) * head + size_t(token_index) * token;
     }
 };
+
+// Eight consecutive input elements as bfloat16 bits.  float16 input is rounded to bfloat16 here, in registers (round to
+// nearest even, what torch's .to(bfloat16) does), so every pass downstream sees exactly what it would see had the caller
+// converted the tensor first, without that conversion's trip through memory (the reference converts: unica/__init__.py:236).
+__device__ __forceinline__ uint4 load_bf16x8(const __nv_bfloat16* src, bool half) {
+    uint4 raw = *reinterpret_cast<const uint4*>(src);
+    if (half) {
+        uint32_t* w = reinterpret_cast<uint32_t*>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+            const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+            w[i] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+    }
+    return raw;
+}
+// Two output values as the 32 bits the output tensor takes: bfloat16, or for a float16 tensor the float16 of that
+// bfloat16 (what converting the bfloat16 result gives; exact unless the value leaves float16's range).
+__device__ __forceinline__ uint32_t output_pair(float x, float y, bool half) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(x, y);
+    if (!half) return *reinterpret_cast<const uint32_t*>(&b);
+    const float2 f = __bfloat1622float2(b);
+    const __half2 h = __floats2half2_rn(f.x, f.y);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
 
 // The same output tensor on other GPUs (peer mappings of their memory): the attention kernels store every output row
 // they compute to `out` and to each of these, at the same offsets.  Plain stores only; nothing is read from a peer.

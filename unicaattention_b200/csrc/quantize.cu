@@ -14,8 +14,8 @@ constexpr int THREADS = 256;
 constexpr int STATS_TOKENS = 256;  // tokens per partial sum; the summation order below is part of the contract
 constexpr int STATS_LANES = 16;
 
-__device__ __forceinline__ void load8(float (&v)[8], const __nv_bfloat16* src) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+__device__ __forceinline__ void load8(float (&v)[8], const __nv_bfloat16* src, bool half) {
+    const uint4 raw = load_bf16x8(src, half);
     const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(THREADS) channel_stats_kernel(const __nv_bfloa
     for (int token = token0 + lane; token < end; token += STATS_LANES) {
         if (skip && skip[size_t(head) * n_tokens + token]) continue;
         float v[8];
-        load8(v, x + in.offset(head, token) + chunk * 8);
+        load8(v, x + in.offset(head, token) + chunk * 8, in.half);
         if (rope.table) rope8(v, rope.row(in, head, token), chunk * 8);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -145,8 +145,8 @@ __global__ void __launch_bounds__(THREADS) quantize_rows_int8_kernel(const __nv_
         if (token0 + row < n_tokens) {
             const __nv_bfloat16* src = x + in.offset(head, token0 + row) + chunk * 16;
             float a[8], b[8];
-            load8(a, src);
-            load8(b, src + 8);
+            load8(a, src, in.half);
+            load8(b, src + 8, in.half);
             if (rope.table) {  // rotate first, then take the mean (of the rotated x) away
                 const __half* f = rope.row(in, head, token0 + row);
                 rope8(a, f, chunk * 16);
@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(THREADS) quantize_v_int8_kernel(const __nv_bfl
         const bool valid = token0 + key < n_tokens;
         uint4 raw = make_uint4(0, 0, 0, 0);
         if (valid && !(skip && skip[size_t(head) * n_tokens + token0 + key]))
-            raw = *reinterpret_cast<const uint4*>(v + in.offset(head, token0 + key) + chunk * 8);
+            raw = load_bf16x8(v + in.offset(head, token0 + key) + chunk * 8, in.half);
         *reinterpret_cast<uint4*>(&tile[key][chunk * 8]) = raw;
         if (PER_TOKEN) {  // one scale per key over its channels: the 16 threads of a key share their maxima
             const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);

@@ -96,8 +96,8 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_rows_fp4_kernel(const __
         const int token = SLOTS ? tile * ROWS + slot_key(row) : tile * ROWS + row;
         float v[16];
         if (token < n_tokens) {
-            const uint4* src = reinterpret_cast<const uint4*>(x + in.offset(head, token) + block * 16);
-            const uint4 raw[2] = {src[0], src[1]};
+            const __nv_bfloat16* src = x + in.offset(head, token) + block * 16;
+            const uint4 raw[2] = {load_bf16x8(src, in.half), load_bf16x8(src + 8, in.half)};
             const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(raw);
             const float* mu = mean ? mean + (size_t(head) * groups + token / mean_tokens) * HEAD_DIM + block * 16 : nullptr;
 #pragma unroll
@@ -142,7 +142,7 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_
         const int slot = item / 16, chunk = item % 16, key = t * KEY_TILE + slot_key(slot);
         float f[8];
         if (key < n_tokens) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(v + in.offset(head, key) + chunk * 8);
+            const uint4 raw = load_bf16x8(v + in.offset(head, key) + chunk * 8, in.half);
             const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -201,7 +201,9 @@ __global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfl
         const int slot = item / (HEAD_DIM / 2), c = item % (HEAD_DIM / 2) * 2, key = t * KEY_TILE + slot_key(slot);
         float2 x = make_float2(0.0f, 0.0f);
         if (key < n_keys) {
-            x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(k + in.offset(head, key) + c));
+            const uint32_t two = *reinterpret_cast<const uint32_t*>(k + in.offset(head, key) + c);
+            x = in.half ? __half22float2(*reinterpret_cast<const __half2*>(&two)) : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&two));
+            if (in.half) x = __bfloat1622float2(__floats2bfloat162_rn(x.x, x.y));  // float16 input counts as its bfloat16 rounding
             if (rope.table) {
                 const float2 r = __half22float2(*reinterpret_cast<const __half2*>(rope.row(in, head, key) + c));  // (cos, sin)
                 x = make_float2(__fsub_rn(__fmul_rn(r.x, x.x), __fmul_rn(r.y, x.y)), __fadd_rn(__fmul_rn(r.y, x.x), __fmul_rn(r.x, x.y)));

@@ -39,7 +39,7 @@ class FP4V(NamedTuple):
 
 
 def _layout(x):
-    return lib.TokenLayout(x.stride(0), x.stride(1), x.stride(2), x.shape[1])
+    return lib.TokenLayout(x.stride(0), x.stride(1), x.stride(2), x.shape[1], int(x.dtype == torch.float16))
 
 
 def quantize_fp4_rows(x: torch.Tensor, mean: torch.Tensor | None, pad_to: int = 1, rope=None,

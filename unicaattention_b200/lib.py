@@ -25,10 +25,10 @@ V_CHANNEL, V_TOKEN, V_OUTLIERS = 0, 1, 2
 
 class TokenLayout(ctypes.Structure):
     """include/unica_b200.h unica_token_layout: strides in elements of a [batch, heads, tokens, 128] tensor, and its
-    heads (the reference's TokenLayout, unica/__init__.py:92-100)."""
+    heads (the reference's TokenLayout, unica/__init__.py:92-100); dtype 0: bfloat16, 1: float16."""
 
     _fields_ = [("batch", ctypes.c_longlong), ("head", ctypes.c_longlong), ("token", ctypes.c_longlong),
-                ("heads", ctypes.c_int)]
+                ("heads", ctypes.c_int), ("dtype", ctypes.c_int)]
 
 
 _P, _I, _F, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
