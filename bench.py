@@ -304,7 +304,7 @@ class Bench:
         rows = min(rows, data["tokens"])
         out = unica.attention(q, k, v, **preset)[0, 0, :rows].float().cpu().numpy()[None]
         ref = oracle.reference_fp32(qs, ks, vs, 0, rows)
-        k_mean = unica.rope_stats(k)[0].cpu()
+        k_mean = (unica.rope_stats(k)[0] if mode == "fast" else unica.quantize_k(k)[2]).cpu()  # the mean the call itself takes away
         if mode == "fast":
             emu = oracle.attention_fast(qs, ks, vs, 512, recip=True, k_mean=k_mean, q_mean=unica.rope_stats(q, None, 512)[0].cpu(), q_count=rows)
         else:

@@ -26,6 +26,7 @@
 #ifndef UNICA_B200_H
 #define UNICA_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -104,6 +105,29 @@ int unica_b200_quantize_int8(const void* x, unica_token_layout layout, const flo
 int unica_b200_quantize_v_int8(const void* v, unica_token_layout layout, const float* low, const float* high,
                                const uint8_t* skip, int per_token, int heads, int n_tokens, int8_t* v8, float* v_scale,
                                float* v_token, void* stream);
+
+/* unica_b200_quantize_int8 for Q (block_tokens 128, no mean, no rotation) as a streaming kernel: persistent blocks with
+ * several tiles in flight each; the same bits, about twice the bandwidth. */
+int unica_b200_quantize_q_int8_stream(const void* q, unica_token_layout layout, int heads, int n_tokens, int tiles, int8_t* codes,
+                                      float* scales, void* stream);
+
+/* Statistics and quantization of K in one launch: what unica_b200_channel_stats (per = 0) followed by
+ * unica_b200_quantize_int8 (block_tokens 64, mean = the statistics' mean) do (csrc/flash.cu:287-372; unica/__init__.py:
+ * 363-378, 592-612), with the second read of K served by L2 instead of HBM.  codes, scales as unica_b200_quantize_int8
+ * writes them, tiles = ceil(n_tokens / 64); mean [heads][128] is written too (the order in which its terms are added
+ * differs from unica_b200_channel_stats', so its last bit can; it is fixed for a device and a token count).
+ * scratch: UNICA_B200_FUSED_SCRATCH_BYTES of device memory, 16-byte aligned, that no other call uses at the same time;
+ * its contents do not matter.  status: as for the attention kernels (a block that never sees its group's statistics
+ * gives up after about a second and leaves STATUS 8 there), or NULL.  A cooperative launch of persistent blocks. */
+#define UNICA_B200_FUSED_SCRATCH_BYTES (2u << 20)
+int unica_b200_quantize_k_int8_fused(const void* k, unica_token_layout layout, int heads, int n_tokens, int tiles, void* scratch,
+                                     size_t scratch_bytes, int8_t* codes, float* scales, float* mean, int* status, void* stream);
+
+/* The same for V with one scale per channel: unica_b200_channel_stats followed by unica_b200_quantize_v_int8
+ * (per_token 0, no skip): v8 and v_scale [heads][128] bit for bit as those two write them (minimum and maximum do not
+ * depend on the order they are taken in). */
+int unica_b200_quantize_v_int8_fused(const void* v, unica_token_layout layout, int heads, int n_tokens, void* scratch,
+                                     size_t scratch_bytes, int8_t* v8, float* v_scale, int* status, void* stream);
 
 /* Replaces attention_int8pv_tma (csrc/flash.cu:806-959; launched from unica/__init__.py:179-189).  The accurate mode:
  * S = Q8.K8^T on tcgen05 kind::i8, softmax in the log2 domain against each 64-key tile's own maximum, P as u8,

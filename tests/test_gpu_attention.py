@@ -21,7 +21,7 @@ def run(q, k, v, preset):
 
     out = unica.attention(q.cuda(), k.cuda(), v.cuda(), **unica.PRESETS[preset])
     unica.check_status()
-    k_mean = unica.rope_stats(k.cuda())[0].cpu()
+    k_mean = unica.quantize_k(k.cuda())[2].cpu()  # the mean the call itself took away
     return out, k_mean
 
 

@@ -255,9 +255,49 @@ def quantize_int8(x: torch.Tensor, mean: torch.Tensor | None, block: int, rope: 
     x8 = torch.empty(batch, heads, tiles, HEAD_DIM // 16, block, 16, dtype=torch.int8, device=x.device)
     scale = torch.empty(batch, heads, tiles, device=x.device)
     mean = None if mean is None else mean.float().contiguous()
+    if block == Q_SCALE_BLOCK and mean is None and rope is None:  # the streaming form of the same kernel
+        lib.call("unica_b200_quantize_q_int8_stream", lib.ptr(x), token_layout(x), batch * heads, n, tiles, lib.ptr(x8), lib.ptr(scale), lib.stream())
+        return x8, scale
     lib.call("unica_b200_quantize_int8" + ("_rope" if rope is not None else ""), lib.ptr(x), token_layout(x), lib.ptr(mean),
              *rope_args(rope, x), batch * heads, n, block, tiles, lib.ptr(x8), lib.ptr(scale), lib.stream())
     return x8, scale
+
+
+FUSED_SCRATCH_BYTES = 2 << 20  # include/unica_b200.h UNICA_B200_FUSED_SCRATCH_BYTES
+
+
+@on_their_device
+def quantize_k(k: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """K's mean over the tokens taken away and the rest in INT8 with a scale per 64 keys, in one launch that reads K from
+    HBM once (unica_b200_quantize_k_int8_fused): what rope_stats(k)[0] and quantize_int8(k, mean, 64) give, except that
+    the mean's terms are added in another (fixed) order.  Returns codes, scales, mean [batch, heads, 128]."""
+    _check_input(k, "k")
+    k = readable(k)
+    batch, heads, n, _ = k.shape
+    tiles = math.ceil(n / K_SCALE_BLOCK)
+    k8 = torch.empty(batch, heads, tiles, HEAD_DIM // 16, K_SCALE_BLOCK, 16, dtype=torch.int8, device=k.device)
+    scale = torch.empty(batch, heads, tiles, device=k.device)
+    mean = torch.empty(batch, heads, HEAD_DIM, device=k.device)
+    scratch = torch.empty(FUSED_SCRATCH_BYTES, dtype=torch.uint8, device=k.device)
+    lib.call("unica_b200_quantize_k_int8_fused", lib.ptr(k), token_layout(k), batch * heads, n, tiles, lib.ptr(scratch), FUSED_SCRATCH_BYTES,
+             lib.ptr(k8), lib.ptr(scale), lib.ptr(mean), lib.ptr(status_word(k.device)), lib.stream())
+    return k8, scale, mean
+
+
+@on_their_device
+def quantize_v_channel(v: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """quantize_v(v) with its statistics pass folded in (unica_b200_quantize_v_int8_fused): the same bits, V read from HBM
+    once."""
+    _check_input(v, "v")
+    v = readable(v)
+    batch, heads, n, _ = v.shape
+    tiles = math.ceil(n / V8_PAD_KEYS)
+    v8 = torch.empty(batch, heads, tiles, 4, HEAD_DIM, 16, dtype=torch.int8, device=v.device)
+    scale = torch.empty(batch, heads, HEAD_DIM, device=v.device)
+    scratch = torch.empty(FUSED_SCRATCH_BYTES, dtype=torch.uint8, device=v.device)
+    lib.call("unica_b200_quantize_v_int8_fused", lib.ptr(v), token_layout(v), batch * heads, n, lib.ptr(scratch), FUSED_SCRATCH_BYTES,
+             lib.ptr(v8), lib.ptr(scale), lib.ptr(status_word(v.device)), lib.stream())
+    return v8, scale
 
 
 def decode_int8(x8: torch.Tensor, n: int) -> torch.Tensor:
@@ -355,15 +395,18 @@ def kernel_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str
         v4, v_outer = quantize_v4(v)
         return q4, k4, v4, qk_outer, v_outer, bias, smooth
     q8, q_scale = quantize_int8(q, None, Q_SCALE_BLOCK, rope, tiles=q_tiles)
-    k_mean = rope_stats(k, rope)[0]  # softmax cancels the mean
-    k8, k_scale = quantize_int8(k, k_mean, K_SCALE_BLOCK, rope)
+    if rope is None:  # statistics and quantizer in one launch
+        k8, k_scale, _ = quantize_k(k)
+    else:
+        k_mean = rope_stats(k, rope)[0]  # softmax cancels the mean
+        k8, k_scale = quantize_int8(k, k_mean, K_SCALE_BLOCK, rope)
     if settings["V_TOKEN"]:
         v8, v_scale, v_token = quantize_v(v, per_token=True)
         return q8, q_scale, k8, k_scale, v8, v_scale, v_token, lib.V_TOKEN
     if settings["V_OUTLIERS"]:
         v8, v_scale, keys, rows = quantize_v(v, outliers=settings["V_OUTLIERS"])
         return q8, q_scale, k8, k_scale, v8, v_scale, (keys, rows), lib.V_OUTLIERS
-    v8, v_scale = quantize_v(v)
+    v8, v_scale = quantize_v_channel(v)
     return q8, q_scale, k8, k_scale, v8, v_scale, None, lib.V_CHANNEL
 
 

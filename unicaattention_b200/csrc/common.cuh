@@ -126,6 +126,7 @@ enum Status : int {
     STATUS_WAIT_FREE = 5,     // a buffer was never released
     STATUS_WAIT_STAGE = 6,    // the producer never got a stage back
     STATUS_WAIT_PARTNER = 7,  // the other thread of a query row never published its value
+    STATUS_WAIT_GROUP = 8,    // a block of a one-launch quantizer never saw its group's statistics
 };
 
 constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second

@@ -6,24 +6,12 @@
 // Numerics follow the reference bit for bit (bench/emulate.py quant(), csrc/flash.cu:334-372 and 590-630):
 // amax over the scale block, scale = max(amax * (1/127), 1e-12), code = clamp(rint(x / scale), -127, 127) with an IEEE
 // division and round-half-even.
-#include "common.cuh"
+#include "quantize_int8.cuh"
 
 namespace unica {
 
-constexpr int THREADS = 256;
 constexpr int STATS_TOKENS = 256;  // tokens per partial sum; the summation order below is part of the contract
 constexpr int STATS_LANES = 16;
-
-__device__ __forceinline__ void load8(float (&v)[8], const __nv_bfloat16* src, bool half) {
-    const uint4 raw = load_bf16x8(src, half);
-    const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(pairs[i]);
-        v[2 * i] = f.x;
-        v[2 * i + 1] = f.y;
-    }
-}
 
 // Sum, min and max per channel over a block of 256 tokens of one head (the reference's rope_stats, csrc/flash.cu:287-327,
 // without RoPE): thread = (lane of 16 tokens, chunk of 8 channels); lane l adds tokens l, l + 16, ... in order, then
@@ -97,162 +85,28 @@ __global__ void __launch_bounds__(HEAD_DIM) channel_stats_finish_kernel(const fl
     high[o] = hi;
 }
 
-__device__ __forceinline__ float block_max(float x, float* scratch) {
-#pragma unroll
-    for (int d = 16; d > 0; d /= 2) x = fmaxf(x, __shfl_xor_sync(0xffffffff, x, d));
-    if (threadIdx.x % 32 == 0) scratch[threadIdx.x / 32] = x;
-    __syncthreads();
-    x = scratch[0];
-#pragma unroll
-    for (int w = 1; w < THREADS / 32; ++w) x = fmaxf(x, scratch[w]);
-    return x;
-}
-
-// clamp(rint(x / scale), -127, 127) as the low byte of the result, bit for bit the IEEE division's answer, without the
-// division: q = x * (1 / scale) is within 2^-23 |q| of the true quotient, so its rounding can differ only when q sits
-// that close to a half; then (a few elements in 10^5) the division is done.  Rounding and the float -> int step are one
-// addition: q + 1.5 * 2^23 has rint(q), in two's complement, in its low mantissa bits.
-__device__ __forceinline__ uint32_t code_bits(float x, float scale, float inv) {
-    const float q = x * inv;
-    float t = q + MAGIC;                                 // MAGIC + rint(q)
-    if (fabsf(fabsf(q - (t - MAGIC)) - 0.5f) < 1e-4f) t = rintf(__fdiv_rn(x, scale)) + MAGIC;  // |q| <= 128: 2^-23 |q| < 1.6e-5
-    return __float_as_uint(fminf(fmaxf(t, MAGIC - 127.0f), MAGIC + 127.0f));
-}
-
-__device__ __forceinline__ uint32_t pack4(const float* v, float scale, float inv) {
-    const uint32_t lo = __byte_perm(code_bits(v[0], scale, inv), code_bits(v[1], scale, inv), 0x0040);
-    const uint32_t hi = __byte_perm(code_bits(v[2], scale, inv), code_bits(v[3], scale, inv), 0x0040);
-    return __byte_perm(lo, hi, 0x5410);
-}
-
-// Q or K (minus `mean`, [heads][128] or null) in INT8 with one scale per tile of ROWS tokens (128: Q, 64: K).
-// One block per tile; the tile stays in registers between the max and the write, so HBM is read once.
-// codes: [heads][tiles][8 chunks of 16 channels][ROWS][16] bytes; rows past n_tokens and tiles past the last are zeros.
-// scales: [heads][tiles].  Grid (tiles, heads).
+// One block per tile.  Grid (tiles, heads).
 template <int ROWS>
 __global__ void __launch_bounds__(THREADS) quantize_rows_int8_kernel(const __nv_bfloat16* __restrict__ x, TokenLayout in,
                                                                       const float* __restrict__ mean, int n_tokens,
                                                                       int8_t* __restrict__ codes, float* __restrict__ scales,
                                                                       RopeTable rope) {
-    constexpr int ITEMS = ROWS * 8 / THREADS;  // (row, 16-channel chunk) items per thread
     __shared__ float scratch[THREADS / 32];
-    const int head = blockIdx.y, tile = blockIdx.x, token0 = tile * ROWS;
-    float v[ITEMS][16];
-    float local = 0.0f;
-#pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-        const int item = it * THREADS + threadIdx.x, row = item % ROWS, chunk = item / ROWS;
-        if (token0 + row < n_tokens) {
-            const __nv_bfloat16* src = x + in.offset(head, token0 + row) + chunk * 16;
-            float a[8], b[8];
-            load8(a, src, in.half);
-            load8(b, src + 8, in.half);
-            if (rope.table) {  // rotate first, then take the mean (of the rotated x) away
-                const __half* f = rope.row(in, head, token0 + row);
-                rope8(a, f, chunk * 16);
-                rope8(b, f, chunk * 16 + 8);
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float m0 = mean ? mean[head * HEAD_DIM + chunk * 16 + i] : 0.0f;
-                const float m1 = mean ? mean[head * HEAD_DIM + chunk * 16 + 8 + i] : 0.0f;
-                v[it][i] = a[i] - m0;
-                v[it][8 + i] = b[i] - m1;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) v[it][i] = 0.0f;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) local = fmaxf(local, fabsf(v[it][i]));
-    }
-    const float scale = fmaxf(block_max(local, scratch) * (1.0f / 127.0f), 1e-12f);
-    const float inv = __frcp_rn(scale);
-    if (threadIdx.x == 0) scales[size_t(head) * gridDim.x + tile] = scale;
-    int8_t* out = codes + (size_t(head) * gridDim.x + tile) * (ROWS * HEAD_DIM);
-#pragma unroll
-    for (int it = 0; it < ITEMS; ++it) {
-        const int item = it * THREADS + threadIdx.x, row = item % ROWS, chunk = item / ROWS;
-        uint4 w;
-        w.x = pack4(&v[it][0], scale, inv);
-        w.y = pack4(&v[it][4], scale, inv);
-        w.z = pack4(&v[it][8], scale, inv);
-        w.w = pack4(&v[it][12], scale, inv);
-        *reinterpret_cast<uint4*>(out + (chunk * ROWS + row) * 16) = w;
-    }
+    const int head = blockIdx.y, tile = blockIdx.x;
+    rows_int8_tile<ROWS>(x, in, mean ? mean + head * HEAD_DIM : nullptr, head, tile, n_tokens,
+                         codes + (size_t(head) * gridDim.x + tile) * (ROWS * HEAD_DIM), scales + size_t(head) * gridDim.x + tile, rope, scratch);
 }
 
-// V in INT8, one block per tile of 64 keys.  PER_TOKEN false: one scale per channel, max(|low|, |high|) * (1/127) from
-// the channel's min and max over the head (low, high: [heads][128]); true: one scale per key over its channels, and
-// v_token [heads][tiles][2][64] gets log2 s and 1 / s of the tile's keys (zeros past n_tokens).  skip: [heads][n_tokens],
-// 1 = the key is written as zeros (outlier keys), or null.
-// v8: [heads][tiles][4 chunks of 16 keys][128 channels][16] bytes: the K-major B operand of P.V.  v_scale [heads][128].
 template <bool PER_TOKEN>
 __global__ void __launch_bounds__(THREADS) quantize_v_int8_kernel(const __nv_bfloat16* __restrict__ v, TokenLayout in,
                                                                    const float* __restrict__ low, const float* __restrict__ high,
                                                                    const uint8_t* __restrict__ skip, int n_tokens,
                                                                    int8_t* __restrict__ v8, float* __restrict__ v_scale,
                                                                    float* __restrict__ v_token) {
-    // The tile goes through shared memory as bf16, keys x channels, and comes out transposed: a thread then owns one
-    // channel and 16 keys, i.e. one 16-byte row of the operand image, and a warp writes 512 contiguous bytes.
-    __shared__ __align__(16) __nv_bfloat16 tile[KEY_TILE][HEAD_DIM];
-    __shared__ float key_scale[KEY_TILE], key_inv[KEY_TILE];
-    const int head = blockIdx.y, t = blockIdx.x, token0 = t * KEY_TILE;
-    const int chunk = threadIdx.x % 16;  // 8 channels
-#pragma unroll
-    for (int it = 0; it < KEY_TILE * 16 / THREADS; ++it) {
-        const int key = it * (THREADS / 16) + threadIdx.x / 16;
-        const bool valid = token0 + key < n_tokens;
-        uint4 raw = make_uint4(0, 0, 0, 0);
-        if (valid && !(skip && skip[size_t(head) * n_tokens + token0 + key]))
-            raw = load_bf16x8(v + in.offset(head, token0 + key) + chunk * 8, in.half);
-        *reinterpret_cast<uint4*>(&tile[key][chunk * 8]) = raw;
-        if (PER_TOKEN) {  // one scale per key over its channels: the 16 threads of a key share their maxima
-            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(pairs[i]);
-                amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-            }
-#pragma unroll
-            for (int d = 8; d > 0; d /= 2) amax = fmaxf(amax, __shfl_xor_sync(0xffffffff, amax, d));
-            if (chunk == 0) {
-                const float s = fmaxf(amax * (1.0f / 127.0f), 1e-12f);
-                key_scale[key] = s;
-                key_inv[key] = __frcp_rn(s);
-                float* tok = v_token + (size_t(head) * gridDim.x + t) * 2 * KEY_TILE;
-                tok[key] = valid ? log2f(s) : 0.0f;
-                tok[KEY_TILE + key] = valid ? __fdiv_rn(1.0f, s) : 0.0f;
-            }
-        }
-    }
-    __syncthreads();
-    const int c = threadIdx.x % HEAD_DIM;
-    float scale = 1.0f, inv = 1.0f;
-    if (!PER_TOKEN) {  // max(|low|, |high|) * (1/127) from the channel's minimum and maximum over the head
-        scale = fmaxf(fmaxf(high[head * HEAD_DIM + c], -low[head * HEAD_DIM + c]) * (1.0f / 127.0f), 1e-12f);
-        inv = __frcp_rn(scale);
-    }
-    if (t == 0 && threadIdx.x < HEAD_DIM) v_scale[head * HEAD_DIM + c] = scale;
-    uint4* dst = reinterpret_cast<uint4*>(v8 + (size_t(head) * gridDim.x + t) * (KEY_TILE * HEAD_DIM));
-#pragma unroll
-    for (int it = 0; it < KEY_TILE / 16 * HEAD_DIM / THREADS; ++it) {
-        const int keys = (it * (THREADS / HEAD_DIM) + threadIdx.x / HEAD_DIM) * 16;  // this thread's 16 keys
-        uint32_t w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint32_t b[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int key = keys + 4 * i + j;
-                const float x = __bfloat162float(tile[key][c]);
-                b[j] = PER_TOKEN ? code_bits(x, key_scale[key], key_inv[key]) : code_bits(x, scale, inv);
-            }
-            w[i] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
-        }
-        dst[(keys / 16) * HEAD_DIM + c] = make_uint4(w[0], w[1], w[2], w[3]);
-    }
+    __shared__ VTileSmem sm;
+    const int head = blockIdx.y;
+    v_int8_tile<PER_TOKEN>(v, in, low ? low + head * HEAD_DIM : nullptr, high ? high + head * HEAD_DIM : nullptr, skip, head, blockIdx.x,
+                           gridDim.x, n_tokens, v8, v_scale, v_token, sm);
 }
 
 }  // namespace unica

@@ -39,6 +39,9 @@ SIGNATURES = {
     "unica_b200_channel_stats_static": [_P, TokenLayout, _I, _I, _I, _P, _P, _P, _P],
     "unica_b200_quantize_int8": [_P, TokenLayout, _P, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_v_int8": [_P, TokenLayout, _P, _P, _P, _I, _I, _I, _P, _P, _P, _P],
+    "unica_b200_quantize_q_int8_stream": [_P, TokenLayout, _I, _I, _I, _P, _P, _P],
+    "unica_b200_quantize_k_int8_fused": [_P, TokenLayout, _I, _I, _I, _P, ctypes.c_size_t, _P, _P, _P, _P, _P],
+    "unica_b200_quantize_v_int8_fused": [_P, TokenLayout, _I, _I, _P, ctypes.c_size_t, _P, _P, _P, _P],
     "unica_b200_attention_int8": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, TokenLayout, _I, _I, _I, _F, _P, _P],
     "unica_b200_attention_int8_peers": [_P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _P, _P, _I, TokenLayout, _I, _I, _I, _F, _P, _P],
     "unica_b200_attention_fp4_peers": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P, _I, TokenLayout, _I, _I, _I, _F, _P, _P],
