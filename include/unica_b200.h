@@ -4,7 +4,7 @@
  * looks an `extern "C" __global__` symbol up by name and launches it with positional arguments (unica/cuda.py:138-160;
  * call sites in unica/__init__.py).  This library replaces that boundary by host entry points, one per reference
  * kernel launch, with plain pointers and sizes: the launch geometry, shared-memory sizes and tensor-memory use are its
- * own business.  A binding needs nothing but dlopen/ctypes.
+ * own business.  A binding needs nothing but dlopen / ctypes.
  *
  * Conventions
  *   - every pointer is a device pointer on the current CUDA device unless said otherwise; nothing here allocates,
@@ -77,12 +77,18 @@ int unica_b200_channel_stats_masked(const void* x, unica_token_layout layout, co
 /* No counterpart in the reference.  unica_b200_channel_stats for callers that cannot provide the `partial` scratch:
  * code running where device memory cannot be had (a hook inside a pipeline that keeps the card full, a C host without
  * an allocator of its own) or must not be asked for (cudaMalloc / cudaFree stall the device).  The partial sums go to
- * a 9 MiB array built into the library, which each GPU that loads the library holds until the process exits.
+ * a 9 MiB array built into the library.  CUDA loads a library's device code into a GPU's context when it is first
+ * used there (lazy module loading), so the 9 MiB are reserved on a GPU by the first call of this entry point (or of any
+ * kernel of the same module) on that GPU, and held until the process exits or the device is reset: make that first call
+ * while memory is still to be had; on a card that is already full it fails with UNICA_B200_ERR_CUDA and a message
+ * that says so.
  *   - limit: heads * ceil(n_tokens / 256) <= 6144 (40 heads x 32760 tokens need 5120); larger calls are refused with
  *     UNICA_B200_ERR_ARGUMENT and should use unica_b200_channel_stats;
- *   - allocates and frees nothing, here or in anything it calls; mean, low, high are still the caller's;
- *   - the first call on each device also looks the array's device address up (the device must be current): make that
- *     first call before starting any stream capture;
+ *   - apart from that first load of the module it allocates and frees nothing, here or in anything it calls; mean,
+ *     low, high are still the caller's;
+ *   - the first call on each device also looks the array's device address up (the device must be current) and keeps
+ *     it: make that first call before starting any stream capture, and do not reset the device afterwards (the kept
+ *     address would point into the old context);
  *   - all calls on a device share the one array, which keeps whatever the last call left in it (nothing in it needs
  *     clearing between calls); two calls whose kernels may run at the same time, e.g. on different streams, race on
  *     it and give wrong statistics: keep them ordered.

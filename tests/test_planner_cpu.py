@@ -9,7 +9,7 @@ GiB = 2**30
 
 
 def plan(monkeypatch, free, reserve, shape=(1, 40, 32760, 128), dtype=torch.bfloat16, kernel=unica.DEFAULT_KERNEL, **tile):
-    monkeypatch.setattr(unica, "free_vram", lambda device: free)
+    monkeypatch.setattr(unica, "free_vram", lambda device, fresh=False: free)
     monkeypatch.setattr(unica, "vram_reserve", lambda device: reserve)
     q = torch.empty(shape, dtype=dtype, device="meta")
     return unica.heads_per_call(q, q, kernel, tile)
@@ -47,4 +47,21 @@ def test_free_vram_is_asked_seldom(monkeypatch):
     assert unica.free_vram("gpu") == 5 * GiB and unica.free_vram("gpu") == 5 * GiB and len(calls) == 1
     monkeypatch.setattr(unica, "FREE_VRAM_MAX_AGE", -1.0)
     assert unica.free_vram("gpu") == 5 * GiB and len(calls) == 2
+    unica._FREE_VRAM.clear()
+
+
+def test_a_large_call_asks_the_driver_again(monkeypatch):
+    """A call that needs more than an eighth of the remembered free memory does not trust the remembered figure."""
+    answers = iter([(24 * GiB, 180 * GiB), (5 * GiB, 180 * GiB)])
+    calls = []
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device: (calls.append(device), next(answers))[1])
+    monkeypatch.setattr(unica, "vram_reserve", lambda device: 4 * GiB)
+    unica._FREE_VRAM.clear()
+
+    small = torch.empty((1, 2, 1024, 128), dtype=torch.bfloat16, device="meta")
+    assert unica.heads_per_call(small, small, unica.DEFAULT_KERNEL, {}) == 2 and len(calls) == 1  # the remembered figure will do
+    big = torch.empty((1, 40, 118320, 128), dtype=torch.bfloat16, device="meta")
+    per_head = 128 * 3 * 118320 * 2
+    assert 40 * per_head > 24 * GiB // unica.STALE_FRACTION
+    assert unica.heads_per_call(big, big, unica.DEFAULT_KERNEL, {}) == (5 * GiB - 4 * GiB) // per_head and len(calls) == 2
     unica._FREE_VRAM.clear()

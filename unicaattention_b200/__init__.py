@@ -163,9 +163,21 @@ def block_stats(x: torch.Tensor, rope: torch.Tensor | None = None) -> torch.Tens
 
 
 def wave_layout(heads: int, n_queries: int, n_keys: int, v_token: int, device) -> dict:
-    """The reference picks between a 4-warp and an 8-warp block per call (unica/__init__.py:281-285).  Here the block is
-    fixed (two query tiles sharing every K and V tile), so there is nothing to pick: always {}."""
+    """The reference picks between a 4-warp and an 8-warp block per call to fill its last wave (unica/__init__.py:281-285).
+    Here every kernel has one block shape (accurate: one tile of 128 queries per block of 16 warps, one block per SM;
+    fast: two query tiles per block of 12 warps), so there is nothing to pick: always {}.  What the last wave costs is
+    what wave_plan() reports."""
     return {}
+
+
+def wave_plan(heads: int, n_queries: int, kernel: str = DEFAULT_KERNEL, device=None) -> dict:
+    """How a call's blocks fall on the SMs: blocks (all of equal length: every query tile meets every key), blocks per wave
+    (one per SM), waves, and the share of the SM time of those waves that does work.  batch * heads for `heads`."""
+    rows = 256 if kernel == "attention_fp4" else 128
+    blocks = heads * math.ceil(n_queries / rows)
+    per_wave = sm_count(torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device))
+    waves = math.ceil(blocks / per_wave)
+    return {"blocks": blocks, "per_wave": per_wave, "waves": waves, "efficiency": blocks / (waves * per_wave)}
 
 
 def source(kernel: str, tile: dict) -> str:
@@ -464,7 +476,16 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
     if n_queries == 0:
         return out
     if inputs is None:
-        inputs = kernel_inputs(q, k, v, kernel, rope, **tile)
+        try:
+            inputs = kernel_inputs(q, k, v, kernel, rope, **tile)
+        except torch.cuda.OutOfMemoryError:
+            # The planner's picture of free memory was out of date (something took memory since it asked): forget it and
+            # go by heads, fewer than before, on what is free now.
+            _FREE_VRAM.pop(q.device, None)
+            torch.cuda.empty_cache()
+            if heads == 1:
+                raise
+            return in_pieces(q, k, v, kernel, rope, tile, out, peer_out, max(1, min(heads // 2, heads_per_call(q, k, kernel, tile))))
     if kernel == "attention_fp4":
         q4, k4, v4, qk_outer, v_outer, bias, smooth = inputs
         lib.call("unica_b200_attention_fp4_peers", lib.ptr(q4.codes), lib.ptr(q4.sf), lib.ptr(k4.codes), lib.ptr(k4.sf),
@@ -488,14 +509,15 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, kernel: str = D
 
 _FREE_VRAM: dict = {}  # device -> (bytes free, when asked)
 FREE_VRAM_MAX_AGE = 0.25  # seconds: the driver's answer costs 0.1 to 1 ms of host time, too much to pay on every call
+STALE_FRACTION = 8  # ... but a call that needs more than an eighth of what was free then asks again (weights may have come in since)
 
 
-def free_vram(device: torch.device) -> int:
+def free_vram(device: torch.device, fresh: bool = False) -> int:
     """Bytes the driver has free on the device (plus what torch's allocator holds unused); does not wait for the GPU.
-    The driver is asked at most every FREE_VRAM_MAX_AGE seconds per device."""
+    The driver is asked at most every FREE_VRAM_MAX_AGE seconds per device, unless `fresh`."""
     now = time.monotonic()
     cached = _FREE_VRAM.get(device)
-    if cached is None or now - cached[1] > FREE_VRAM_MAX_AGE:
+    if fresh or cached is None or now - cached[1] > FREE_VRAM_MAX_AGE:
         free, _ = torch.cuda.mem_get_info(device)
         cached = _FREE_VRAM[device] = (free, now)
     return cached[0]
@@ -520,6 +542,8 @@ def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) ->
     if smooth:
         per_head += batch * 4 * math.ceil(n_queries / smooth) * n_keys
     free, reserve = free_vram(q.device), vram_reserve(q.device)
+    if heads * per_head > free // STALE_FRACTION:  # a call this size must not trust an answer something else may have outdated
+        free = free_vram(q.device, fresh=True)
     if heads * per_head <= min(reserve // SMALL_CALL_FRACTION, free):
         step = heads
     else:
@@ -530,11 +554,12 @@ def heads_per_call(q: torch.Tensor, k: torch.Tensor, kernel: str, tile: dict) ->
     return step
 
 
-def in_pieces(q, k, v, kernel: str, rope, tile: dict, out: torch.Tensor | None = None, peer_out: Sequence[int] = ()) -> torch.Tensor:
+def in_pieces(q, k, v, kernel: str, rope, tile: dict, out: torch.Tensor | None = None, peer_out: Sequence[int] = (),
+              step: int | None = None) -> torch.Tensor:
     """attention() a few heads at a time into one output in q's dtype and layout (or into `out` and its peers, piece by
     piece).  Every head has its own statistics and scales, summed in a
     fixed order, so the result is bit for bit that of one call."""
-    step = heads_per_call(q, k, kernel, tile)
+    step = step or heads_per_call(q, k, kernel, tile)
     if out is not None:
         for first in range(0, q.shape[1], step):
             piece = slice(first, first + step)
@@ -547,7 +572,7 @@ def in_pieces(q, k, v, kernel: str, rope, tile: dict, out: torch.Tensor | None =
             piece = slice(first, first + step)
             out[:, piece] = attention(q[:, piece], k[:, piece], v[:, piece], kernel, None, rope, **tile)
         return out
-    return in_pieces(q, k, v, kernel, rope, tile, out)
+    return in_pieces(q, k, v, kernel, rope, tile, out, (), step)
 
 
 _SM_COUNTS: dict = {}

@@ -6,6 +6,8 @@
 // Numerics follow the reference bit for bit (bench/emulate.py quant(), csrc/flash.cu:334-372 and 590-630):
 // amax over the scale block, scale = max(amax * (1/127), 1e-12), code = clamp(rint(x / scale), -127, 127) with an IEEE
 // division and round-half-even.
+#include <cstdio>
+
 #include "quantize_int8.cuh"
 
 namespace unica {
@@ -153,8 +155,10 @@ extern "C" int unica_b200_channel_stats_rope(const void* x, unica_token_layout l
 // one: an attention hook that runs inside a sampler whose memory manager has already filled the card with staged
 // weights (an allocation there fails, or pushes something else out), a host written in C that owns no device
 // allocator, or a latency-critical loop that must not enter the CUDA allocator because cudaMalloc and cudaFree stall
-// the whole device.  For them the partial sums live in the array below, which is part of the library image: every GPU
-// that loads the library sets these bytes aside once, at load, and keeps them until the process ends.
+// the whole device.  For them the partial sums live in the array below, which is part of the library image.  CUDA loads
+// the image into a GPU's context lazily, on the first use of anything in this module on that GPU, and that is when the
+// bytes are set aside there (until the process ends or the device is reset): the first call must come while memory is
+// still available.
 constexpr int STATIC_STATS_RECORDS = 6144;  // (head, 256-token block) pairs: 40 heads x 32760 tokens need 5120
 static __device__ __align__(256) float g_stats_scratch[size_t(STATIC_STATS_RECORDS) * 3 * HEAD_DIM];  // 9 MiB
 
@@ -172,7 +176,13 @@ static float* stats_scratch_of_current_device(int* error) {
         float* p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_stats_scratch);
         if (e != cudaSuccess || !p) {
-            *error = unica_fail(UNICA_B200_ERR_CUDA, cudaGetErrorString(e));
+            static thread_local char message[256];
+            snprintf(message, sizeof message,
+                     "channel_stats_static: the built-in scratch could not be set up on this device (%s); the first call on a device "
+                     "loads the module and reserves 9 MiB, which needs free device memory",
+                     cudaGetErrorString(e));
+            cudaGetLastError();  // the error is reported here, not by the next launch check
+            *error = unica_fail(UNICA_B200_ERR_CUDA, message);
             return nullptr;
         }
         address[device] = p;  // the same value whichever thread gets here first
