@@ -54,3 +54,15 @@ def test_slice_heads_on_plain_tuples():
     got = shard.slice_heads((a, Pair(a, b), (a, b), None, 512), slice(1, 3))
     assert got[0].shape == (1, 2, 3) and isinstance(got[1], Pair) and got[1].sf.shape == (1, 2, 2, 2)
     assert got[2][1].shape == (1, 2, 2, 2) and got[3] is None and got[4] == 512
+
+
+def test_host_groups_are_small_at_both_ends():
+    from unicaattention_b200.host import group_sizes
+
+    for heads in (1, 3, 5, 7, 10, 20, 30, 40, 64):
+        for largest in (None, 1, 4, 100):
+            sizes = group_sizes(heads, largest)
+            assert sum(sizes) == heads and all(s >= 1 for s in sizes)
+            assert max(sizes) <= (largest or max(1, -(-heads // 8)))
+            assert sizes[0] <= 2 and sizes[-1] <= 2
+    assert group_sizes(40) == [2, 4, 5, 5, 5, 3, 5, 5, 4, 2]

@@ -44,17 +44,32 @@ __device__ __forceinline__ unsigned load_acquire(const unsigned* p) {
 }
 __device__ __forceinline__ void store_release(unsigned* p, unsigned v) { asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 
+// A thread's share of every tile copy: the same two 16-byte pieces (row, piece of the row) of each tile, so their offsets
+// in the stage and from the tile's first token are worked out once.
+struct FetchLane {
+    uint32_t in_stage[KEY_TILE * 16 / STREAM_THREADS];
+    long long from_tile[KEY_TILE * 16 / STREAM_THREADS];  // in elements
+    int row[KEY_TILE * 16 / STREAM_THREADS];
+    __device__ __forceinline__ explicit FetchLane(long long token_stride) {
+#pragma unroll
+        for (int it = 0; it < KEY_TILE * 16 / STREAM_THREADS; ++it) {
+            const int piece = it * STREAM_THREADS + threadIdx.x, piece16 = piece % 16;
+            row[it] = piece / 16;
+            in_stage[it] = staged_offset(row[it], piece16);
+            from_tile[it] = row[it] * token_stride + piece16 * 8;
+        }
+    }
+};
 // 64 tokens x 256 bytes into a stage (laid out as staged_chunk describes), 16 bytes per copy, two copies per thread; rows
-// past the last token arrive as zeros.  head_base: the head's first token; token_stride in elements.
-__device__ __forceinline__ void ring_fetch(uint8_t* stage, const __nv_bfloat16* __restrict__ head_base, long long token_stride, int token0,
-                                           int n_tokens) {
+// past the last token arrive as zeros.  tile_base: the tile's first token (token0) in the head.
+__device__ __forceinline__ void ring_fetch(uint8_t* stage, const __nv_bfloat16* __restrict__ tile_base, int token0, int n_tokens,
+                                           const FetchLane& lane) {
+    const uint32_t stage_address = smem_u32(stage);
 #pragma unroll
     for (int it = 0; it < KEY_TILE * 16 / STREAM_THREADS; ++it) {
-        const int piece = it * STREAM_THREADS + threadIdx.x, row = piece / 16, piece16 = piece % 16;
-        const bool valid = token0 + row < n_tokens;
-        const __nv_bfloat16* src = head_base + (valid ? token0 + row : 0) * token_stride + piece16 * 8;
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(stage) + staged_offset(row, piece16)), "l"(src),
-                     "r"(valid ? 16 : 0)
+        const bool valid = token0 + lane.row[it] < n_tokens;
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(stage_address + lane.in_stage[it]),
+                     "l"(valid ? tile_base + lane.from_tile[it] : tile_base), "r"(valid ? 16 : 0)
                      : "memory");
     }
 }
@@ -75,11 +90,18 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) quantize_q_int8_stream_kern
     // 32-bit counters throughout: the host checks that heads * tiles fits, and 64-bit divisions here would cost more than
     // the quantization itself
     const int mine = (heads * tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);  // this block's tiles
-    int fetched = 0;  // half tiles whose copies have been started
+    const FetchLane lane(in.token);
+    int fetched = 0, fetch_t = 0;  // half tiles whose copies have been started; the tile of the head the next one is in
+    const __nv_bfloat16* fetch_head = x;
     auto fetch = [&]() {  // the next half tile of 64 queries
         if (fetched < 2 * mine) {
-            const int tile = int(blockIdx.x) + (fetched / 2) * int(gridDim.x), head = tile / tiles, t = tile - head * tiles;
-            ring_fetch(ring + (fetched % RING_STAGES) * RING_TILE_BYTES, x + in.offset(head, 0), in.token, t * 128 + (fetched % 2) * KEY_TILE, n_tokens);
+            if (fetched % 2 == 0) {  // a new tile: one division for both halves
+                const int tile = int(blockIdx.x) + (fetched / 2) * int(gridDim.x), head = tile / tiles;
+                fetch_t = tile - head * tiles;
+                fetch_head = x + in.offset(head, 0);
+            }
+            const int token0 = fetch_t * 128 + (fetched % 2) * KEY_TILE;
+            ring_fetch(ring + (fetched % RING_STAGES) * RING_TILE_BYTES, fetch_head + token0 * in.token, token0, n_tokens, lane);
         }
         ++fetched;
         ring_commit();
@@ -129,17 +151,22 @@ __global__ void __launch_bounds__(STREAM_THREADS, 2) quantize_head_int8_kernel(c
 
     // The block's stream of tiles: per head its tiles once for the statistics, then once more to be quantized.  The fetches
     // walk it with counters of their own (no divisions on the way).
+    const FetchLane copies(in.token);
+    const long long tile_step = KEY_TILE * in.token;
     int fetch_round = 0, fetch_pass = 0, fetch_tile = tile0, fetched = 0;
-    const __nv_bfloat16* fetch_base = x + in.offset(group, 0);
+    const __nv_bfloat16* fetch_first = x + in.offset(group, 0) + tile0 * tile_step;  // the block's first tile of the head
+    const __nv_bfloat16* fetch_at = fetch_first;
     auto fetch = [&]() {
         if (fetch_round < rounds && mine > 0) {
-            ring_fetch(ring + (fetched % RING_STAGES) * RING_TILE_BYTES, fetch_base, in.token, fetch_tile * KEY_TILE, n_tokens);
+            ring_fetch(ring + (fetched % RING_STAGES) * RING_TILE_BYTES, fetch_at, fetch_tile * KEY_TILE, n_tokens, copies);
+            fetch_at += tile_step;
             if (++fetch_tile == tile1) {
                 fetch_tile = tile0;
                 if (++fetch_pass == 2) {
                     fetch_pass = 0;
-                    if (++fetch_round < rounds) fetch_base = x + in.offset(group + fetch_round * groups, 0);
+                    if (++fetch_round < rounds) fetch_first = x + in.offset(group + fetch_round * groups, 0) + tile0 * tile_step;
                 }
+                fetch_at = fetch_first;
             }
         }
         ++fetched;

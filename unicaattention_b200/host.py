@@ -1,6 +1,6 @@
-"""attention() for tensors that live in host memory: the heads go through the GPU in groups, so that the copy of the next
-group's q, k, v, the kernels of this one and the copy of the previous group's output run at the same time (three
-streams).  Heads are independent (every head has its own statistics and scales), so the result is bit for bit that of
+"""attention() for tensors that live in host memory: the heads go through the GPU in groups (small ones first and last,
+see group_sizes), so that the copy of the next group's q, k, v, the kernels of this one and the copy of the previous
+group's output run at the same time (three streams).  Heads are independent (every head has its own statistics and scales), so the result is bit for bit that of
 one call on the whole tensors.
 
 The reference has no such call: its callers hold their tensors on the GPU.  It is here for hosts that do not (the C-ABI
@@ -22,6 +22,22 @@ def _streams(device: torch.device):
     return _STREAMS[device]
 
 
+def group_sizes(heads: int, largest: int | None = None) -> list[int]:
+    """Heads per group, in order: small groups first and last, so that little of the first copy in and of the last copy
+    out is left without kernels to hide behind, and groups of `largest` (default: an eighth of the heads) in between.
+    40 heads: 2, 4, 5, 5, 5, 3, 5, 5, 4, 2."""
+    largest = max(1, -(-heads // 8)) if largest is None else max(1, largest)
+    front, back, left, size = [], [], heads, min(2, largest)
+    while left > 0:
+        for side in (front, back):
+            take = min(size, left)
+            if take:
+                side.append(take)
+                left -= take
+        size = min(2 * size, largest)
+    return front + back[::-1]
+
+
 def attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,
                    device: torch.device | int | None = None, heads_per_group: int | None = None, **settings) -> torch.Tensor:
     """softmax(q k^T / sqrt(d)) v for q [batch, heads, n_queries, 128], k, v [batch, heads, n_keys, 128] in HOST memory
@@ -40,15 +56,24 @@ def attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch
         out = torch.empty(q.shape, dtype=q.dtype, pin_memory=True)
     elif out.shape != q.shape or out.dtype != q.dtype or out.is_cuda:
         raise ValueError("out must be a host tensor like q")
-    group = heads_per_group or max(1, -(-heads // 5))
+    if heads_per_group is None:
+        # the largest group: about an eighth of the heads, picked so that its blocks fill their last wave of SMs well
+        kernel = settings.get("kernel", unica.DEFAULT_KERNEL)
+        candidates = range(max(1, -(-heads // 10)), max(1, -(-heads // 6)) + 1)
+        largest = max(candidates, key=lambda g: (round(unica.wave_plan(batch * g, q.shape[2], kernel, device)["efficiency"], 2), g))
+        sizes = group_sizes(heads, largest)
+    else:
+        sizes = [min(heads_per_group, heads - f) for f in range(0, heads, heads_per_group)]
     with torch.cuda.device(device):
         compute = torch.cuda.current_stream(device)
         copy_in, copy_out = _streams(device)
         qd, kd, vd = (torch.empty(x.shape, dtype=x.dtype, device=device) for x in (q, k, v))
         copy_in.wait_stream(compute)  # the staging memory may still be in use by work queued before this call
         copy_out.wait_stream(compute)
-        for first in range(0, heads, group):
-            piece = slice(first, min(first + group, heads))
+        first = 0
+        for size in sizes:
+            piece = slice(first, first + size)
+            first += size
             with torch.cuda.stream(copy_in):
                 for dst, src in ((qd, q), (kd, k), (vd, v)):
                     dst[:, piece].copy_(src[:, piece], non_blocking=True)
