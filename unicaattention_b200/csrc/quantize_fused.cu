@@ -26,7 +26,7 @@ namespace unica {
 
 constexpr int STREAM_THREADS = 512;  // two blocks of 16 warps per SM at 64 registers a thread
 constexpr int FUSED_LANES = STREAM_THREADS / 16;  // token lanes: thread = (lane, chunk of 8 channels)
-constexpr int FUSED_MAX_GROUPS = 64;
+constexpr int FUSED_MAX_GROUPS = 12;  // heads in flight at most: more would only thin out the blocks a head gets
 constexpr int RING_STAGES = 4;                       // tiles in flight per block: three ahead of the one in hand
 constexpr int RING_TILE_BYTES = KEY_TILE * HEAD_DIM * 2;  // 16 KB
 constexpr int RING_BYTES = RING_STAGES * RING_TILE_BYTES;
@@ -324,7 +324,8 @@ static int fused_plan(const void* kernel, const char* name, int heads, int n_tok
     in_flight = in_flight > FUSED_MAX_GROUPS ? FUSED_MAX_GROUPS : in_flight;
     in_flight = in_flight > blocks ? blocks : in_flight;
     *per_group = blocks / int(in_flight);
-    *groups = heads < in_flight ? heads : int(in_flight);
+    const int rounds = int((heads + in_flight - 1) / in_flight);
+    *groups = (heads + rounds - 1) / rounds;  // the same number of rounds with the heads spread evenly over them
     *grid = *groups * *per_group;
     return UNICA_B200_OK;
 }
