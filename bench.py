@@ -404,8 +404,8 @@ class Bench:
         configs = {}
         if not args.no_configs:
             for workload in ("image", "hires"):
-                if workload == args.workload or (workload == "image" and self.world > 1 and WORKLOADS["image"][1] % self.world):
-                    continue
+                if workload == args.workload:
+                    continue  # (30 heads over 4 or 8 ranks: uneven slices, which both ways of gathering take)
                 other = self.load(workload, None, args.hires_tokens if workload == "hires" else None)
                 entry = {"shape": [other["batch"], other["heads"], other["tokens"], 128],
                          "inputs": {"q_channel_spread": channel_spread(other["dev"][0]), "k_channel_spread": channel_spread(other["dev"][1]),
@@ -425,14 +425,14 @@ class Bench:
                 entry["roofline"]["frac_of_tensor_mix_microbench"] = entry["roofline"]["achieved"] / entry["roofline"]["tensor_mix_microbench"]
             # DRAM traffic of the attention kernel per launch: one ncu capture on 40 heads x 8192 tokens scaled by heads x
             # tokens (every K/V tile comes from HBM once and is re-read from L2, so traffic grows with the token count)
-            per_token_bytes = {"per_channel": 540.6, "fast": 433.4}.get(args.mode)
+            per_token_bytes = {"per_channel": 552.7, "fast": 441.9}.get(args.mode)
             head["roofline"]["traffic"] = per_token_bytes * batch * heads * tokens / self.world if per_token_bytes else None
             head["roofline"]["traffic_unit"] = "bytes per launch per GPU, derived: ncu dram bytes of a 40 x 8192 capture scaled by heads x tokens"
             line = {"metric": metric_name(args.mode, batch, heads, tokens), "value": head["value"], "unit": "TOPS", "n_gpus": self.world,
                     "steps": args.steps, "warmup": args.warmup, "ms_per_step": head["ms_per_step"], "higher_is_better": True,
                     "scaling": "strong", "vs_baseline": None, "dtype": dtype_of(args.mode), "data": "synthetic",
                     "config": config_of(args, batch, heads, tokens) | {"input_channel_spread": spreads} | ({"gather": self.gather_note} if self.world > 1 else {}), "clocks": clocks, "e2e": e2e,
-                    "gpu_launches": head["gpu_launches"], "roofline": head["roofline"], "quantization": head["quantization"],
+                    "gpu_launches": head["gpu_launches"], "roofline": head["roofline"], "quantization": head["quantization"], "grid": head.get("grid"),
                     "accuracy": head.get("accuracy"), "modes": modes, "configs": configs,
                     "published_other_hardware": {"rtx5080_tops": PUBLISHED_RTX5080_TOPS.get(args.mode)}}
             if not args.no_cpu and self.world == 1:
