@@ -330,10 +330,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             const int valid = MASKED ? n_keys - t * KEY_TILE : KEY_TILE;
             const uint32_t ts = t_s + buf * 64;
             TRACE(7);
+            // Per token: the keys' scales came with the V tile.  That tile has long landed when its scores are there (the
+            // scores were issued after it), so the barrier is only looked at, and the look is started before the wait for
+            // the scores so that its latency hides behind that.
+            const bool scales_there = !V_TOKEN || mbar_try(&sm.kv_full[stage], kv_phase);
             if (!flag_wait_warp(&sm.s_done[buf], t + 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
             TRACE(0);
             EVENT(0, t);
-            if (V_TOKEN && !mbar_wait_warp(&sm.kv_full[stage], kv_phase, abort_flag, status, STATUS_WAIT_TILE)) return false;
+            if (V_TOKEN && !__all_sync(0xffffffffu, scales_there) && !mbar_wait_warp(&sm.kv_full[stage], kv_phase, abort_flag, status, STATUS_WAIT_TILE))
+                return false;
             tc_fence_after();
 #if defined(UNICA_STUB) && (UNICA_STUB & 1)  // measurement only: the protocol without the arithmetic (results are wrong)
             sm.st[record][row] = make_float2(0.0f, 1.0f);
