@@ -182,9 +182,12 @@ int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layout, const fl
 /* Replaces smooth_bias (csrc/flash.cu:1254-1322; unica/__init__.py:503-521): q_mean[block] . (k - k_mean) in FP32 for
  * every block of smoothed queries and every key, times scale_log2.  q_mean [heads][q_blocks][128], k_mean [heads][128].
  * bias [heads][q_blocks][ceil(n_keys / 64) * 64] in the slot order of K4's tiles; the slots past the last key hold -inf
- * (the attention kernel adds the table to the scores, which takes those slots out of the softmax). */
+ * (the attention kernel adds the table to the scores, which takes those slots out of the softmax).  Computed on the
+ * tensor core (kind::tf32, every FP32 value as two tf32 parts, three products): accurate to about 2^-22 of
+ * sum |q_mean| |k - k_mean|.  status: as for unica_b200_attention_int8 (the kernel waits for its tensor-core
+ * instructions with a time limit). */
 int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean, int heads,
-                           int q_blocks, int n_keys, float scale_log2, float* bias, void* stream);
+                           int q_blocks, int n_keys, float scale_log2, float* bias, int* status, void* stream);
 
 /* ---- RoPE inside the quantizers -----------------------------------------------------------------------------------
  * Replace the reference's `freqs, freqs_batch` kernel arguments (rope_chunk / load_chunk_rope, csrc/flash.cu:250-279;
@@ -204,7 +207,7 @@ int unica_b200_quantize_fp4_rows_rope(const void* x, unica_token_layout layout, 
                                       int n_tokens, int rows_per_tile, int tiles, uint8_t* codes, uint8_t* sf, void* stream);
 int unica_b200_smooth_bias_rope(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
                                 const void* rope, long long rope_batch_stride, int heads, int q_blocks, int n_keys,
-                                float scale_log2, float* bias, void* stream);
+                                float scale_log2, float* bias, int* status, void* stream);
 
 /* No counterpart in the reference (which runs on one GPU).  unica_b200_attention_int8 for a job that shards the heads
  * over several GPUs and wants every GPU to end up with all heads: each output row is stored to `out` and, at the same
@@ -223,7 +226,9 @@ int unica_b200_attention_int8_peers(const int8_t* q8, const float* q_scale, cons
  * result exact, so a wrong lane or layout cannot hide).  One tcgen05.mma kind::i8 chain D[128 x n] = A[128 x k] . B[n x k]^T
  * with A (u8 if a_unsigned, else s8) and B (s8) given as the shared-memory images described above
  * ([k / 16][rows][16] bytes); d gets int32 [128][n] row-major.  The operands are described as the attention
- * kernels describe theirs; variant must be 0.
+ * kernels describe theirs; variant must be 0.  a_unsigned = 2: the same chain as kind::tf32 (what
+ * unica_b200_smooth_bias issues): the images hold floats, [k / 16][rows][4], k / 4 of them per row, and d receives the
+ * bits of the float results.
  * Allocates a status word and synchronises the stream: not for the hot path. */
 int unica_b200_selftest_mma_i8(const void* a_image, const void* b_image, int n, int k, int a_unsigned, int variant,
                                int32_t* d, void* stream);

@@ -30,6 +30,23 @@ def test_mma_i8_exact(n, k, unsigned):
     assert np.array_equal(got, expected), f"{np.sum(got != expected)} of {got.size} differ"
 
 
+@pytest.mark.parametrize("n,k_values", [(64, 32), (32, 8), (128, 16)])
+def test_mma_tf32_exact(n, k_values):
+    """kind::tf32 as the smoothing-table kernel issues it: small integers, and values that need tf32's 11 bits."""
+    from unicaattention_b200 import lib
+
+    rng = np.random.default_rng(n + k_values)
+    a = rng.integers(-1023, 1024, (128, k_values)).astype(np.float32)  # 11 significant bits: exact in tf32
+    b = (rng.integers(-15, 16, (n, k_values)) / 4.0).astype(np.float32)
+    expected = (a.astype(np.float64) @ b.astype(np.float64).T).astype(np.float32)  # sums below 2^24 / 4: exact in float
+    a_dev = torch.from_numpy(image(a.view(np.uint8).reshape(128, -1))).cuda()
+    b_dev = torch.from_numpy(image(b.view(np.uint8).reshape(n, -1))).cuda()
+    d = torch.full((128, n), -1, dtype=torch.int32, device="cuda")
+    lib.call("unica_b200_selftest_mma_i8", lib.ptr(a_dev), lib.ptr(b_dev), n, 4 * k_values, 2, 0, lib.ptr(d), lib.stream())
+    got = d.cpu().numpy().view(np.float32)
+    assert np.array_equal(got, expected), f"{np.sum(got != expected)} of {got.size} differ"
+
+
 E2M1 = np.array([0, 0.5, 1, 1.5, 2, 3, 4, 6, -0.0, -0.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
 SCALE_BYTES = np.array([0x30, 0x38, 0x3C, 0x40, 0x44, 0x28], dtype=np.uint8)  # 0.5, 1, 1.5, 2, 3, 0.25 in e4m3
 

@@ -599,10 +599,12 @@ __global__ void __launch_bounds__(128) selftest_mma_i8_kernel(const uint8_t* __r
     tc_fence_after();
     const uint32_t tmem = tmem_base;
     if (threadIdx.x == 0) {
-        const uint32_t idesc = idesc_i8(!a_unsigned, 128, n);
         for (int ks = 0; ks < k / 32; ++ks) {
-            mma_i8_ss(tmem, smem_desc(smem_u32(a_s) + ks * 2 * 128 * 16, 128 * 16, 128), smem_desc(smem_u32(b_s) + ks * 2 * n * 16, n * 16, 128),
-                      idesc, ks > 0);
+            const uint64_t a_desc = smem_desc(smem_u32(a_s) + ks * 2 * 128 * 16, 128 * 16, 128), b_desc = smem_desc(smem_u32(b_s) + ks * 2 * n * 16, n * 16, 128);
+            if (a_unsigned == 2)  // kind::tf32: the images hold floats, k / 4 per row; an instruction takes 8 = 32 bytes of a row
+                mma_tf32_ss(tmem, a_desc, b_desc, idesc_tf32(128, n), ks > 0);
+            else
+                mma_i8_ss(tmem, a_desc, b_desc, idesc_i8(!a_unsigned, 128, n), ks > 0);
         }
         mma_commit(&done);
     }

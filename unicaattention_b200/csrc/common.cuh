@@ -573,6 +573,32 @@ __host__ __device__ constexpr uint32_t idesc_i8(bool a_signed, int m, int n) {
     return (2u << 4) | (uint32_t(a_signed) << 7) | (1u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
 }
 
+// Instruction descriptor of kind::tf32: D f32; A and B tf32 (32-bit words whose low 13 bits the tensor core ignores);
+// both K-major; M x N.  The operand images have the byte geometry of the 8-bit ones: 16 bytes (four values) per row and
+// chunk, an instruction takes K = 8 values = two chunks.
+__host__ __device__ constexpr uint32_t idesc_tf32(int m, int n) {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+__device__ __forceinline__ void mma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(uint32_t(accumulate))
+        : "memory");
+}
+// x = hi + lo up to 2^-24 |x|, both with tf32's 11 significant bits (round to nearest): three tf32 products
+// hi.hi + lo.hi + hi.lo then carry an FP32 product to about 2^-22.
+__device__ __forceinline__ void tf32_split(float x, float& hi, float& lo) {
+    uint32_t bits;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x));
+    hi = __uint_as_float(bits);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(bits) : "f"(x - hi));  // the difference is exact
+    lo = __uint_as_float(bits);
+}
+
 // D[tmem] (+)= A[smem] . B[smem]^T, issued by one thread.
 __device__ __forceinline__ void mma_i8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
     asm volatile(

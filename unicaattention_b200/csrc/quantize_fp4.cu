@@ -183,68 +183,202 @@ __global__ void __launch_bounds__(FP4_THREADS) quantize_v_fp4_kernel(const __nv_
 
 // The part of the scores that Q smoothing took out, added back exactly (bench/emulate.py:308-309; the reference's
 // smooth_bias kernel, csrc/flash.cu:1254-1322, gets there with three bf16 MMAs): for every block of `mean_tokens`
-// queries and every key, q_mean[block] . (k - k_mean) in FP32, times scale_log2, keys of a tile in slot order, 0 past
-// the last key.  bias: [heads][q_blocks][k_tiles * 64].  Grid (k_tiles, heads).
-constexpr int BIAS_ROW = HEAD_DIM + 4;  // row stride in floats: 16-byte aligned rows, no bank conflicts for 16-byte loads
-constexpr int BIAS_BATCH = 64;          // query blocks per pass
-constexpr int BIAS_SMEM = (KEY_TILE * BIAS_ROW + BIAS_BATCH * HEAD_DIM) * 4;  // 66560 bytes
+// queries and every key, q_mean[block] . (k - k_mean) to FP32 accuracy, times scale_log2, keys of a tile in slot
+// order, -inf past the last key.  bias: [heads][q_blocks][k_tiles * 64].
+//
+// On the tensor core: D[128 keys][64 query blocks] = Kc . Qm^T as kind::tf32, every FP32 value split into two tf32
+// parts and the product taken as hi.hi + lo.hi + hi.lo.  Keys are the rows, so a thread of the epilogue holds one
+// key's terms for 16 query blocks and a warp's stores are 128 contiguous bytes of one table row.  A block keeps the
+// images of its 64 query blocks' means and walks over pairs of key tiles of one head, half the channels at a time:
+// centred K (rotated first when a table is given) -> images of 64 channels -> 24 instructions of K = 8, into one of two
+// accumulators.  The instructions of one half run while the other half's images are made and the pair before is
+// written out.  Grid (strips of key-tile pairs, heads, ceil(q_blocks / 64)).
+constexpr int BIAS_KEYS = 2 * KEY_TILE;  // rows of an instruction: two K4 tiles
+constexpr int BIAS_BLOCKS = 64;          // query blocks per pass (columns)
+constexpr int BIAS_THREADS = 512;
+constexpr int BIAS_HALF = HEAD_DIM / 2;  // channels per set of images
+struct __align__(128) BiasSmem {
+    float k_hi[2][BIAS_HALF / 4][BIAS_KEYS][4];  // operand images, one per half: [channel / 4][row][4 values]
+    float k_lo[2][BIAS_HALF / 4][BIAS_KEYS][4];
+    float q_hi[HEAD_DIM / 4][BIAS_BLOCKS][4];
+    float q_lo[HEAD_DIM / 4][BIAS_BLOCKS][4];
+    uint64_t done[2];  // the instructions of a half have completed (its images are free; after the second, the accumulator is whole)
+    uint32_t tmem_base;
+    int abort_flag;
+};
+constexpr uint32_t IDESC_BIAS = idesc_tf32(BIAS_KEYS, BIAS_BLOCKS);
 
-__global__ void __launch_bounds__(FP4_THREADS) smooth_bias_kernel(const __nv_bfloat16* __restrict__ k, TokenLayout in,
-                                                                   const float* __restrict__ k_mean, const float* __restrict__ q_mean,
-                                                                   int q_blocks, int n_keys, float scale_log2, float* __restrict__ bias,
-                                                                   RopeTable rope) {
-    extern __shared__ __align__(16) float bias_smem[];
-    float (*centred)[BIAS_ROW] = reinterpret_cast<float (*)[BIAS_ROW]>(bias_smem);                            // [KEY_TILE][BIAS_ROW]
-    float (*qm)[HEAD_DIM] = reinterpret_cast<float (*)[HEAD_DIM]>(bias_smem + KEY_TILE * BIAS_ROW);          // [BIAS_BATCH][HEAD_DIM]
-    const int head = blockIdx.y, t = blockIdx.x, k_tiles = gridDim.x;
-    for (int item = threadIdx.x; item < KEY_TILE * HEAD_DIM / 2; item += FP4_THREADS) {  // a pair of channels each
-        const int slot = item / (HEAD_DIM / 2), c = item % (HEAD_DIM / 2) * 2, key = t * KEY_TILE + slot_key(slot);
-        float2 x = make_float2(0.0f, 0.0f);
-        if (key < n_keys) {
-            const uint32_t two = *reinterpret_cast<const uint32_t*>(k + in.offset(head, key) + c);
-            x = in.half ? __half22float2(*reinterpret_cast<const __half2*>(&two)) : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&two));
-            if (in.half) x = __bfloat1622float2(__floats2bfloat162_rn(x.x, x.y));  // float16 input counts as its bfloat16 rounding
-            if (rope.table) {
-                const float2 r = __half22float2(*reinterpret_cast<const __half2*>(rope.row(in, head, key) + c));  // (cos, sin)
-                x = make_float2(__fsub_rn(__fmul_rn(r.x, x.x), __fmul_rn(r.y, x.y)), __fadd_rn(__fmul_rn(r.y, x.x), __fmul_rn(r.x, x.y)));
-            }
-            x.x -= k_mean[head * HEAD_DIM + c], x.y -= k_mean[head * HEAD_DIM + c + 1];
-        }
-        centred[slot][c] = x.x, centred[slot][c + 1] = x.y;
+// x = hi + lo with hi rounded to tf32's 11 significant bits (to nearest, ties away from zero) and lo exact: the tensor
+// core drops what lo has below its own 11 bits, at most 2^-23 |x|.
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+    hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
+    lo = x - hi;
+}
+__device__ __forceinline__ void split4(const float (&x)[4], float4& hi, float4& lo) {
+    split_tf32(x[0], hi.x, lo.x);
+    split_tf32(x[1], hi.y, lo.y);
+    split_tf32(x[2], hi.z, lo.z);
+    split_tf32(x[3], hi.w, lo.w);
+}
+
+__global__ void __launch_bounds__(BIAS_THREADS, 1) smooth_bias_kernel(const __nv_bfloat16* __restrict__ k, TokenLayout in,
+                                                                      const float* __restrict__ k_mean, const float* __restrict__ q_mean,
+                                                                      int q_blocks, int n_keys, float scale_log2, float* __restrict__ bias,
+                                                                      RopeTable rope, int* status) {
+    extern __shared__ __align__(128) uint8_t bias_smem_raw[];
+    BiasSmem& sm = *reinterpret_cast<BiasSmem*>((reinterpret_cast<uintptr_t>(bias_smem_raw) + 127) & ~uintptr_t(127));
+    const int head = blockIdx.y, b0 = blockIdx.z * BIAS_BLOCKS, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE, pairs = (k_tiles + 1) / 2;
+    volatile int* abort_flag = &sm.abort_flag;
+    if (threadIdx.x == 0) {
+        sm.abort_flag = 0;
+        mbar_init(&sm.done[0], 1);
+        mbar_init(&sm.done[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // Thread = (two key slots, eight query blocks): per four channels it reads two 16-byte pieces of the keys' centred rows
-    // and eight of the block means (broadcast) for 64 multiply-adds, i.e. a sixth of a shared-memory load per multiply-add.
-    constexpr int KEYS = 2, MINE = BIAS_BATCH / (FP4_THREADS / (KEY_TILE / KEYS));  // 8 blocks per thread
-    const int slot = threadIdx.x % (KEY_TILE / KEYS), group = threadIdx.x / (KEY_TILE / KEYS);  // slots `slot` and `slot + 32`
-    for (int b0 = 0; b0 < q_blocks; b0 += BIAS_BATCH) {
-        __syncthreads();
-        for (int item = threadIdx.x; item < BIAS_BATCH * HEAD_DIM; item += FP4_THREADS) {
-            const int b = b0 + item / HEAD_DIM;
-            qm[item / HEAD_DIM][item % HEAD_DIM] = b < q_blocks ? q_mean[(size_t(head) * q_blocks + b) * HEAD_DIM + item % HEAD_DIM] : 0.0f;
+    if (warp == 0) tmem_alloc(&sm.tmem_base, 2 * BIAS_BLOCKS);
+    // the means of this pass's query blocks, rows past the last block zero
+    for (int item = threadIdx.x; item < BIAS_BLOCKS * (HEAD_DIM / 4); item += BIAS_THREADS) {
+        const int r = item % BIAS_BLOCKS, c4 = item / BIAS_BLOCKS;
+        float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (b0 + r < q_blocks) {
+            const float4 m = *reinterpret_cast<const float4*>(q_mean + (size_t(head) * q_blocks + b0 + r) * HEAD_DIM + c4 * 4);
+            x[0] = m.x, x[1] = m.y, x[2] = m.z, x[3] = m.w;
         }
-        __syncthreads();
-        float dot[KEYS][MINE] = {};
-#pragma unroll 2
-        for (int c = 0; c < HEAD_DIM; c += 4) {
-            const float4 k0 = *reinterpret_cast<const float4*>(&centred[slot][c]);
-            const float4 k1 = *reinterpret_cast<const float4*>(&centred[slot + KEY_TILE / KEYS][c]);
+        float4 hi, lo;
+        split4(x, hi, lo);
+        *reinterpret_cast<float4*>(sm.q_hi[c4][r]) = hi;
+        *reinterpret_cast<float4*>(sm.q_lo[c4][r]) = lo;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = sm.tmem_base;
+    const float* mean = k_mean + head * HEAD_DIM;
+    // A thread makes the images of one key (threads in key order: conflict-free 16-byte stores), 16 channels of each half
+    const int r = threadIdx.x % BIAS_KEYS, g0 = 2 * (threadIdx.x / BIAS_KEYS);  // groups of 8 channels g0, g0 + 1 of a half
+    auto key_of = [&](int pair) { return (2 * pair + r / KEY_TILE) * KEY_TILE + slot_key(r % KEY_TILE); };
+    auto fetch = [&](int pair, int half, uint4 (&raw)[2]) {  // 32 contiguous bytes of the key's row
+        const int key = key_of(pair);
+        if (key < n_keys) {
+            const __nv_bfloat16* src = k + in.offset(head, key) + half * BIAS_HALF + g0 * 8;
+            raw[0] = load_bf16x8(src, in.half), raw[1] = load_bf16x8(src + 8, in.half);
+        } else {
+            raw[0] = raw[1] = make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto make_images = [&](int pair, int half, const uint4 (&raw)[2]) {
+        const int key = key_of(pair);
+        const bool live = key < n_keys;
 #pragma unroll
-            for (int j = 0; j < MINE; ++j) {
-                const float4 qc = *reinterpret_cast<const float4*>(&qm[group * MINE + j][c]);
-                dot[0][j] = fmaf(qc.w, k0.w, fmaf(qc.z, k0.z, fmaf(qc.y, k0.y, fmaf(qc.x, k0.x, dot[0][j]))));  // channels in order
-                dot[1][j] = fmaf(qc.w, k1.w, fmaf(qc.z, k1.z, fmaf(qc.y, k1.y, fmaf(qc.x, k1.x, dot[1][j]))));
-            }
-        }
+        for (int i = 0; i < 2; ++i) {
+            const int g = g0 + i, channel = half * BIAS_HALF + g * 8;
+            float x[8];
+            const __nv_bfloat162* two = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
 #pragma unroll
-        for (int j = 0; j < MINE; ++j) {
-            const int b = b0 + group * MINE + j;
-            if (b < q_blocks) {
-                float* row = bias + (size_t(head) * q_blocks + b) * (size_t(k_tiles) * KEY_TILE) + t * KEY_TILE;
-                // slots past the last key get -inf: added to a score it keeps the slot out of the softmax
-                row[slot] = t * KEY_TILE + slot_key(slot) < n_keys ? dot[0][j] * scale_log2 : -INFINITY;
-                row[slot + KEY_TILE / KEYS] = t * KEY_TILE + slot_key(slot + KEY_TILE / KEYS) < n_keys ? dot[1][j] * scale_log2 : -INFINITY;
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(two[j]);
+                x[2 * j] = f.x, x[2 * j + 1] = f.y;
             }
+            if (live) {
+                if (rope.table) rope8(x, rope.row(in, head, key), channel);
+                const float4 m0 = *reinterpret_cast<const float4*>(mean + channel), m1 = *reinterpret_cast<const float4*>(mean + channel + 4);
+                x[0] -= m0.x, x[1] -= m0.y, x[2] -= m0.z, x[3] -= m0.w, x[4] -= m1.x, x[5] -= m1.y, x[6] -= m1.z, x[7] -= m1.w;
+            }
+            float4 hi, lo;
+            split4(reinterpret_cast<const float(&)[4]>(x[0]), hi, lo);
+            *reinterpret_cast<float4*>(sm.k_hi[half][2 * g][r]) = hi;
+            *reinterpret_cast<float4*>(sm.k_lo[half][2 * g][r]) = lo;
+            split4(reinterpret_cast<const float(&)[4]>(x[4]), hi, lo);
+            *reinterpret_cast<float4*>(sm.k_hi[half][2 * g + 1][r]) = hi;
+            *reinterpret_cast<float4*>(sm.k_lo[half][2 * g + 1][r]) = lo;
         }
+    };
+    // The block's pairs are counted by `turn`: accumulator turn & 1, and the barriers' phase parity turn & 1.
+    // the 24 instructions of one half of a pair, by one thread; half 0 starts the accumulator afresh
+    auto issue = [&](int turn, int half) {
+        if (warp == 0 && elect_one()) {
+            tc_fence_after();
+            const uint32_t acc = tmem + (turn & 1) * BIAS_BLOCKS;
+            const uint64_t k_hi = smem_desc(smem_u32(sm.k_hi[half]), BIAS_KEYS * 16, 128), k_lo = smem_desc(smem_u32(sm.k_lo[half]), BIAS_KEYS * 16, 128);
+            const uint64_t q_hi = smem_desc(smem_u32(sm.q_hi[half * (BIAS_HALF / 4)]), BIAS_BLOCKS * 16, 128);
+            const uint64_t q_lo = smem_desc(smem_u32(sm.q_lo[half * (BIAS_HALF / 4)]), BIAS_BLOCKS * 16, 128);
+            // a descriptor's address counts 16-byte units; an instruction takes two chunks of each image
+#pragma unroll
+            for (int ks = 0; ks < BIAS_HALF / 8; ++ks) mma_tf32_ss(acc, k_hi + ks * (2 * BIAS_KEYS), q_hi + ks * (2 * BIAS_BLOCKS), IDESC_BIAS, half + ks > 0);
+#pragma unroll
+            for (int ks = 0; ks < BIAS_HALF / 8; ++ks) mma_tf32_ss(acc, k_lo + ks * (2 * BIAS_KEYS), q_hi + ks * (2 * BIAS_BLOCKS), IDESC_BIAS, true);
+#pragma unroll
+            for (int ks = 0; ks < BIAS_HALF / 8; ++ks) mma_tf32_ss(acc, k_hi + ks * (2 * BIAS_KEYS), q_lo + ks * (2 * BIAS_BLOCKS), IDESC_BIAS, true);
+            mma_commit(&sm.done[half]);
+        }
+        __syncwarp();
+    };
+    // one warp watches the barrier, everybody learns the outcome
+    auto wait_done = [&](int half, int turn) {
+        return __syncthreads_and(warp != 0 || mbar_wait(&sm.done[half], turn & 1, abort_flag, status, STATUS_WAIT_SCORES)) != 0;
+    };
+    // warp w: the 32 keys of lane quarter w % 4, query blocks 16 (w / 4) .. + 15 of this pass
+    auto write_out = [&](int pair, int turn) {
+        float2 d[8];
+        tc_fence_after();
+        tmem_ld16_sync(tmem + (uint32_t((warp % 4) * 32) << 16) + (turn & 1) * BIAS_BLOCKS + (warp / 4) * 16, d);
+        tc_fence_before();
+        const int row = (warp % 4) * 32 + lane, tile = 2 * pair + row / KEY_TILE, slot = row % KEY_TILE;
+        if (tile < k_tiles) {
+            const bool live = tile * KEY_TILE + slot_key(slot) < n_keys;  // slots past the last key: -inf keeps them out of the softmax
+            float* at = bias + (size_t(head) * q_blocks + b0 + (warp / 4) * 16) * (size_t(k_tiles) * KEY_TILE) + tile * KEY_TILE + slot;
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (b0 + (warp / 4) * 16 + j < q_blocks) at[size_t(j) * k_tiles * KEY_TILE] = live ? (j % 2 ? d[j / 2].y : d[j / 2].x) * scale_log2 : -INFINITY;
+        }
+    };
+
+    bool ok = true;
+    int last = -1, turn = 0;       // the pair whose instructions are in flight; this block's count of pairs
+    int seen[2] = {0, 0}, sent[2] = {0, 0};  // per half: completions waited for, sets of instructions issued
+    uint4 raw[2];
+    if (blockIdx.x < pairs) fetch(blockIdx.x, 0, raw);
+    for (int pair = blockIdx.x; pair < pairs; pair += gridDim.x, ++turn) {
+        // images 0 were last read by the first half of the pair before: waited for at the end of that turn
+        make_images(pair, 0, raw);
+        fetch(pair, 1, raw);  // in flight while the pair before is written out
+        fence_proxy_async();  // the images, written through the generic proxy, are read by the tensor core
+        __syncthreads();
+        issue(turn, 0);
+        ++sent[0];
+        if (last >= 0) {
+            ok = wait_done(1, turn - 1);  // the pair before is whole (and images 1 are free)
+            if (!ok) break;
+            ++seen[1];
+            write_out(last, turn - 1);
+        }
+        make_images(pair, 1, raw);
+        const int next = pair + gridDim.x;
+        if (next < pairs) fetch(next, 0, raw);
+        fence_proxy_async();
+        __syncthreads();  // also: the accumulator of the pair before has been read before anything is issued into it again
+        issue(turn, 1);
+        ++sent[1];
+        last = pair;
+        ok = wait_done(0, turn);  // images 0 are free for the next pair
+        if (!ok) break;
+        ++seen[0];
+    }
+    if (ok && last >= 0) {
+        ok = wait_done(1, turn - 1);
+        if (ok) ++seen[1], write_out(last, turn - 1);
+    }
+    if (!ok && threadIdx.x == 0) {  // whatever was issued must finish before tensor memory is freed
+        int never = 0;
+        for (int half = 0; half < 2; ++half)
+            if (sent[half] > seen[half]) mbar_wait(&sm.done[half], (sent[half] - 1) & 1, &never, nullptr, 0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        tmem_dealloc(tmem, 2 * BIAS_BLOCKS);
     }
 }
 
@@ -305,26 +439,33 @@ extern "C" int unica_b200_quantize_v_fp4(const void* v, unica_token_layout layou
 }
 
 static int smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean, RopeTable rope, int heads,
-                       int q_blocks, int n_keys, float scale_log2, float* bias, void* stream) {
-    if (!k || !k_mean || !q_mean || !bias) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: null pointer");
+                       int q_blocks, int n_keys, float scale_log2, float* bias, int* status, void* stream) {
+    if (!k || !k_mean || !q_mean || !bias || !status) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: null pointer");
     if (heads <= 0 || q_blocks <= 0 || n_keys <= 0) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: heads, q_blocks and n_keys must be positive");
-    const int tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
-    if (cudaFuncSetAttribute(smooth_bias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BIAS_SMEM) != cudaSuccess)
+    if (int e = unica_check_device()) return e;
+    const int tiles = (n_keys + KEY_TILE - 1) / KEY_TILE, pairs = (tiles + 1) / 2, passes = (q_blocks + BIAS_BLOCKS - 1) / BIAS_BLOCKS;
+    if (heads > 65535 || passes > 65535) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias: more than 65535 heads or passes of 64 query blocks");
+    constexpr int SMEM = int(sizeof(BiasSmem)) + 128;
+    if (cudaFuncSetAttribute(smooth_bias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
         return unica_check_launch("smooth_bias (shared memory size)");
-    smooth_bias_kernel<<<dim3(tiles, heads), FP4_THREADS, BIAS_SMEM, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias, rope);
+    // a block per SM (its images take most of the shared memory); some four waves of blocks, each walking over its
+    // strip of key-tile pairs with the query blocks' images built once
+    const long long others = (long long)heads * passes;
+    const int strips = int(std::min<long long>(pairs, std::max<long long>(1, (4 * 148 + others - 1) / others)));
+    smooth_bias_kernel<<<dim3(strips, heads, passes), BIAS_THREADS, SMEM, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias, rope, status);
     return unica_check_launch("smooth_bias");
 }
 
 extern "C" int unica_b200_smooth_bias(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
-                                      int heads, int q_blocks, int n_keys, float scale_log2, float* bias, void* stream) {
-    return smooth_bias(k, layout, k_mean, q_mean, RopeTable{nullptr, 0}, heads, q_blocks, n_keys, scale_log2, bias, stream);
+                                      int heads, int q_blocks, int n_keys, float scale_log2, float* bias, int* status, void* stream) {
+    return smooth_bias(k, layout, k_mean, q_mean, RopeTable{nullptr, 0}, heads, q_blocks, n_keys, scale_log2, bias, status, stream);
 }
 
 extern "C" int unica_b200_smooth_bias_rope(const void* k, unica_token_layout layout, const float* k_mean, const float* q_mean,
                                            const void* rope, long long rope_batch_stride, int heads, int q_blocks, int n_keys,
-                                           float scale_log2, float* bias, void* stream) {
+                                           float scale_log2, float* bias, int* status, void* stream) {
     if (!rope) return unica_fail(UNICA_B200_ERR_ARGUMENT, "smooth_bias_rope: null table");
     return smooth_bias(k, layout, k_mean, q_mean, RopeTable{static_cast<const __half*>(rope), rope_batch_stride}, heads, q_blocks, n_keys,
-                       scale_log2, bias, stream);
+                       scale_log2, bias, status, stream);
 }

@@ -98,7 +98,8 @@ def quantize_v4(v: torch.Tensor) -> tuple[FP4V, torch.Tensor]:
 
 def smooth_bias(k: torch.Tensor, k_mean: torch.Tensor, q_mean: torch.Tensor, qk_outer: torch.Tensor | None = None,
                 padded_keys: int | None = None, rope=None) -> torch.Tensor:
-    """The scores' share of Q's block means, added back exactly: q_mean[block] . (k - k_mean) in FP32, times
+    """The scores' share of Q's block means, added back exactly: q_mean[block] . (k - k_mean) to FP32 accuracy (on the
+    tensor core, each value as two tf32 parts), times
     log2(e) / sqrt(128) (the attention kernel adds it to scores that are already in the log2 domain; the reference's
     table is divided by qk_outer instead, an argument kept here for the call's sake).  Keys of each 64-key tile in slot
     order, 0 past the last key.  Returns float32 [batch, heads, blocks, ceil64(n_keys)]."""
@@ -114,7 +115,7 @@ def smooth_bias(k: torch.Tensor, k_mean: torch.Tensor, q_mean: torch.Tensor, qk_
     bias = torch.empty(batch, heads, blocks, padded, device=k.device)
     lib.call("unica_b200_smooth_bias" + ("_rope" if rope is not None else ""), lib.ptr(k), _layout(k),
              lib.ptr(k_mean.float().contiguous()), lib.ptr(q_mean.float().contiguous()), *unica.rope_args(rope, k), batch * heads,
-             blocks, n, HEAD_DIM**-0.5 * LOG2E, lib.ptr(bias), lib.stream())
+             blocks, n, HEAD_DIM**-0.5 * LOG2E, lib.ptr(bias), lib.ptr(unica.status_word(k.device)), lib.stream())
     return bias
 
 

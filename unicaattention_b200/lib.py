@@ -54,11 +54,11 @@ SIGNATURES = {
     "unica_b200_nvfp4_outer": [_P, _P, _P, _I, _I, _P, _P],
     "unica_b200_quantize_fp4_rows": [_P, TokenLayout, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_v_fp4": [_P, TokenLayout, _P, _P, _I, _I, _P, _P, _P, _P],
-    "unica_b200_smooth_bias": [_P, TokenLayout, _P, _P, _I, _I, _I, _F, _P, _P],
+    "unica_b200_smooth_bias": [_P, TokenLayout, _P, _P, _I, _I, _I, _F, _P, _P, _P],
     "unica_b200_channel_stats_rope": [_P, TokenLayout, _P, _LL, _I, _I, _I, _P, _P, _P, _P, _P],
     "unica_b200_quantize_int8_rope": [_P, TokenLayout, _P, _P, _LL, _I, _I, _I, _I, _P, _P, _P],
     "unica_b200_quantize_fp4_rows_rope": [_P, TokenLayout, _P, _I, _P, _LL, _P, _I, _I, _I, _I, _P, _P, _P],
-    "unica_b200_smooth_bias_rope": [_P, TokenLayout, _P, _P, _P, _LL, _I, _I, _I, _F, _P, _P],
+    "unica_b200_smooth_bias_rope": [_P, TokenLayout, _P, _P, _P, _LL, _I, _I, _I, _F, _P, _P, _P],
 }
 
 
