@@ -64,5 +64,7 @@ def test_host_groups_are_small_at_both_ends():
             sizes = group_sizes(heads, largest)
             assert sum(sizes) == heads and all(s >= 1 for s in sizes)
             assert max(sizes) <= (largest or max(1, -(-heads // 8)))
-            assert sizes[0] <= 2 and sizes[-1] <= 2
-    assert group_sizes(40) == [2, 4, 5, 5, 5, 3, 5, 5, 4, 2]
+            assert sizes[0] == 1 and sizes[-1] <= 2
+            assert all(b - a <= 1 for a, b in zip(sizes, sizes[1:])), "a group's copy must fit behind the group before it"
+    assert group_sizes(40) == [1, 2, 3, 4] + [5] * 5 + [3, 2]
+    assert group_sizes(40, 4) == [1, 2, 3] + [4] * 8 + [2]

@@ -1,5 +1,5 @@
-"""attention() for tensors that live in host memory: the heads go through the GPU in groups (small ones first and last,
-see group_sizes), so that the copy of the next group's q, k, v, the kernels of this one and the copy of the previous
+"""attention() for tensors that live in host memory: the heads go through the GPU in groups (growing at first, a small
+one last: see group_sizes), so that the copy of the next group's q, k, v, the kernels of this one and the copy of the previous
 group's output run at the same time (three streams).  Heads are independent (every head has its own statistics and scales), so the result is bit for bit that of
 one call on the whole tensors.
 
@@ -23,19 +23,21 @@ def _streams(device: torch.device):
 
 
 def group_sizes(heads: int, largest: int | None = None) -> list[int]:
-    """Heads per group, in order: small groups first and last, so that little of the first copy in and of the last copy
-    out is left without kernels to hide behind, and groups of `largest` (default: an eighth of the heads) in between.
-    40 heads: 2, 4, 5, 5, 5, 3, 5, 5, 4, 2."""
+    """Heads per group, in order.  The copies in run back to back, a head's worth taking a little less time than its
+    kernels, and a group can start when its last head has arrived: so the groups grow by one head at a time (1, 2, 3, ..:
+    each is there by the time the one before it is done), then stay at `largest` (default: an eighth of the heads), and
+    the last one is small because its copy out has no kernels to hide behind.
+    40 heads, largest 4: 1, 2, 3, 4, 4, 4, 4, 4, 4, 4, 4, 2."""
     largest = max(1, -(-heads // 8)) if largest is None else max(1, largest)
-    front, back, left, size = [], [], heads, min(2, largest)
-    while left > 0:
-        for side in (front, back):
-            take = min(size, left)
-            if take:
-                side.append(take)
-                left -= take
-        size = min(2 * size, largest)
-    return front + back[::-1]
+    back = [min(2, largest)] if heads >= 4 else []
+    room = heads - sum(back)
+    front, size = [], 1
+    while size < largest and sum(front) + size <= room:
+        front.append(size)
+        size += 1
+    left = room - sum(front)
+    middle = [largest] * (left // largest) + ([left % largest] if left % largest else [])
+    return front + middle + back
 
 
 def attention_host(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor | None = None,
