@@ -257,6 +257,11 @@ __global__ void __launch_bounds__(BIAS_THREADS, 1) smooth_bias_kernel(const __nv
     const float* mean = k_mean + head * HEAD_DIM;
     // A thread makes the images of one key (threads in key order: conflict-free 16-byte stores), 16 channels of each half
     const int r = threadIdx.x % BIAS_KEYS, g0 = 2 * (threadIdx.x / BIAS_KEYS);  // groups of 8 channels g0, g0 + 1 of a half
+    float mine[2][16];  // the mean of K in this thread's channels
+#pragma unroll
+    for (int half = 0; half < 2; ++half)
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[half][j] = mean[half * BIAS_HALF + g0 * 8 + j];
     auto key_of = [&](int pair) { return (2 * pair + r / KEY_TILE) * KEY_TILE + slot_key(r % KEY_TILE); };
     auto fetch = [&](int pair, int half, uint4 (&raw)[2]) {  // 32 contiguous bytes of the key's row
         const int key = key_of(pair);
@@ -282,8 +287,8 @@ __global__ void __launch_bounds__(BIAS_THREADS, 1) smooth_bias_kernel(const __nv
             }
             if (live) {
                 if (rope.table) rope8(x, rope.row(in, head, key), channel);
-                const float4 m0 = *reinterpret_cast<const float4*>(mean + channel), m1 = *reinterpret_cast<const float4*>(mean + channel + 4);
-                x[0] -= m0.x, x[1] -= m0.y, x[2] -= m0.z, x[3] -= m0.w, x[4] -= m1.x, x[5] -= m1.y, x[6] -= m1.z, x[7] -= m1.w;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) x[j] -= mine[half][i * 8 + j];
             }
             float4 hi, lo;
             split4(reinterpret_cast<const float(&)[4]>(x[0]), hi, lo);
@@ -337,12 +342,13 @@ __global__ void __launch_bounds__(BIAS_THREADS, 1) smooth_bias_kernel(const __nv
     bool ok = true;
     int last = -1, turn = 0;       // the pair whose instructions are in flight; this block's count of pairs
     int seen[2] = {0, 0}, sent[2] = {0, 0};  // per half: completions waited for, sets of instructions issued
-    uint4 raw[2];
-    if (blockIdx.x < pairs) fetch(blockIdx.x, 0, raw);
+    uint4 raw[2][2], ahead[2][2];  // this pair's and the next pair's 2 x 32 bytes of the thread's key: loaded a whole pair ahead
+    if (blockIdx.x < pairs) fetch(blockIdx.x, 0, raw[0]), fetch(blockIdx.x, 1, raw[1]);
     for (int pair = blockIdx.x; pair < pairs; pair += gridDim.x, ++turn) {
+        const int next = pair + gridDim.x;
+        if (next < pairs) fetch(next, 0, ahead[0]), fetch(next, 1, ahead[1]);
         // images 0 were last read by the first half of the pair before: waited for at the end of that turn
-        make_images(pair, 0, raw);
-        fetch(pair, 1, raw);  // in flight while the pair before is written out
+        make_images(pair, 0, raw[0]);
         fence_proxy_async();  // the images, written through the generic proxy, are read by the tensor core
         __syncthreads();
         issue(turn, 0);
@@ -353,9 +359,7 @@ __global__ void __launch_bounds__(BIAS_THREADS, 1) smooth_bias_kernel(const __nv
             ++seen[1];
             write_out(last, turn - 1);
         }
-        make_images(pair, 1, raw);
-        const int next = pair + gridDim.x;
-        if (next < pairs) fetch(next, 0, raw);
+        make_images(pair, 1, raw[1]);
         fence_proxy_async();
         __syncthreads();  // also: the accumulator of the pair before has been read before anything is issued into it again
         issue(turn, 1);
@@ -364,6 +368,8 @@ __global__ void __launch_bounds__(BIAS_THREADS, 1) smooth_bias_kernel(const __nv
         ok = wait_done(0, turn);  // images 0 are free for the next pair
         if (!ok) break;
         ++seen[0];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) raw[half][0] = ahead[half][0], raw[half][1] = ahead[half][1];
     }
     if (ok && last >= 0) {
         ok = wait_done(1, turn - 1);
@@ -451,7 +457,8 @@ static int smooth_bias(const void* k, unica_token_layout layout, const float* k_
     // a block per SM (its images take most of the shared memory); some four waves of blocks, each walking over its
     // strip of key-tile pairs with the query blocks' images built once
     const long long others = (long long)heads * passes;
-    const int strips = int(std::min<long long>(pairs, std::max<long long>(1, (4 * 148 + others - 1) / others)));
+    // (at least eight pairs to a block where there are that many: the query blocks' images cost about two pairs' work)
+    const int strips = int(std::min<long long>(std::max(1, pairs / 8), std::max<long long>(1, (4 * 148 + others - 1) / others)));
     smooth_bias_kernel<<<dim3(strips, heads, passes), BIAS_THREADS, SMEM, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias, rope, status);
     return unica_check_launch("smooth_bias");
