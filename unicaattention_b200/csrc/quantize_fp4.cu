@@ -454,11 +454,13 @@ static int smooth_bias(const void* k, unica_token_layout layout, const float* k_
     constexpr int SMEM = int(sizeof(BiasSmem)) + 128;
     if (cudaFuncSetAttribute(smooth_bias_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
         return unica_check_launch("smooth_bias (shared memory size)");
-    // a block per SM (its images take most of the shared memory); some four waves of blocks, each walking over its
-    // strip of key-tile pairs with the query blocks' images built once
+    // a block per SM (its images take most of the shared memory); at most four full waves of blocks, each walking over
+    // its strip of key-tile pairs with the query blocks' images built once
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        return unica_check_launch("smooth_bias (device)");
     const long long others = (long long)heads * passes;
-    // (at least eight pairs to a block where there are that many: the query blocks' images cost about two pairs' work)
-    const int strips = int(std::min<long long>(std::max(1, pairs / 8), std::max<long long>(1, (4 * 148 + others - 1) / others)));
+    const int strips = int(std::min<long long>(pairs, std::max<long long>(1, 4LL * sms / others)));
     smooth_bias_kernel<<<dim3(strips, heads, passes), BIAS_THREADS, SMEM, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const __nv_bfloat16*>(k), to_layout(layout), k_mean, q_mean, q_blocks, n_keys, scale_log2, bias, rope, status);
     return unica_check_launch("smooth_bias");
