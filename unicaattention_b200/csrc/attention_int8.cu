@@ -62,6 +62,7 @@ constexpr int TOK_BYTES = 2 * KEY_TILE * 4;     // 512
 constexpr int P_BYTES = QUERY_TILE * KEY_TILE;  // 8192
 constexpr int TMEM_COLUMNS = 512;
 constexpr int COL_S = 0, COL_ACC = 256;
+constexpr int OUTLIER_BATCH = 16;  // outlier keys whose rows are in shared memory at a time (the epilogue of the outliers mode)
 constexpr float REFERENCE_SLACK = 60.0f;  // log2: how far a tile maximum may rise above a row's reference exponent
 
 struct __align__(128) AttSmem {
@@ -516,19 +517,41 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
         if constexpr (OUTLIERS) {
             // The outlier keys were zeros in V8: their exact share p * v / v_scale, with p = 255 * 2^(score - final max),
             // from this row's Q^ (still in shared memory) and the key's K^ row and scale (csrc/flash.cu:748-790).
+            // The keys' K^ rows and V rows are the same for all 128 rows: the flush warps bring them into two P^ slots
+            // that nobody uses any more (sixteen outliers at a time) and meet at a barrier of their own, which every
+            // flush warp reaches whatever happened to it.
             if (ok) ok = mbar_wait_warp(&sm.q_full, 0, abort_flag, status, STATUS_WAIT_TILE);
-            if (ok) {
-                const float sq = q_scale[size_t(head) * q_tiles + q_tile];
-                const float* sk = k_scale + size_t(head) * k_tiles;
-                const uint4* q_row8 = reinterpret_cast<const uint4*>(sm.q + row * 16);  // chunk c: QUERY_TILE uint4 further
-                for (int i = 0; i < n_outliers; ++i) {
-                    const int key = outlier_keys[size_t(head) * n_outliers + i];
-                    if (key < 0 || key >= n_keys) continue;
-                    const uint4* k_row8 = reinterpret_cast<const uint4*>(k8 + (size_t(head) * k_tiles + key / KEY_TILE) * K_BYTES + (key % KEY_TILE) * 16);
+            static_assert(P_RING >= 6 && OUTLIER_BATCH * HEAD_DIM * 4 <= P_BYTES, "two spare P^ slots hold a batch of outlier rows");
+            float* rows_s = reinterpret_cast<float*>(sm.p[4]);                            // [OUTLIER_BATCH][128]
+            uint4* k_rows_s = reinterpret_cast<uint4*>(sm.p[5]);                          // [OUTLIER_BATCH][8]: the key's 128 codes
+            int* keys_s = reinterpret_cast<int*>(sm.p[5] + OUTLIER_BATCH * HEAD_DIM);     // [OUTLIER_BATCH], -1: no such key
+            const int mine = threadIdx.x - FLUSH_WARP * 32;
+            const float sq = q_scale[size_t(head) * q_tiles + q_tile];
+            const float* sk = k_scale + size_t(head) * k_tiles;
+            const uint4* q_row8 = reinterpret_cast<const uint4*>(sm.q + row * 16);  // chunk c: QUERY_TILE uint4 further
+            for (int i0 = 0; i0 < n_outliers; i0 += OUTLIER_BATCH) {
+                const int n = min(OUTLIER_BATCH, n_outliers - i0);
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // the batch before has been used
+                for (int item = mine; item < n * (HEAD_DIM / 4); item += 128)
+                    reinterpret_cast<float4*>(rows_s)[item] =
+                        reinterpret_cast<const float4*>(outlier_rows + (size_t(head) * n_outliers + i0) * HEAD_DIM)[item];
+                for (int item = mine; item < n * (HEAD_DIM / 16); item += 128) {
+                    const int i = item / (HEAD_DIM / 16), c = item % (HEAD_DIM / 16);
+                    const int key = outlier_keys[size_t(head) * n_outliers + i0 + i];
+                    const bool there = key >= 0 && key < n_keys;
+                    k_rows_s[item] = there ? reinterpret_cast<const uint4*>(k8 + (size_t(head) * k_tiles + key / KEY_TILE) * K_BYTES + (key % KEY_TILE) * 16)[c * KEY_TILE]
+                                           : make_uint4(0, 0, 0, 0);
+                    if (c == 0) keys_s[i] = there ? key : -1;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!ok) continue;
+                for (int i = 0; i < n; ++i) {
+                    const int key = keys_s[i];
+                    if (key < 0) continue;
                     int dot = 0;
 #pragma unroll
                     for (int c = 0; c < HEAD_DIM / 16; ++c) {
-                        const uint4 qv = q_row8[c * QUERY_TILE], kv = k_row8[c * KEY_TILE];
+                        const uint4 qv = q_row8[c * QUERY_TILE], kv = k_rows_s[i * (HEAD_DIM / 16) + c];
                         dot = __dp4a(int(qv.x), int(kv.x), dot);
                         dot = __dp4a(int(qv.y), int(kv.y), dot);
                         dot = __dp4a(int(qv.z), int(kv.z), dot);
@@ -536,7 +559,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                     }
                     const float p = ex2(__int2float_rn(dot) * ((sq * sk[key / KEY_TILE]) * scale_log2) - m) * 255.0f;
                     const float2 p2 = make_float2(p, p);
-                    const float2* v_row = reinterpret_cast<const float2*>(outlier_rows + (size_t(head) * n_outliers + i) * HEAD_DIM);
+                    const float2* v_row = reinterpret_cast<const float2*>(rows_s + i * HEAD_DIM);
 #pragma unroll
                     for (int j = 0; j < HEAD_DIM / 2; ++j) o[j] = fma2(p2, v_row[j], o[j]);
                 }
