@@ -20,9 +20,11 @@
 // What was measured on the way here (B200): the exponentials of two softmax warps per scheduler alone take 567 cycles
 // per 128 x 64 tile and overlap with a flush warp's conversions almost freely, the tensor pipe alone 476; what decides
 // the kernel's speed is the chain of hand-overs between the roles.  A lone thread pays some 250 cycles for an mbarrier
-// probe, so MMA issue is dealt out to four threads, a thread waits for two barriers with both probes in flight, and the
-// completion of tcgen05.mma is passed on by the issuing thread through words in shared memory that a waiting warp
-// reads in 30 cycles.
+// probe, so MMA issue is dealt out to four threads and a thread waits for two barriers with both probes in flight.  A
+// thread or warp that has to wait longer is suspended by the hardware on the barrier (mbarrier.try_wait with a time
+// hint) instead of spinning: a spinning waiter takes issue slots from the computing warps of its scheduler.  Per token
+// the completion of tcgen05.mma is instead passed on by the issuing thread through words in shared memory that a
+// waiting warp reads in 30 cycles.
 //
 // Numerics (bench/emulate.py:298-369 with the accurate contract): scores in the log2 domain, c = (q_scale * k_scale) *
 // log2(e) / sqrt(d); P^ as u8 against the tile's own maximum; the denominator sums the rounded P^ (per channel) or
@@ -158,6 +160,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
     if (q_tile * QUERY_TILE >= n_queries) return;  // the padding tile of an odd count: nothing to do
     const int k_tiles = (n_keys + KEY_TILE - 1) / KEY_TILE;
     volatile int* abort_flag = &sm.abort_flag;
+    // How the softmax and flush warps learn that S(t) / P.V(t) is complete.  Per channel and with outliers they wait on the
+    // instructions' own barrier, suspended by the hardware; per token that measured 1 % slower than looking at a word
+    // in shared memory that the issuing thread, which watches the barrier anyway, advances (flag_publish).
+    constexpr bool FLAG_WAITS = V_TOKEN;
 
     if (threadIdx.x == 0) {
         sm.abort_flag = 0;
@@ -211,12 +217,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 mma_commit(&sm.s_full[buf]);
                 TRACE(2);
                 EVENT(6, n);
-                // the thread watches its own instructions complete and tells the softmax threads through a word they can
-                // look at cheaply
+                // the thread watches its own instructions complete before it turns to its next tile (going on at once
+                // measured slower) and, per token, tells the softmax threads through a word they can look at cheaply
                 ok = mbar_wait<SERVICE_SLEEP>(&sm.s_full[buf], (n / S_RING) & 1, abort_flag, status, STATUS_WAIT_SCORES);
                 if (!ok) break;
-                tc_fence_before();
-                flag_publish(&sm.s_done[buf], n + 1);
+                if (FLAG_WAITS) {
+                    tc_fence_before();
+                    flag_publish(&sm.s_done[buf], n + 1);
+                }
                 TRACE(3);
                 stage += 2;
                 if (stage >= STAGES) stage -= STAGES, phase ^= 1;
@@ -274,11 +282,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
                 mma_commit(&sm.kv_empty[stage]);
                 TRACE(4);
                 EVENT(2, t);
-                // P.V(t) complete: the flush threads are told through a word they can look at cheaply, and the stage is free
+                // P.V(t) complete: the stage is free (and, per token, the flush threads are told through a word)
                 ok = mbar_wait<SERVICE_SLEEP>(&sm.kv_empty[stage], phase, abort_flag, status, STATUS_WAIT_STAGE);
                 if (!ok) break;
-                tc_fence_before();
-                flag_publish(&sm.acc_done[b], t + 1);
+                if (FLAG_WAITS) {
+                    tc_fence_before();
+                    flag_publish(&sm.acc_done[b], t + 1);
+                }
                 if (t + STAGES < k_tiles) copy_tile(t + STAGES, stage);
                 TRACE(5);
                 stage += 2;
@@ -335,7 +345,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             // scores were issued after it), so the barrier is only looked at, and the look is started before the wait for
             // the scores so that its latency hides behind that.
             const bool scales_there = !V_TOKEN || mbar_try(&sm.kv_full[stage], kv_phase);
-            if (!flag_wait_warp(&sm.s_done[buf], t + 1, abort_flag, status, STATUS_WAIT_SCORES)) return false;
+            if (FLAG_WAITS ? !flag_wait_warp(&sm.s_done[buf], t + 1, abort_flag, status, STATUS_WAIT_SCORES)
+                           : !mbar_wait_warp<0>(&sm.s_full[buf], (t / S_RING) & 1, abort_flag, status, STATUS_WAIT_SCORES))
+                return false;
             TRACE(0);
             EVENT(0, t);
             if (V_TOKEN && !__all_sync(0xffffffffu, scales_there) && !mbar_wait_warp(&sm.kv_full[stage], kv_phase, abort_flag, status, STATUS_WAIT_TILE))
@@ -470,7 +482,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1)
             const int b = t & 1;
             TRACE(7);
             // P.V(t) was issued after the softmax of tile t had delivered its record, so the record is there too
-            if (!flag_wait_warp(&sm.acc_done[b], t + 1, abort_flag, status, STATUS_WAIT_PV)) {
+            if (FLAG_WAITS ? !flag_wait_warp(&sm.acc_done[b], t + 1, abort_flag, status, STATUS_WAIT_PV)
+                           : !mbar_wait_warp<0>(&sm.kv_empty[t % STAGES], (t / STAGES) & 1, abort_flag, status, STATUS_WAIT_PV)) {
                 ok = false;
                 break;
             }

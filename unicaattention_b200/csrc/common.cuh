@@ -165,6 +165,22 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, int parity) {
     return done != 0;
 }
 
+// The same probe, but the thread may be suspended by the hardware for up to UNICA_WAIT_HINT_NS until the phase completes:
+// a waiting thread then issues no instructions, where a loop of plain probes takes issue slots from the computing
+// warps of its scheduler.
+#ifndef UNICA_WAIT_HINT_NS
+#define UNICA_WAIT_HINT_NS 2000
+#endif
+__device__ __forceinline__ bool mbar_try_suspended(uint64_t* bar, int parity) {
+    uint32_t done;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3; selp.u32 %0, 1, 0, p; }"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(uint32_t(UNICA_WAIT_HINT_NS))
+        : "memory");
+    return done != 0;
+}
+
 // Waits for the phase of parity `parity`.  abort_flag: a word in shared memory any thread of the block sets when it
 // gave up; everyone else then stops waiting at once.  Returns false when the wait was abandoned.
 // A waiting warp shares its scheduler with computing warps and every instruction of its loop takes an issue slot from
@@ -228,7 +244,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity, volatile in
         if (mbar_try(bar, parity)) return true;
         const long long start = clock64();
         while (true) {
-            if (mbar_try(bar, parity)) return true;
+            if (UNICA_WAIT_HINT_NS > 0 ? mbar_try_suspended(bar, parity) : mbar_try(bar, parity)) return true;
             if (*abort_flag) return false;
             if (clock64() - start > WAIT_LIMIT_CYCLES) {
                 *abort_flag = 1;
@@ -304,6 +320,25 @@ template <unsigned SLEEP_NS = WAIT_SLEEP_NS>
 __device__ __forceinline__ bool mbar_wait2(uint64_t* bar_a, int parity_a, uint64_t* bar_b, int parity_b, volatile int* abort_flag, int* status,
                                            int code) {
     if (parity_b < 0) return mbar_wait<SLEEP_NS>(bar_a, parity_a, abort_flag, status, code);
+    if constexpr (SLEEP_NS == 0 && UNICA_WAIT_HINT_NS > 0) {  // one look at both with the probes in flight together, then suspended waits
+        uint32_t seen;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            ".reg .u32 a, b;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 q, [%3], %4;\n\t"
+            "selp.u32 a, 1, 0, p;\n\t"
+            "selp.u32 b, 2, 0, q;\n\t"
+            "or.b32 %0, a, b;\n\t"
+            "}"
+            : "=r"(seen)
+            : "r"(smem_u32(bar_a)), "r"(parity_a), "r"(smem_u32(bar_b)), "r"(parity_b)
+            : "memory");
+        if (seen == 3) return true;
+        if (!(seen & 1) && !mbar_wait<0>(bar_a, parity_a, abort_flag, status, code)) return false;
+        return (seen & 2) || mbar_wait<0>(bar_b, parity_b, abort_flag, status, code);
+    }
     if (mbar_probe_many2<SLEEP_NS>(bar_a, parity_a, bar_b, parity_b)) return true;
     const long long start = clock64();
     while (true) {
