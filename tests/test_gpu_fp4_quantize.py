@@ -102,3 +102,27 @@ def test_smooth_bias_is_exact_to_float():
     bound = (q_mean.abs().double() @ centred.abs().transpose(-1, -2))[..., order[valid]] * 2.0**-20 + 1e-6
     assert ((got - want).abs() <= bound).all(), ((got - want).abs() / bound).max()
     assert bool(torch.isneginf(bias[..., ~valid]).all())  # slots past the last key
+
+
+def test_smooth_bias_many_query_blocks_and_an_odd_tile_count():
+    """More than 64 query blocks (several passes of the kernel's 64 columns, the last one partly empty) and an odd number
+    of key tiles (the last pair of tiles half empty)."""
+    import unicaattention_b200 as unica
+
+    g = torch.Generator().manual_seed(11)
+    blocks, n_keys = 150, 3 * 64 - 7
+    q_mean = torch.randn((1, 2, blocks, 128), generator=g).cuda() * torch.linspace(0.5, 2.0, blocks).cuda()[:, None]
+    k = (torch.randn((1, 2, n_keys, 128), generator=g) + 0.5).bfloat16().cuda()
+    k_mean = unica.rope_stats(k)[0]
+    bias = unica.smooth_bias(k, k_mean, q_mean)
+    unica.check_status()
+    assert bias.shape == (1, 2, blocks, 192)
+    centred = k.double() - k_mean.double()[..., None, :]
+    expected = (q_mean.double() @ centred.transpose(-1, -2)) * (128**-0.5 * 1.4426950408889634)
+    slot_key = torch.tensor(unica.fp4.SLOT_KEY, device="cuda")
+    order = (torch.arange(3, device="cuda")[:, None] * 64 + slot_key).flatten()
+    valid = order < n_keys
+    got, want = bias[..., valid].double(), expected[..., order[valid]]
+    bound = (q_mean.abs().double() @ centred.abs().transpose(-1, -2))[..., order[valid]] * 2.0**-20 + 1e-6
+    assert ((got - want).abs() <= bound).all(), ((got - want).abs() / bound).max()
+    assert bool(torch.isneginf(bias[..., ~valid]).all())
